@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Headline benchmark: images/s of ResNet-50 (v1, BN folded) batch-256 inference through the
+Occamy runtime C ABI on B200, batch-sharded over N GPUs, logits gathered with NCCL.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...     # the CPU restatement on the host cores
+
+One step = one inference of the whole batch: the replayed call sequence a compiled model
+would issue (pool init, mem-offsets, constant uploads, 53 fused conv calls, adds, pools,
+Gemm, softmax).  `value` times it with the input batch resident in HBM (device->device
+copy into the pool, logits left on the device); `e2e` times the same calls with the batch
+in pinned host memory and the logits read back to the host.  Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+GLOBAL_BATCH = 256
+METRIC = "images/sec ResNet-50 b=256"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, mx, power, reasons = [], [], [], set()
+        for line in self.tmp.read().splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.tmp.name)
+        if sm:
+            # median over the samples taken under load (upper half of the power readings)
+            cut = statistics.median(power)
+            loaded = [s for s, p in zip(sm, power) if p >= cut] or sm
+            out.update(sm_mhz=statistics.median(loaded), sm_max_mhz=max(mx),
+                       reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_baseline_sample(batch: int, repeats: int):
+    """Times the CPU restatement (oracle port) of the same graph on the host cores."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import run_graph_oracle
+    from occamy_b200 import graphs
+    g = graphs.resnet50(batch=batch, seed=0, variant="v1", softmax=True)
+    x = graphs.make_input(g, 0)
+    run_graph_oracle(g, x)  # warm-up (page in the library, OpenMP pool)
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        run_graph_oracle(g, x)
+    dt = (time.perf_counter() - t0) / repeats
+    return batch / dt, dt
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's CPU implementation of the path.  Its own onnx-mlir
+    CPU build cannot be produced offline, so this is the C restatement (oracle port), all
+    host threads, on a bounded sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample_batch = 2
+    cores = os.cpu_count() or 1
+    for _ in range(max(args.warmup, 1)):
+        cpu_baseline_sample(sample_batch, 1)
+    times = []
+    for _ in range(args.steps):
+        _, dt = cpu_baseline_sample(sample_batch, 1)
+        times.append(dt)
+    ms = 1000.0 * sum(times) / len(times)
+    value = sample_batch / (ms / 1000.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "ResNet-50 v1 inference, global batch 256 (N(0,1) images, "
+                               "He-normal weights)", "global_batch": GLOBAL_BATCH},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample_batch} images per step of the batch-256 workload, "
+                                   "fp32 C restatement with OpenMP"},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch")
+    ap.add_argument("--math", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--graph", default="resnet50", choices=["resnet50", "mobilenet_v2", "vgg16"])
+    ap.add_argument("--fuse", type=int, default=1)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--per-layer", default="", help="write a per-launch roofline table here")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from occamy_b200 import graphs, replay
+    from occamy_b200 import runtime as rt
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: no CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    assert args.batch % world == 0, "global batch must divide over the ranks"
+    per_rank = args.batch // world
+
+    rt.set_math_mode(rt.MATH_BF16 if args.math == "bf16" else rt.MATH_FP32)
+    builder = getattr(graphs, args.graph)
+    g = builder(batch=per_rank, seed=0)
+    prog = g.to_program()
+    prog.lower(fuse=args.fuse, dealloc_opt=True, pool_opt=True)
+    binding = replay.Binding()
+    stream = torch.cuda.ExternalStream(rt.lib().occamy_stream())
+
+    # rank r owns images [r*B/R, (r+1)*B/R) of the seeded global batch
+    full = graphs.make_input(builder(batch=1, seed=0), 0).shape[1:]
+    rng = np.random.Generator(np.random.PCG64(1000003 + rank))
+    x_host = torch.from_numpy(rng.standard_normal((per_rank,) + tuple(full), dtype=np.float32)).pin_memory()
+    x_dev = x_host.cuda(non_blocking=False)
+    n_out = g.shapes[g.outputs[0]][1]
+    out_dev = torch.empty((per_rank, n_out), dtype=torch.float32, device="cuda")
+    gathered = torch.empty((args.batch, n_out), dtype=torch.float32, device="cuda")
+    out_host = torch.empty((args.batch, n_out), dtype=torch.float32).pin_memory()
+    import ctypes as C
+
+    def step_resident():
+        prog.run_raw(binding, x_dev.data_ptr(), 3, [out_dev.data_ptr()], 3)
+        if world > 1:
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(gathered, out_dev)
+
+    def step_e2e():
+        prog.run_raw(binding, x_host.data_ptr(), 1, [out_dev.data_ptr()], 3)
+        with torch.cuda.stream(stream):
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, out_dev)
+                src = gathered
+            else:
+                src = out_dev
+            if rank == 0:
+                out_host[: src.shape[0]].copy_(src, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+        for _ in range(steps):
+            fn()
+        with torch.cuda.stream(stream):
+            e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        barrier()
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- warm-up (first call packs and caches the weights) ----
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    torch.cuda.synchronize()
+    if rt.last_error():
+        raise SystemExit("runtime reported an error during warm-up")
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    c0 = rt.counters()
+    ms_total = timed(step_resident, args.steps)
+    c1 = rt.counters()
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if sampler else None
+
+    # ---- dominant kernel: CUDA-event pair around every tensor-core launch ----
+    rt.lib().occamy_profile_begin()
+    prof_steps = 3
+    for _ in range(prof_steps):
+        step_resident()
+    buf = (C.c_float * 4096)()
+    n_prof = rt.lib().occamy_profile_end(buf, 4096)
+    per_step = n_prof // prof_steps if prof_steps else 0
+    tc_ms = [[buf[s * per_step + i] for s in range(prof_steps)] for i in range(per_step)]
+    tc_ms = [statistics.median(v) for v in tc_ms]
+    tc_total_ms = sum(tc_ms)
+    err = rt.last_error()
+    if err:
+        raise SystemExit(f"runtime reported error {err}")
+
+    ms_step = ms_total / args.steps
+    value = args.batch / (ms_step / 1000.0)
+    e2e_value = args.batch / (ms_e2e / args.steps / 1000.0)
+    peaks = measured_peaks()
+    flops = g.conv_flops()            # algorithmic conv + Gemm FLOPs of this rank's batch
+    achieved = flops / (tc_total_ms / 1000.0) / 1e12 if tc_total_ms > 0 else 0.0
+    peak = peaks["bf16_tflops_sustained"]
+
+    if args.per_layer and rank == 0:
+        write_per_layer(args.per_layer, g, tc_ms, peaks, ms_step)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16" if args.math == "bf16" else "f32", "data": "synthetic",
+        "config": {"workload": f"{g.name} inference, global batch {args.batch} "
+                               f"({per_rank} per GPU), N(0,1) images, He-normal weights, "
+                               f"replayed fused call sequence (fuse={args.fuse})",
+                   "global_batch": args.batch, "parallelism": f"dp{world}",
+                   "l2": "per-step working set (activations > 1 GB) exceeds the 126 MB L2"},
+        "e2e": {"value": e2e_value, "unit": "images/s",
+                "h2d_bytes_per_step": int(x_host.numel() * 4 * world),
+                "d2h_bytes_per_step": int(args.batch * n_out * 4)},
+        "gpu_launches": int(c1["launches"] - c0["launches"]),
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak if peak else None, "traffic": None,
+                     "kernel": "tc_conv_kernel", "launches_per_step": per_step,
+                     "kernel_ms_per_step": tc_total_ms, "peak_source": peaks["source"] +
+                     " (sustained cuBLAS bf16)"},
+    }
+    if not args.no_cpu_baseline and world == 1:
+        cores = os.cpu_count() or 1
+        sample = 4
+        v, dt = cpu_baseline_sample(sample, 3)
+        line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": cores, "kind": "port",
+                                "sample": f"{sample} images (of the batch-256 workload), fp32 C "
+                                          f"restatement with OpenMP, {dt:.2f} s per pass"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def write_per_layer(path, g, tc_ms, peaks, ms_step):
+    """Per-launch table: algorithmic FLOPs and bytes (bf16 activations, bf16 weights) of each
+    convolution / Gemm, its CUDA-event time, and the fraction of max(tensor, HBM) roofline."""
+    rows = []
+    idx = 0
+    for n in g.nodes:
+        if n.op not in ("conv", "gemm"):
+            continue
+        if n.op == "conv":
+            N, K, P, Q = g.shapes[n.out]
+            _, Cg, R, S = g.shapes[n.ins[1]]
+            if n.attrs["groups"] != 1:
+                continue
+            flops = 2 * N * K * P * Q * Cg * R * S
+            xin = int(np.prod(g.shapes[n.ins[0]]))
+            byts = 2 * xin + 2 * K * Cg * R * S + 4 * K + 2 * N * K * P * Q
+            name = f"conv {Cg}->{K} {R}x{S} s{n.attrs['strides'][0]} out {P}x{Q}"
+        else:
+            M, Nn = g.shapes[n.out]
+            Kd = g.shapes[n.ins[0]][1]
+            flops = 2 * M * Nn * Kd
+            byts = 4 * M * Kd + 2 * Nn * Kd + 4 * M * Nn
+            name = f"gemm {M}x{Kd}x{Nn}"
+        if idx >= len(tc_ms):
+            break
+        ms = tc_ms[idx]
+        idx += 1
+        t_tensor = flops / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
+        t_hbm = byts / (peaks["hbm_gbs"] * 1e9) * 1e3
+        bound = max(t_tensor, t_hbm)
+        rows.append((name, flops / 1e9, byts / 1e6, ms, flops / ms / 1e9 if ms else 0,
+                     byts / ms / 1e6 if ms else 0, "tensor" if t_tensor >= t_hbm else "hbm",
+                     bound / ms if ms else 0))
+    with open(path, "w") as f:
+        f.write(f"# {g.name}: per tensor-core launch, ms_per_step {ms_step:.3f}\n")
+        f.write("# layer | GFLOP | MB (bf16 act) | ms | TFLOP/s | GB/s | bound | frac of roofline\n")
+        for r in rows:
+            f.write(f"{r[0]:40s} {r[1]:9.2f} {r[2]:9.2f} {r[3]:8.4f} {r[4]:8.1f} {r[5]:8.1f} "
+                    f"{r[6]:7s} {r[7]:6.3f}\n")
+        f.write(f"# total kernel ms {sum(r[3] for r in rows):.3f}\n")
+
+
+if __name__ == "__main__":
+    main()

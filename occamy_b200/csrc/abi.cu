@@ -1,0 +1,665 @@
+// The C-ABI entry points on the CNN hot path (declared in include/occamy_dnn_api.h) and
+// the dispatch between the fp32 NCHW kernels and the bf16 NHWC / tensor-core kernels.
+#include <cstring>
+#include <vector>
+
+#include "kernels.h"
+#include "runtime.h"
+
+#define OCCAMY_NO_VENDOR_TYPES
+typedef cudaError_t occamy_cuda_error_t;
+struct cudnnContext;
+typedef struct cudnnContext *cudnnHandle_t;
+#include "../../include/occamy_dnn_api.h"
+
+using namespace occ;
+
+namespace {
+
+struct PoolRec {
+  void *base;
+  size_t bytes;
+};
+std::vector<PoolRec> g_pools;
+// The pool of the previous inference, kept so that the next wrapDNNMemPoolInit of the same
+// size costs no cudaMalloc / cudaFree (a compiled model creates and frees its pool on
+// every call).  OCCAMY_POOL_CACHE=0 turns this off.
+PoolRec g_pool_cache = {nullptr, 0};
+bool pool_cache_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char *e = getenv("OCCAMY_POOL_CACHE");
+    v = (e && !strcmp(e, "0")) ? 0 : 1;
+  }
+  return v == 1;
+}
+
+void die(const char *what, cudaError_t e, size_t size) {
+  // Same convention as the reference's memory wrappers (cuda/wrapDNNMalloc.cpp:11-16).
+  printf("[%s] GPU error: (size: %zu) %s\n", what, size, cudaGetErrorString(e));
+  exit(-1);
+}
+
+enum PackLayout { PACK_KRSC = 1, PACK_DW = 2, PACK_FOLD = 3, PACK_RAW = 4 };
+
+// Device pointer of the packed form of the filter at `w`; resident across calls when the
+// filter was uploaded from host memory (a compiled model's constant), otherwise packed
+// into scratch.  `packed_bytes` is the size of the packed form.
+void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int C, int R, int S,
+                     int Sp, int Cp) {
+  Runtime &r = rt();
+  uintptr_t base;
+  TensorRec *rec = reg_find(w, &base);
+  const bool cacheable = r.cache_weights && rec && base == (uintptr_t)w && rec->host_src;
+  WeightKey key{nullptr, 0, layout * 4096 + Sp * 64 + Cp};
+  if (cacheable) {
+    key.src = rec->host_src;
+    key.bytes = rec->host_bytes;
+    auto it = r.wcache.find(key);
+    if (it != r.wcache.end() && it->second.hash == rec->host_hash && it->second.bytes == packed_bytes)
+      return it->second.dev;
+  }
+  ensure_f32(w);
+  void *dst = nullptr;
+  if (cacheable) {
+    PackedWeight &pw = r.wcache[key];
+    if (pw.dev && pw.bytes != packed_bytes) {
+      OCC_CUDA(cudaStreamSynchronize(r.stream));
+      OCC_CUDA(cudaFree(pw.dev));
+      pw.dev = nullptr;
+    }
+    if (!pw.dev) OCC_CUDA(cudaMalloc(&pw.dev, packed_bytes));
+    pw.bytes = packed_bytes;
+    pw.hash = rec->host_hash;
+    pw.layout = layout;
+    dst = pw.dev;
+    r.resident[rec->host_src] = std::make_pair(rec->host_bytes, rec->host_hash);
+  } else {
+    dst = scratch_get(1, packed_bytes);
+  }
+  if (!dst) return nullptr;
+  if (layout == PACK_KRSC) launch_pack_krsc_bf16(w, (bf16 *)dst, K, C, R, S, r.stream);
+  else if (layout == PACK_DW) launch_pack_dw_f32(w, (float *)dst, C, R, S, r.stream);
+  else if (layout == PACK_RAW)
+    OCC_CUDA(cudaMemcpyAsync(dst, w, packed_bytes, cudaMemcpyDeviceToDevice, r.stream));
+  else launch_pack_fold_bf16(w, (bf16 *)dst, K, C, R, S, Sp, Cp, r.stream);
+  return dst;
+}
+
+// Small fp32 constants (biases): the resident copy when there is one, else the tensor itself.
+const float *resident_f32(const float *p, size_t bytes) {
+  uintptr_t base;
+  TensorRec *rec = reg_find(p, &base);
+  if (rt().cache_weights && rec && base == (uintptr_t)p && rec->host_src && rec->host_bytes == bytes) {
+    const float *d = (const float *)packed_weights(p, PACK_RAW, bytes, 0, 0, 0, 0, 0, 0);
+    if (d) return d;
+  }
+  ensure_f32(p);
+  return p;
+}
+
+bool conv_tensor_core(const float *x, const float *w, const float *bias, float *y,
+                      const ConvGeom &g) {
+  Runtime &r = rt();
+  if (g.groups != 1 || g.K % 8 != 0) return false;
+  TcConvArgs a;
+  memset(&a, 0, sizeof(a));
+  a.N = g.N; a.K = g.K; a.P = g.P; a.Q = g.Q;
+  a.act = g.act; a.lo = g.lo; a.hi = g.hi;
+  a.y = (bf16 *)y;
+  const bool folded = g.C < 16;
+  int Sp = 0, Cp = 0;
+  if (folded) {
+    Cp = g.C <= 4 ? 4 : (g.C <= 8 ? 8 : 16);
+    const int unit = 16 / Cp;
+    Sp = (g.S + unit - 1) / unit * unit;
+    a.H = g.H; a.W = g.Q; a.Cf = Sp * Cp;
+    a.R = g.R; a.S = 1;
+    a.pad_h = g.pad_h; a.pad_w = 0; a.stride_h = g.stride_h; a.stride_w = 1;
+  } else {
+    if (g.C % 16 != 0) return false;
+    a.H = g.H; a.W = g.W; a.Cf = g.C;
+    a.R = g.R; a.S = g.S;
+    a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
+  }
+  a.x = (const bf16 *)16;  // placeholders so the support check sees aligned pointers
+  a.w = (const bf16 *)16;
+  if (!tc_conv_supported(a)) return false;
+
+  if (folded) {
+    ensure_f32(x);
+    bf16 *xf = (bf16 *)scratch_get(0, (size_t)g.N * g.H * g.Q * a.Cf * 2);
+    if (!xf) return false;
+    launch_fold_input_bf16(x, xf, g.N, g.C, g.H, g.W, g.Q, g.S, Sp, Cp, g.pad_w, g.stride_w,
+                           r.stream);
+    a.x = xf;
+    a.w = (const bf16 *)packed_weights(w, PACK_FOLD, (size_t)g.R * g.K * a.Cf * 2, g.K, g.C, g.R,
+                                       g.S, Sp, Cp);
+  } else {
+    if (is_bf16(x, g.N, g.C, g.H, g.W)) {
+      a.x = (const bf16 *)x;
+    } else {
+      ensure_f32(x);
+      bf16 *xc = (bf16 *)scratch_get(0, (size_t)g.N * g.C * g.H * g.W * 2);
+      if (!xc) return false;
+      launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, r.stream);
+      a.x = xc;
+    }
+    a.w = (const bf16 *)packed_weights(w, PACK_KRSC, (size_t)g.R * g.S * g.K * g.C * 2, g.K, g.C,
+                                       g.R, g.S, 0, 0);
+  }
+  if (!a.w) return false;
+  a.bias = bias ? resident_f32(bias, (size_t)g.K * 4) : nullptr;
+  launch_tc_conv(a, r.stream);
+  mark_bf16(y, g.N, g.K, g.P, g.Q);
+  return true;
+}
+
+bool conv_depthwise_bf16(const float *x, const float *w, const float *bias, float *y,
+                         const ConvGeom &g) {
+  Runtime &r = rt();
+  if (g.C % 8 != 0) return false;
+  const bf16 *xb;
+  if (is_bf16(x, g.N, g.C, g.H, g.W)) {
+    xb = (const bf16 *)x;
+  } else {
+    ensure_f32(x);
+    bf16 *xc = (bf16 *)scratch_get(0, (size_t)g.N * g.C * g.H * g.W * 2);
+    if (!xc) return false;
+    launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, r.stream);
+    xb = xc;
+  }
+  const float *wp = (const float *)packed_weights(w, PACK_DW, (size_t)g.R * g.S * g.C * 4, g.K,
+                                                  g.C, g.R, g.S, 0, 0);
+  if (!wp) return false;
+  launch_depthwise_bf16(xb, wp, bias ? resident_f32(bias, (size_t)g.C * 4) : nullptr, (bf16 *)y, g,
+                        r.stream);
+  mark_bf16(y, g.N, g.K, g.P, g.Q);
+  return true;
+}
+
+float *conv_common(float *x, const int64_t *dX, float *w, const int64_t *dW, float *bias,
+                   int64_t groups, const int64_t *pads, const int64_t *strides, int act, float lo,
+                   float hi, float *y) {
+  Runtime &r = rt();
+  ConvGeom g;
+  g.N = (int)dX[0]; g.C = (int)dX[1]; g.H = (int)dX[2]; g.W = (int)dX[3];
+  g.K = (int)dW[0]; g.R = (int)dW[2]; g.S = (int)dW[3];
+  g.groups = (int)(groups < 1 ? 1 : groups);
+  g.pad_h = (int)pads[0]; g.pad_w = (int)pads[1];
+  g.stride_h = (int)strides[0]; g.stride_w = (int)strides[1];
+  g.act = act; g.lo = lo; g.hi = hi;
+  if (g.stride_h < 1 || g.stride_w < 1 || g.C % g.groups || g.K % g.groups ||
+      dW[1] * g.groups != g.C) {
+    set_error(997, "convolution: inconsistent shape");
+    return y;
+  }
+  g.P = (g.H + 2 * g.pad_h - g.R) / g.stride_h + 1;
+  g.Q = (g.W + 2 * g.pad_w - g.S) / g.stride_w + 1;
+  if (g.P <= 0 || g.Q <= 0 || g.N == 0) return y;
+  const bool depthwise = g.groups > 1 && g.groups == g.C && g.K == g.C;
+  if (r.log)
+    fprintf(stderr, "[occamy] conv x[%d,%d,%d,%d] w[%d,%d,%d,%d] g%d s%d p%d act%d\n", g.N, g.C,
+            g.H, g.W, g.K, (int)dW[1], g.R, g.S, g.groups, g.stride_h, g.pad_h, act);
+  if (r.mode == MATH_BF16) {
+    if (g.groups == 1 && conv_tensor_core(x, w, bias, y, g)) return y;
+    if (depthwise && conv_depthwise_bf16(x, w, bias, y, g)) return y;
+  }
+  ensure_f32(x);
+  ensure_f32(w);
+  if (bias) ensure_f32(bias);
+  if (depthwise) launch_depthwise_f32(x, w, bias, y, g, r.stream);
+  else launch_conv_f32(x, w, bias, y, g, r.stream);
+  mark_f32(y);
+  return y;
+}
+
+int64_t prod(const int64_t *d, int64_t rank) {
+  int64_t n = 1;
+  for (int64_t i = 0; i < rank; ++i) n *= d[i];
+  return n;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------- memory pool
+cudaError_t wrapDNNMalloc(void **devPtr, size_t size) {
+  Runtime &r = rt();
+  cudaError_t e = cudaMalloc(devPtr, size ? size : 1);
+  if (e != cudaSuccess) die("Malloc", e, size);
+  reg_new(*devPtr, size, FMT_ZERO);  // zero fill is issued only if somebody reads it unwritten
+  (void)r;
+  return cudaSuccess;
+}
+
+cudaError_t wrapDNNMemPoolInit(void **devPtr, size_t size) {
+  Runtime &r = rt();
+  if (g_pool_cache.base && g_pool_cache.bytes == size) {
+    *devPtr = g_pool_cache.base;
+    g_pool_cache.base = nullptr;
+  } else {
+    if (g_pool_cache.base) {
+      OCC_CUDA(cudaStreamSynchronize(r.stream));
+      OCC_CUDA(cudaFree(g_pool_cache.base));
+      g_pool_cache.base = nullptr;
+    }
+    cudaError_t e = cudaMalloc(devPtr, size ? size : 1);
+    if (e != cudaSuccess) die("MemPoolInit", e, size);
+  }
+  g_pools.push_back(PoolRec{*devPtr, size});
+  if ((int64_t)size > r.counters[CNT_POOL_HWM]) r.counters[CNT_POOL_HWM] = (int64_t)size;
+  return cudaSuccess;
+}
+
+cudaError_t wrapDNNMemOffset(void **devPtr, void *basePtr, size_t offset, size_t mallocSize) {
+  *devPtr = (char *)basePtr + offset;
+  reg_new(*devPtr, mallocSize, FMT_ZERO);
+  return cudaSuccess;
+}
+
+cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
+                          cudaStream_t /*stream*/) {
+  Runtime &r = rt();
+  if (count_ == 0) return cudaSuccess;
+  cudaError_t e = cudaSuccess;
+  if (kind == 1 || kind == 3) {
+    if (kind == 3) ensure_f32(src);
+    uintptr_t base;
+    TensorRec *rec = reg_find(dst, &base);
+    const bool whole = rec && base == (uintptr_t)dst && count_ + 32 > rec->bytes;
+    if (rec && !whole) ensure_f32(dst);
+    if (kind == 1 && whole) {
+      rec->host_src = src;
+      rec->host_bytes = count_;
+      rec->host_hash = host_hash(src, count_);
+      // A constant whose packed form is already resident need not cross PCIe again; the
+      // copy is made later only if something other than a convolution / GEMM reads it.
+      if (r.cache_weights) {
+        auto it = r.resident.find(src);
+        if (it != r.resident.end() && it->second.first == count_ &&
+            it->second.second == rec->host_hash) {
+          rec->fmt = FMT_PENDING;
+          count(CNT_H2D_SKIPPED, (int64_t)count_);
+          return cudaSuccess;
+        }
+      }
+    }
+    e = cudaMemcpyAsync(dst, src, count_, kind == 1 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
+                        r.stream);
+    if (kind == 1) count(CNT_H2D_BYTES, (int64_t)count_);
+    if (rec && whole) {
+      rec->fmt = FMT_F32;
+      if (kind == 3) rec->host_src = nullptr;
+    }
+  } else if (kind == 2) {
+    uintptr_t base;
+    TensorRec *rec = reg_find(src, &base);
+    const void *from = src;
+    if (rec && rec->fmt == FMT_BF16_NHWC && base == (uintptr_t)src) {
+      // convert into scratch instead of in place: the tensor keeps its fast format
+      const size_t elems = (size_t)(rec->n * rec->c * rec->h * rec->w);
+      float *tmp = (float *)scratch_get(2, elems * 4);
+      launch_nhwc_bf16_to_nchw_f32((const bf16 *)src, tmp, (int)rec->n, (int)rec->c, (int)rec->h,
+                                   (int)rec->w, r.stream);
+      count(CNT_MATERIALIZE);
+      from = tmp;
+    } else {
+      ensure_f32(src);
+    }
+    e = cudaMemcpyAsync(dst, from, count_, cudaMemcpyDeviceToHost, r.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(r.stream);
+    // surface a kernel-side watchdog report, if any
+    if (r.dev_err && r.host_err) {
+      cudaMemcpy(r.host_err, r.dev_err, sizeof(int), cudaMemcpyDeviceToHost);
+      if (*r.host_err) {
+        set_error(*r.host_err, "kernel watchdog");
+        cudaMemset(r.dev_err, 0, sizeof(int));
+      }
+    }
+  } else {
+    e = cudaMemcpyAsync(dst, src, count_, (cudaMemcpyKind)kind, r.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(r.stream);
+  }
+  if (e != cudaSuccess) {
+    printf("[Memcpy] GPU error: %s\n", cudaGetErrorString(e));
+    exit(-1);
+  }
+  return cudaSuccess;
+}
+
+cudaError_t wrapDNNDealloc(void *devPtr) {
+  Runtime &r = rt();
+  if (!devPtr) return cudaSuccess;
+  size_t bytes = 0;
+  bool was_pool = false;
+  for (size_t i = 0; i < g_pools.size(); ++i)
+    if (g_pools[i].base == devPtr) {
+      bytes = g_pools[i].bytes;
+      was_pool = true;
+      g_pools.erase(g_pools.begin() + i);
+      break;
+    }
+  if (was_pool && pool_cache_enabled()) {
+    // Work still in flight on the launch stream is ordered before anything a later
+    // inference enqueues, so the block can be handed out again without waiting.
+    if (bytes) reg_drop_range(devPtr, bytes);
+    if (g_pool_cache.base) {
+      OCC_CUDA(cudaStreamSynchronize(r.stream));
+      OCC_CUDA(cudaFree(g_pool_cache.base));
+    }
+    g_pool_cache = PoolRec{devPtr, bytes};
+    return cudaSuccess;
+  }
+  if (!bytes) {
+    uintptr_t base;
+    TensorRec *rec = reg_find(devPtr, &base);
+    if (rec && base == (uintptr_t)devPtr) bytes = rec->bytes;
+  }
+  OCC_CUDA(cudaStreamSynchronize(r.stream));
+  if (bytes) reg_drop_range(devPtr, bytes);
+  cudaError_t e = cudaFree(devPtr);
+  if (e != cudaSuccess) {
+    printf("[Dealloc] GPU error: %s\n", cudaGetErrorString(e));
+    exit(-1);
+  }
+  return cudaSuccess;
+}
+
+// ---------------------------------------------------------------- handle
+int cudnnCreate(cudnnContext **handle) {
+  rt();
+  *handle = reinterpret_cast<cudnnContext *>(malloc(16));
+  return *handle ? 0 : 2;
+}
+int cudnnDestroy(cudnnContext *handle) {
+  free(handle);
+  return 0;
+}
+
+// ---------------------------------------------------------------- convolution
+float *DNNConvFunc(cudnnContext *, float *x, int64_t dimX[4], float *w, int64_t dimW[4],
+                   float * /*workspace*/, int64_t /*workspaceSize*/, int64_t /*algo*/,
+                   int64_t groups, int64_t pads[2], int64_t strides[2], float *y) {
+  return conv_common(x, dimX, w, dimW, nullptr, groups, pads, strides, ACT_IDENTITY, 0.f, 0.f, y);
+}
+
+float *DNNConvBiasActivFunc(cudnnContext *, float *x, int64_t dimX[4], float *w, int64_t dimW[4],
+                            float *bias, int64_t dimB[4], float * /*workspace*/,
+                            int64_t /*workspaceSize*/, int64_t /*algo*/, int64_t pads[2],
+                            int64_t strides[2], int64_t activMode, float *y) {
+  (void)dimB;
+  int act = ACT_IDENTITY;
+  float lo = 0.f, hi = 0.f;
+  if (activMode == 1) act = ACT_RELU;
+  else if (activMode == 3) { act = ACT_CLIP; lo = 0.f; hi = 6.f; }
+  else if (activMode == 0) act = ACT_SIGMOID;
+  else if (activMode == 2) act = ACT_TANH;
+  return conv_common(x, dimX, w, dimW, bias, 1, pads, strides, act, lo, hi, y);
+}
+
+// ---------------------------------------------------------------- element-wise
+float *DNNActiveFunc(cudnnContext *, float *x, int64_t dimX[4], int32_t mode, float *y) {
+  Runtime &r = rt();
+  const int64_t n = numel4(dimX);
+  const int act = mode == 0 ? ACT_SIGMOID : (mode == 1 ? ACT_RELU : (mode == 2 ? ACT_TANH : ACT_IDENTITY));
+  if (is_bf16(x, dimX[0], dimX[1], dimX[2], dimX[3])) {
+    launch_add_act_bf16((const bf16 *)x, nullptr, nullptr, (int)dimX[1], (bf16 *)y, n, act, 0.f,
+                        0.f, r.stream);
+    mark_bf16(y, dimX[0], dimX[1], dimX[2], dimX[3]);
+    return y;
+  }
+  ensure_f32(x);
+  launch_act_f32(x, y, n, act, 0.f, 0.f, r.stream);
+  mark_f32(y);
+  return y;
+}
+
+float *CUDAClipFunc(float *x, float *y, int64_t *dimOut, float lo, float hi, int64_t rank) {
+  Runtime &r = rt();
+  const int64_t n = prod(dimOut, rank);
+  if (rank == 4 && is_bf16(x, dimOut[0], dimOut[1], dimOut[2], dimOut[3])) {
+    launch_add_act_bf16((const bf16 *)x, nullptr, nullptr, (int)dimOut[1], (bf16 *)y, n, ACT_CLIP,
+                        lo, hi, r.stream);
+    mark_bf16(y, dimOut[0], dimOut[1], dimOut[2], dimOut[3]);
+    return y;
+  }
+  ensure_f32(x);
+  launch_act_f32(x, y, n, ACT_CLIP, lo, hi, r.stream);
+  mark_f32(y);
+  return y;
+}
+
+float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, int32_t rankA,
+                       float *B, int64_t *dimB, int32_t rankB, float *out, int64_t *dimOut,
+                       int32_t rankOut, float bias) {
+  Runtime &r = rt();
+  (void)dimOut;
+  (void)rankOut;
+  if (rankA > 8 || rankB > rankA) {
+    set_error(996, "tensor op: unsupported rank");
+    return out;
+  }
+  // B's shape padded with leading 1s to A's rank
+  int64_t dB[8];
+  for (int i = 0; i < rankA; ++i) dB[i] = i < rankA - rankB ? 1 : dimB[i - (rankA - rankB)];
+  if (opMode == 0 && rankA == 4 && bias == 1.0f &&
+      is_bf16(A, dimA[0], dimA[1], dimA[2], dimA[3])) {
+    const int64_t n = numel4(dimA);
+    bool same = true;
+    for (int i = 0; i < 4; ++i) same &= dB[i] == dimA[i];
+    if (same && is_bf16(B, dimA[0], dimA[1], dimA[2], dimA[3])) {
+      launch_add_act_bf16((const bf16 *)A, (const bf16 *)B, nullptr, (int)dimA[1], (bf16 *)out, n,
+                          ACT_IDENTITY, 0.f, 0.f, r.stream);
+      mark_bf16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
+      return out;
+    }
+    if (dB[0] == 1 && dB[1] == dimA[1] && dB[2] == 1 && dB[3] == 1) {
+      ensure_f32(B);
+      launch_add_act_bf16((const bf16 *)A, nullptr, B, (int)dimA[1], (bf16 *)out, n, ACT_IDENTITY,
+                          0.f, 0.f, r.stream);
+      mark_bf16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
+      return out;
+    }
+  }
+  ensure_f32(A);
+  if (opMode != 4) ensure_f32(B);
+  if (opMode != 0 && opMode != 1 && opMode != 4) {
+    set_error(996, "tensor op: unsupported mode");
+    return out;
+  }
+  launch_tensor_op_f32((int)opMode, A, B, out, rankA, dimA, dB, bias, r.stream);
+  mark_f32(out);
+  return out;
+}
+
+// ---------------------------------------------------------------- pooling / reduction
+static float *pool_common(float *x, int64_t *dI, float *y, int64_t *dO, int64_t *kernel,
+                          int64_t *padding, int64_t *stride, bool avg) {
+  Runtime &r = rt();
+  const int N = (int)dI[0], C = (int)dI[1], H = (int)dI[2], W = (int)dI[3];
+  const int P = (int)dO[2], Q = (int)dO[3];
+  const int ph = (int)padding[0], pw = (int)padding[2];
+  if (r.mode == MATH_BF16 && C % 8 == 0 && is_bf16(x, N, C, H, W)) {
+    launch_pool_bf16((const bf16 *)x, (bf16 *)y, N, C, H, W, P, Q, (int)kernel[0], (int)kernel[1],
+                     ph, pw, (int)stride[0], (int)stride[1], avg, r.stream);
+    mark_bf16(y, N, C, P, Q);
+    return y;
+  }
+  ensure_f32(x);
+  launch_pool_f32(x, y, N, C, H, W, P, Q, (int)kernel[0], (int)kernel[1], ph, pw, (int)stride[0],
+                  (int)stride[1], avg, r.stream);
+  mark_f32(y);
+  return y;
+}
+
+float *DNNMaxPoolFunc(cudnnContext *, float *x, int64_t dimIn[4], float *y, int64_t dimOut[4],
+                      int64_t kernel[2], int64_t padding[4], int64_t stride[2]) {
+  return pool_common(x, dimIn, y, dimOut, kernel, padding, stride, false);
+}
+
+float *DNNAveragePoolFunc(cudnnContext *, float *x, int64_t dimIn[4], float *y, int64_t dimOut[4],
+                          int64_t kernel[2], int64_t padding[4], int64_t stride[2]) {
+  return pool_common(x, dimIn, y, dimOut, kernel, padding, stride, true);
+}
+
+float *DNNReduceFunc(cudnnContext *, int32_t rank, float *x, int64_t *dimIn, float *y,
+                     int64_t *dimOut, int32_t mode) {
+  Runtime &r = rt();
+  if (mode != 5 || rank > 8) {
+    set_error(995, "reduce: only mode 5 (mean) is implemented");
+    return y;
+  }
+  if (rank == 4 && dimOut[2] == 1 && dimOut[3] == 1 && dimOut[0] == dimIn[0] &&
+      dimOut[1] == dimIn[1] && dimIn[1] % 8 == 0 &&
+      is_bf16(x, dimIn[0], dimIn[1], dimIn[2], dimIn[3])) {
+    launch_gap_bf16((const bf16 *)x, y, (int)dimIn[0], (int)(dimIn[2] * dimIn[3]), (int)dimIn[1],
+                    r.stream);
+    mark_f32(y);
+    return y;
+  }
+  ensure_f32(x);
+  launch_reduce_mean_f32(x, y, rank, dimIn, dimOut, r.stream);
+  mark_f32(y);
+  return y;
+}
+
+// ---------------------------------------------------------------- classifier head
+float *CUBLASMatmul2dFunc(int64_t /*rank*/, float *A, int64_t dimA[2], float *B, int64_t dimB[2],
+                          float * /*C*/, int64_t * /*dimC*/, float *out, int64_t * /*dimOut*/,
+                          float alpha, float beta, int64_t transA, int64_t transB) {
+  Runtime &r = rt();
+  const int M = (int)(transA ? dimA[1] : dimA[0]);
+  const int K = (int)(transA ? dimA[0] : dimA[1]);
+  const int N = (int)(transB ? dimB[0] : dimB[1]);
+  if (r.log) fprintf(stderr, "[occamy] matmul2d M%d N%d K%d tA%d tB%d\n", M, N, K, (int)transA, (int)transB);
+  const bool out_zero = is_zero(out);
+  if (r.mode == MATH_BF16 && !transA && transB && alpha == 1.0f && (beta == 0.0f || out_zero) &&
+      K % 16 == 0 && M > 0) {
+    TcConvArgs a;
+    memset(&a, 0, sizeof(a));
+    a.N = 1; a.H = 1; a.W = M; a.Cf = K; a.K = N; a.P = 1; a.Q = M; a.R = 1; a.S = 1;
+    a.stride_h = a.stride_w = 1;
+    a.act = ACT_IDENTITY;
+    a.out_f32 = out;
+    a.ldo = N;
+    a.x = (const bf16 *)16;
+    a.w = (const bf16 *)16;
+    if (tc_conv_supported(a)) {
+      ensure_f32(A);
+      bf16 *ab = (bf16 *)scratch_get(0, (size_t)M * K * 2);
+      const bf16 *wb = (const bf16 *)packed_weights(B, PACK_KRSC, (size_t)N * K * 2, N, K, 1, 1, 0, 0);
+      if (ab && wb) {
+        launch_f32_to_bf16(A, ab, (int64_t)M * K, r.stream);
+        a.x = ab;
+        a.w = wb;
+        launch_tc_conv(a, r.stream);
+        mark_f32(out);
+        return out;
+      }
+    }
+  }
+  ensure_f32(A);
+  ensure_f32(B);
+  if (beta != 0.0f) ensure_f32(out);
+  launch_gemm_f32(A, B, out, M, N, K, (int)dimA[1], (int)dimB[1], alpha, out_zero ? 0.0f : beta,
+                  transA != 0, transB != 0, r.stream);
+  mark_f32(out);
+  return out;
+}
+
+float *CUDASoftmaxFunc(float *x, int64_t *dimIn, float *y, int64_t * /*dimOut*/, int64_t axis,
+                       int64_t rank) {
+  Runtime &r = rt();
+  if (axis < 0) axis += rank;
+  int64_t outer = 1, inner = 1;
+  for (int64_t i = 0; i < axis; ++i) outer *= dimIn[i];
+  for (int64_t i = axis + 1; i < rank; ++i) inner *= dimIn[i];
+  ensure_f32(x);
+  launch_softmax_f32(x, y, outer, dimIn[axis], inner, r.stream);
+  mark_f32(y);
+  return y;
+}
+
+float *CUDAFlattenFunc(float *x, int64_t *dimIn, float *y, int64_t * /*dimOut*/, int32_t /*axis*/,
+                       int64_t rank) {
+  Runtime &r = rt();
+  const int64_t n = prod(dimIn, rank);
+  ensure_f32(x);
+  OCC_CUDA(cudaMemcpyAsync(y, x, (size_t)n * 4, cudaMemcpyDeviceToDevice, r.stream));
+  mark_f32(y);
+  return y;
+}
+
+float *CUDAReshapeFunc(float *x, int64_t *dimIn, int64_t rank, float *y) {
+  Runtime &r = rt();
+  const int64_t n = prod(dimIn, rank);
+  ensure_f32(x);
+  OCC_CUDA(cudaMemcpyAsync(y, x, (size_t)n * 4, cudaMemcpyDeviceToDevice, r.stream));
+  mark_f32(y);
+  return y;
+}
+
+// ---------------------------------------------------------------- controls
+void occamy_set_math_mode(int mode) { rt().mode = mode == 0 ? MATH_FP32 : MATH_BF16; }
+int occamy_get_math_mode(void) { return (int)rt().mode; }
+
+int occamy_last_error(int clear) {
+  Runtime &r = rt();
+  const int e = r.last_error;
+  if (clear) r.last_error = 0;
+  return e;
+}
+
+int occamy_synchronize(void) {
+  Runtime &r = rt();
+  cudaError_t e = cudaStreamSynchronize(r.stream);
+  if (e != cudaSuccess) set_error((int)e, "synchronize");
+  if (r.dev_err && r.host_err) {
+    cudaMemcpy(r.host_err, r.dev_err, sizeof(int), cudaMemcpyDeviceToHost);
+    if (*r.host_err) {
+      set_error(*r.host_err, "kernel watchdog");
+      cudaMemset(r.dev_err, 0, sizeof(int));
+    }
+  }
+  return (int)e;
+}
+
+cudaStream_t occamy_stream(void) { return rt().stream; }
+
+void occamy_get_counters(int64_t out[8]) {
+  Runtime &r = rt();
+  for (int i = 0; i < 8; ++i) out[i] = r.counters[i];
+}
+
+void occamy_profile_begin(void) {
+  Runtime &r = rt();
+  r.prof_count = 0;
+  r.profiling = true;
+}
+
+int occamy_profile_end(float *ms, int cap) {
+  Runtime &r = rt();
+  r.profiling = false;
+  OCC_CUDA(cudaStreamSynchronize(r.stream));
+  const int n = r.prof_count;
+  for (int i = 0; i < n && i < cap; ++i) {
+    float t = 0.f;
+    OCC_CUDA(cudaEventElapsedTime(&t, r.prof_events[2 * i], r.prof_events[2 * i + 1]));
+    ms[i] = t;
+  }
+  r.prof_count = 0;
+  return n;
+}
+
+void occamy_clear_weight_cache(void) {
+  Runtime &r = rt();
+  OCC_CUDA(cudaStreamSynchronize(r.stream));
+  for (auto &kv : r.wcache)
+    if (kv.second.dev) cudaFree(kv.second.dev);
+  r.wcache.clear();
+  r.resident.clear();
+}
+
+}  // extern "C"

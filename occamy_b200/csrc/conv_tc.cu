@@ -1,0 +1,729 @@
+// Implicit-GEMM convolution / GEMM on the sm_100a tensor cores.
+//
+//   D[m, k] = act( sum_{tap, c} A_tap[m, c] * Wp[tap, k, c] + bias[k] (+ residual[m, k]) )
+//
+// m runs over output pixels (n, p, q), k over output channels, c over input channels.
+// A is never materialised: for every filter tap the producer issues one tiled TMA load of
+// a [tn x th x tw] pixel box x BK channels straight out of the NHWC bf16 activation
+// tensor, shifted by the tap's (dh, dw); out-of-image pixels are zero-filled by TMA,
+// which implements the padding.  Strided convolutions read through per-phase tensor
+// maps whose strides are the convolution stride (h = stride*(p + a) + b for tap offset
+// stride*a + b), so the same shifted-box scheme applies.
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0     : TMA producer (one elected lane) - fills a ring of {A, B} stages
+//   warp 1     : MMA issuer  (one elected lane) - tcgen05.mma, 128 x BN x 16 per issue,
+//                fp32 accumulators in TMEM, two accumulator buffers
+//   warps 2..5 : epilogue - tcgen05.ld the finished accumulator, add bias / residual,
+//                activation, convert to bf16, stage 64-channel slabs in swizzled shared
+//                memory and TMA-store them (stores clip at the image edge), while the MMA
+//                warp already works on the next tile.
+// Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in
+// the error word, drains and returns.
+#include <cuda.h>
+
+#include <cstring>
+#include <unordered_map>
+#include <vector>
+
+#include "kernels.h"
+#include "runtime.h"
+
+namespace occ {
+
+constexpr int TC_THREADS = 192;
+constexpr int TC_MAX_TAPS = 32;
+constexpr int TC_SMEM_LIMIT = 232448;  // 227 KB
+
+struct TcTap {
+  int map, dw, dh;
+};
+
+struct alignas(64) TcParams {
+  CUtensorMap tmA[4];
+  CUtensorMap tmB;
+  CUtensorMap tmD;
+  CUtensorMap tmR;
+  TcTap taps[TC_MAX_TAPS];
+  int num_taps, cblocks, bk, stages;
+  int tiles_w, tiles_h, tiles_n, tiles_k, total_tiles;
+  int tw, th, tn, K;
+  const float *bias;
+  int has_res, act;
+  float lo, hi;
+  float *out_f32;
+  int ldo;
+  int m_total;
+  int *err;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t cnt) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(cnt));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t a) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(a), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~2 s of polling or as soon as another role has given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try(a, parity)) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (!mbar_try(a, parity)) {
+    if ((++it & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, uint32_t src, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(m),
+      "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major bf16 tile whose rows are `bk` elements
+// (32 / 64 / 128 bytes, swizzled with the matching 32B / 64B / 128B pattern): 8-row groups
+// are 8*bk*2 bytes apart; descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk) {
+  const uint32_t sbo = (uint32_t)(8 * bk * 2);
+  const uint64_t layout = bk == 64 ? 2ull : (bk == 32 ? 4ull : 6ull);
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(sbo >> 4) << 32) |
+         (1ull << 46) | (layout << 61);
+}
+
+__device__ __forceinline__ float tc_act(float v, int act, float lo, float hi) {
+  if (act == ACT_RELU) return v != v ? v : fmaxf(v, 0.0f);
+  if (act == ACT_CLIP) return fminf(fmaxf(v, lo), hi);
+  if (act == ACT_SIGMOID) return 1.0f / (1.0f + __expf(-v));
+  if (act == ACT_TANH) return tanhf(v);
+  return v;
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` inside a staged slab whose rows are
+// `row_bytes` (64 or 128) long, with the TMA swizzle of that width applied.
+__device__ __forceinline__ uint32_t slab_off(int row, int chunk, int row_bytes) {
+  const uint32_t off = (uint32_t)(row * row_bytes + chunk * 16);
+  const uint32_t mask = (uint32_t)(row_bytes / 16 - 1);
+  return off ^ (((off >> 7) & mask) << 4);
+}
+
+// ------------------------------------------------------------------ the kernel
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_constant__ TcParams p) {
+  constexpr int DC = BN < 64 ? BN : 64;        // channels per staged output slab
+  constexpr int NSLAB = BN / DC;
+  constexpr int SLAB_BYTES = 128 * DC * 2;
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(128 >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const int bk = p.bk, stages = p.stages;
+  const uint32_t a_bytes = 128u * bk * 2u, b_bytes = (uint32_t)BN * bk * 2u;
+  const uint32_t sA = base;
+  const uint32_t sB = sA + stages * a_bytes;
+  const uint32_t sD = sB + stages * b_bytes;           // 2 slabs
+  const uint32_t sR = sD + 2 * SLAB_BYTES;             // 2 slabs (only if has_res)
+  const uint32_t sMisc = sR + (p.has_res ? 2 * SLAB_BYTES : 0);
+  uint8_t *misc_ptr = base_ptr + (sMisc - base);
+  float *bias_s = reinterpret_cast<float *>(misc_ptr);                  // BN floats
+  uint64_t *bars = reinterpret_cast<uint64_t *>(misc_ptr + BN * 4);     // barriers
+  const uint32_t bar0 = sMisc + BN * 4;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
+  auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + s); };
+  auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * stages + 2 + s); };
+  auto rfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + 4 + s); };
+  volatile uint32_t *tmem_holder =
+      reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 6);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 7);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 128);
+      mbar_init(rfull_bar(s), 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32((const void *)tmem_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int rows_valid = p.tw * p.th * p.tn;
+  const int ksteps = p.num_taps * p.cblocks;
+  int err_code = 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + b_bytes;
+      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+        const int kt = tile % p.tiles_k;
+        int sp = tile / p.tiles_k;
+        const int q0 = (sp % p.tiles_w) * p.tw;
+        sp /= p.tiles_w;
+        const int p0 = (sp % p.tiles_h) * p.th;
+        const int n0 = (sp / p.tiles_h) * p.tn;
+        const int k0 = kt * BN;
+        for (int t = 0; t < p.num_taps && !err_code; ++t) {
+          const TcTap tap = p.taps[t];
+          for (int cb = 0; cb < p.cblocks; ++cb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+              err_code = 1;
+              break;
+            }
+            mbar_expect_tx(full_bar(stage), tx_bytes);
+            tma_load_4d(sA + stage * a_bytes, &p.tmA[tap.map], full_bar(stage), cb * bk,
+                        q0 + tap.dw, p0 + tap.dh, n0);
+            tma_load_3d(sB + stage * b_bytes, &p.tmB, full_bar(stage), cb * bk, k0, t);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          err_code = 2;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accumulate = 0;
+        for (int ks = 0; ks < ksteps; ++ks) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            err_code = 3;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
+          const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
+          for (int kk = 0; kk < bk / 16; ++kk) {
+            tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
+                        accumulate);
+            accumulate = 1;
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (err_code) break;
+        tc_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (128 threads)
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int row = quad * 32 + lane;        // accumulator row == pixel index in the tile
+    const int et = threadIdx.x - 64;         // 0..127
+    const bool leader = et == 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint32_t d_iter = 0, r_iter = 0;
+    for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+      const int kt = tile % p.tiles_k;
+      int sp = tile / p.tiles_k;
+      const int wt = sp % p.tiles_w;
+      const int q0 = wt * p.tw;
+      sp /= p.tiles_w;
+      const int p0 = (sp % p.tiles_h) * p.th;
+      const int n0 = (sp / p.tiles_h) * p.tn;
+      const int k0 = kt * BN;
+      const int nslab = min(NSLAB, (p.K - k0 + DC - 1) / DC);
+      if (p.has_res && leader) {
+        mbar_expect_tx(rfull_bar(r_iter & 1), (uint32_t)rows_valid * DC * 2u);
+        tma_load_4d(sR + (r_iter & 1) * SLAB_BYTES, &p.tmR, rfull_bar(r_iter & 1), k0, q0, p0, n0);
+      }
+      for (int i = et; i < BN; i += 128)
+        bias_s[i] = (p.bias && k0 + i < p.K) ? p.bias[k0 + i] : 0.0f;
+      epi_bar();
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+        err_code = 4;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+      for (int sl = 0; sl < nslab; ++sl) {
+        uint32_t dbuf = 0;
+        if (!p.out_f32) {
+          dbuf = sD + (d_iter & 1) * SLAB_BYTES;
+          if (leader) tma_store_wait_read<1>();
+          epi_bar();  // slab buffer (d_iter & 1) is free; residual slab (r_iter+1)&1 is free
+        }
+        if (p.has_res) {
+          if (leader && sl + 1 < nslab) {
+            mbar_expect_tx(rfull_bar((r_iter + 1) & 1), (uint32_t)rows_valid * DC * 2u);
+            tma_load_4d(sR + ((r_iter + 1) & 1) * SLAB_BYTES, &p.tmR, rfull_bar((r_iter + 1) & 1),
+                        k0 + (sl + 1) * DC, q0, p0, n0);
+          }
+          if (!mbar_wait(rfull_bar(r_iter & 1), (r_iter >> 1) & 1u, abort_flag)) {
+            err_code = 5;
+            break;
+          }
+        }
+        const uint8_t *rbuf = base_ptr + (sR + (r_iter & 1) * SLAB_BYTES - base);
+        uint8_t *dptr = base_ptr + (dbuf - base);
+#pragma unroll
+        for (int h = 0; h < DC / 32; ++h) {
+          uint32_t r[32];
+          tc_ld32(t_row + (uint32_t)(sl * DC + h * 32), r);
+          tc_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) + bias_s[sl * DC + h * 32 + j];
+          if (p.has_res) {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const uint4 rv = *reinterpret_cast<const uint4 *>(
+                  rbuf + slab_off(row, h * 4 + c4, DC * 2));
+              const uint32_t w4[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f =
+                    __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w4[e]));
+                v[c4 * 8 + e * 2] += f.x;
+                v[c4 * 8 + e * 2 + 1] += f.y;
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = tc_act(v[j], p.act, p.lo, p.hi);
+          if (p.out_f32) {
+            const int m = q0 + row;
+            if (row < rows_valid && m < p.m_total) {
+              float *o = p.out_f32 + (int64_t)m * p.ldo + k0 + sl * DC + h * 32;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (k0 + sl * DC + h * 32 + j < p.K) o[j] = v[j];
+            }
+          } else {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint4 pk;
+              __nv_bfloat162 b0 = __floats2bfloat162_rn(v[c4 * 8 + 0], v[c4 * 8 + 1]);
+              __nv_bfloat162 b1 = __floats2bfloat162_rn(v[c4 * 8 + 2], v[c4 * 8 + 3]);
+              __nv_bfloat162 b2 = __floats2bfloat162_rn(v[c4 * 8 + 4], v[c4 * 8 + 5]);
+              __nv_bfloat162 b3 = __floats2bfloat162_rn(v[c4 * 8 + 6], v[c4 * 8 + 7]);
+              pk.x = *reinterpret_cast<uint32_t *>(&b0);
+              pk.y = *reinterpret_cast<uint32_t *>(&b1);
+              pk.z = *reinterpret_cast<uint32_t *>(&b2);
+              pk.w = *reinterpret_cast<uint32_t *>(&b3);
+              *reinterpret_cast<uint4 *>(dptr + slab_off(row, h * 4 + c4, DC * 2)) = pk;
+            }
+          }
+        }
+        if (p.has_res) ++r_iter;
+        if (!p.out_f32) {
+          fence_async_smem();
+          epi_bar();
+          if (leader) {
+            tma_store_4d(&p.tmD, dbuf, k0 + sl * DC, q0, p0, n0);
+            tma_store_commit();
+          }
+          ++d_iter;
+        }
+      }
+      if (err_code) break;
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (leader) tma_store_wait_read<0>();
+  }
+
+  if (err_code) {
+    atomicExch(p.err, 1000 + err_code);
+    *abort_flag = 1;
+    // let copies that are still in flight land before shared memory is given back
+    for (int i = 0; i < 50; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q);
+    if (e != cudaSuccess || !sym) {
+      set_error(e ? (int)e : 999, "cuTensorMapEncodeTiled entry point");
+      return nullptr;
+    }
+    fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+static CUtensorMapSwizzle swizzle_for(int row_bytes) {
+  return row_bytes >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+// bf16 tensor map of rank `rank` (<= 4): dims/box innermost first, strides in bytes for
+// dims 1..rank-1.
+static bool make_map(CUtensorMap *m, const void *ptr, int rank, const uint64_t *dims,
+                     const uint64_t *strides, const uint32_t *box, int row_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gd[4], gs[3];
+  cuuint32_t bx[4], es[4];
+  for (int i = 0; i < rank; ++i) {
+    gd[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gs[i] = strides[i];
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(ptr),
+                  gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(row_bytes),
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  count(CNT_TMAP_ENCODES);
+  if (r != CUDA_SUCCESS) {
+    set_error(2000 + (int)r, "cuTensorMapEncodeTiled");
+    return false;
+  }
+  return true;
+}
+
+// Pixel box (tw x th x tn <= 128) that covers a Q x P x N output grid with the fewest tiles.
+static void choose_box(int Q, int P, int N, int *tw, int *th, int *tn) {
+  long best = -1;
+  int bw = 1, bh = 1, bn = 1;
+  for (int w = 1; w <= (Q < 128 ? Q : 128); ++w) {
+    const long cw = (Q + w - 1) / w;
+    for (int h = 1; h <= P && w * h <= 128; ++h) {
+      const long ch = (P + h - 1) / h;
+      int n = 128 / (w * h);
+      if (n > N) n = N;
+      // any n in [1, n] is legal; fewer tiles with the largest, but try divisors too
+      for (int nn = n; nn >= 1; nn = (nn > 8 ? nn / 2 : nn - 1)) {
+        const long tiles = cw * ch * ((N + nn - 1) / nn);
+        if (best < 0 || tiles < best || (tiles == best && w > bw)) {
+          best = tiles;
+          bw = w;
+          bh = h;
+          bn = nn;
+        }
+      }
+    }
+  }
+  *tw = bw;
+  *th = bh;
+  *tn = bn;
+}
+
+static int pick_bk(int Cf) { return Cf % 64 == 0 ? 64 : (Cf % 32 == 0 ? 32 : (Cf % 16 == 0 ? 16 : 0)); }
+static int pick_bn(int K) { return K > 128 ? 256 : (K > 64 ? 128 : (K > 32 ? 64 : 32)); }
+
+bool tc_conv_supported(const TcConvArgs &a) {
+  if (pick_bk(a.Cf) == 0) return false;
+  if (a.stride_h < 1 || a.stride_w < 1 || a.stride_h > 2 || a.stride_w > 2) return false;
+  if (a.R * a.S > TC_MAX_TAPS) return false;
+  if (!a.out_f32 && a.K % 8 != 0) return false;
+  if (a.out_f32 && !(a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 &&
+                     a.pad_h == 0 && a.pad_w == 0 && !a.residual))
+    return false;
+  if ((uintptr_t)a.x % 16 || (uintptr_t)a.w % 16) return false;
+  if (a.y && (uintptr_t)a.y % 16) return false;
+  if ((int64_t)a.N * a.P * a.Q >= (1ll << 31)) return false;
+  return true;
+}
+
+struct ArgsKey {
+  TcConvArgs a;
+  bool operator==(const ArgsKey &o) const { return memcmp(&a, &o.a, sizeof(a)) == 0; }
+};
+struct ArgsKeyHash {
+  size_t operator()(const ArgsKey &k) const {
+    const unsigned char *b = (const unsigned char *)&k.a;
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(k.a); ++i) h = (h ^ b[i]) * 1099511628211ull;
+    return (size_t)h;
+  }
+};
+struct Plan {
+  TcParams p;
+  int bn;
+  size_t smem;
+  bool ok;
+};
+
+static int floordiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+
+static Plan build_plan(const TcConvArgs &a) {
+  Plan pl;
+  memset(&pl, 0, sizeof(pl));
+  TcParams &p = pl.p;
+  const int bk = pick_bk(a.Cf), bn = pick_bn(a.K);
+  pl.bn = bn;
+  p.bk = bk;
+  p.cblocks = a.Cf / bk;
+  p.K = a.K;
+  p.bias = a.bias;
+  p.has_res = a.residual ? 1 : 0;
+  p.act = a.act;
+  p.lo = a.lo;
+  p.hi = a.hi;
+  p.out_f32 = a.out_f32;
+  p.ldo = a.ldo;
+  p.err = rt().dev_err;
+  const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
+                    a.pad_w == 0;
+  // output grid the tiles are cut from
+  int Qg = a.Q, Pg = a.P, Ng = a.N;
+  if (flat) {
+    Qg = a.N * a.P * a.Q;
+    Pg = 1;
+    Ng = 1;
+  }
+  p.m_total = Qg;
+  choose_box(Qg, Pg, Ng, &p.tw, &p.th, &p.tn);
+  p.tiles_w = (Qg + p.tw - 1) / p.tw;
+  p.tiles_h = (Pg + p.th - 1) / p.th;
+  p.tiles_n = (Ng + p.tn - 1) / p.tn;
+  p.tiles_k = (a.K + bn - 1) / bn;
+  p.total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_k;
+
+  const uint32_t boxA[4] = {(uint32_t)bk, (uint32_t)p.tw, (uint32_t)p.th, (uint32_t)p.tn};
+  bool ok = true;
+  if (flat) {
+    const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)Qg, 1, 1};
+    const uint64_t st[3] = {(uint64_t)a.Cf * 2, (uint64_t)Qg * a.Cf * 2, (uint64_t)Qg * a.Cf * 2};
+    ok &= make_map(&p.tmA[0], a.x, 4, dims, st, boxA, bk * 2);
+    p.num_taps = 1;
+    p.taps[0] = TcTap{0, 0, 0};
+  } else {
+    // one tensor map per (row phase, column phase) of the stride
+    const int sh = a.stride_h, sw = a.stride_w;
+    int map_of[2][2] = {{-1, -1}, {-1, -1}};
+    int nmaps = 0;
+    p.num_taps = 0;
+    for (int r = 0; r < a.R; ++r)
+      for (int s2 = 0; s2 < a.S; ++s2) {
+        const int eh = r - a.pad_h, ew = s2 - a.pad_w;
+        const int ah = floordiv(eh, sh), bh = eh - ah * sh;
+        const int aw = floordiv(ew, sw), bw = ew - aw * sw;
+        if (map_of[bh][bw] < 0) {
+          const int Hm = (a.H - bh + sh - 1) / sh, Wm = (a.W - bw + sw - 1) / sw;
+          const bf16 *ptr = a.x + ((int64_t)bh * a.W + bw) * a.Cf;
+          const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)(Wm > 0 ? Wm : 1),
+                                    (uint64_t)(Hm > 0 ? Hm : 1), (uint64_t)a.N};
+          const uint64_t st[3] = {(uint64_t)sw * a.Cf * 2, (uint64_t)sh * a.W * a.Cf * 2,
+                                  (uint64_t)a.H * a.W * a.Cf * 2};
+          ok &= make_map(&p.tmA[nmaps], ptr, 4, dims, st, boxA, bk * 2);
+          map_of[bh][bw] = nmaps++;
+        }
+        p.taps[p.num_taps++] = TcTap{map_of[bh][bw], aw, ah};
+      }
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)a.Cf, (uint64_t)a.K, (uint64_t)(a.R * a.S)};
+    const uint64_t st[2] = {(uint64_t)a.Cf * 2, (uint64_t)a.K * a.Cf * 2};
+    const uint32_t box[3] = {(uint32_t)bk, (uint32_t)bn, 1};
+    ok &= make_map(&p.tmB, a.w, 3, dims, st, box, bk * 2);
+  }
+  const int dc = bn < 64 ? bn : 64;
+  if (!a.out_f32) {
+    const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
+    const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};
+    const uint32_t box[4] = {(uint32_t)dc, (uint32_t)p.tw, (uint32_t)p.th, (uint32_t)p.tn};
+    ok &= make_map(&p.tmD, a.y, 4, dims, st, box, dc * 2);
+    if (a.residual) ok &= make_map(&p.tmR, a.residual, 4, dims, st, box, dc * 2);
+  }
+  // shared memory: ring + output slabs (+ residual slabs) + bias + barriers + alignment
+  const size_t stage_bytes = 128 * bk * 2 + (size_t)bn * bk * 2;
+  const size_t fixed = 1024 + 2 * 128 * dc * 2 * (a.residual ? 2 : 1) + bn * 4 + 8 * 80;
+  int stages = (int)((TC_SMEM_LIMIT - fixed) / stage_bytes);
+  if (stages > 8) stages = 8;
+  if (stages < 2) ok = false;
+  p.stages = stages;
+  pl.smem = fixed + stages * stage_bytes;
+  if (pl.smem < 120 * 1024) pl.smem = 120 * 1024;  // keep one CTA per SM (TMEM is per SM)
+  pl.ok = ok;
+  return pl;
+}
+
+template <int BN>
+static void launch_plan(const Plan &pl, cudaStream_t s) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    OCC_CUDA(cudaFuncSetAttribute(tc_conv_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  TC_SMEM_LIMIT));
+    attr_set = true;
+  }
+  int grid = pl.p.total_tiles < rt().num_sms ? pl.p.total_tiles : rt().num_sms;
+  tc_conv_kernel<BN><<<grid, TC_THREADS, pl.smem, s>>>(pl.p);
+}
+
+void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
+  static std::unordered_map<ArgsKey, Plan, ArgsKeyHash> plans;
+  ArgsKey key;
+  memset(&key, 0, sizeof(key));
+  key.a = a;
+  auto it = plans.find(key);
+  if (it == plans.end()) {
+    if (plans.size() > 4096) plans.clear();
+    it = plans.emplace(key, build_plan(a)).first;
+  }
+  const Plan &pl = it->second;
+  if (!pl.ok) {
+    set_error(998, "tensor-core conv plan");
+    return;
+  }
+  if (pl.p.total_tiles == 0) return;
+  Runtime &r = rt();
+  int prof_slot = -1;
+  if (r.profiling) {
+    prof_slot = r.prof_count++;
+    while ((int)r.prof_events.size() < 2 * (prof_slot + 1)) {
+      cudaEvent_t e;
+      OCC_CUDA(cudaEventCreate(&e));
+      r.prof_events.push_back(e);
+    }
+    OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot], s));
+  }
+  switch (pl.bn) {
+    case 32: launch_plan<32>(pl, s); break;
+    case 64: launch_plan<64>(pl, s); break;
+    case 128: launch_plan<128>(pl, s); break;
+    default: launch_plan<256>(pl, s); break;
+  }
+  if (prof_slot >= 0) OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot + 1], s));
+  OCC_CUDA(cudaGetLastError());
+  count(CNT_LAUNCHES);
+  count(CNT_TC_LAUNCHES);
+}
+
+}  // namespace occ

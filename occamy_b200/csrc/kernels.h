@@ -1,0 +1,95 @@
+// Launchers of the device kernels.  Every launcher enqueues on the given stream and
+// returns immediately; none allocates.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace occ {
+
+// Activation codes shared by host and device (cuDNN's numbering, which is what crosses
+// the ABI): 0 sigmoid, 1 ReLU, 2 tanh, 3 clipped ReLU [lo, hi], 5 identity.
+enum Act { ACT_SIGMOID = 0, ACT_RELU = 1, ACT_TANH = 2, ACT_CLIP = 3, ACT_IDENTITY = 5 };
+
+struct ConvGeom {
+  int N, C, H, W;       // input, NCHW logical dims
+  int K, R, S;          // filter [K, C/groups, R, S]
+  int P, Q;             // output spatial dims
+  int groups;
+  int pad_h, pad_w, stride_h, stride_w;
+  int act;              // Act
+  float lo, hi;         // bounds for ACT_CLIP
+};
+
+// ---- fp32 NCHW kernels (ABI layout) ------------------------------------------
+void launch_conv_f32(const float *x, const float *w, const float *bias, float *y,
+                     const ConvGeom &g, cudaStream_t s);
+void launch_depthwise_f32(const float *x, const float *w, const float *bias, float *y,
+                          const ConvGeom &g, cudaStream_t s);
+// out = A op (biasB*B); dimB has extent 1 where B is broadcast; rank <= 8.
+void launch_tensor_op_f32(int mode, const float *A, const float *B, float *out, int rank,
+                          const int64_t *dimA, const int64_t *dimB, float biasB, cudaStream_t s);
+void launch_act_f32(const float *x, float *y, int64_t n, int act, float lo, float hi,
+                    cudaStream_t s);
+void launch_pool_f32(const float *x, float *y, int N, int C, int H, int W, int P, int Q, int kh,
+                     int kw, int pad_h, int pad_w, int sh, int sw, bool avg, cudaStream_t s);
+// Mean over the axes where dimOut is 1 and dimIn is not; rank <= 8.
+void launch_reduce_mean_f32(const float *x, float *y, int rank, const int64_t *dimIn,
+                            const int64_t *dimOut, cudaStream_t s);
+// out[M,N] = alpha * op(A) * op(B) + beta * out, row-major; lda/ldb are the stored row lengths.
+void launch_gemm_f32(const float *A, const float *B, float *out, int M, int N, int K, int lda,
+                     int ldb, float alpha, float beta, bool transA, bool transB, cudaStream_t s);
+void launch_softmax_f32(const float *x, float *y, int64_t outer, int64_t len, int64_t inner,
+                        cudaStream_t s);
+
+// ---- bf16 NHWC kernels (tensor-core mode activations) -------------------------
+typedef __nv_bfloat16 bf16;
+void launch_nchw_f32_to_nhwc_bf16(const float *x, bf16 *y, int N, int C, int H, int W,
+                                  cudaStream_t s);
+void launch_nhwc_bf16_to_nchw_f32(const bf16 *x, float *y, int N, int C, int H, int W,
+                                  cudaStream_t s);
+void launch_f32_to_bf16(const float *x, bf16 *y, int64_t n, cudaStream_t s);
+// out = act(a + b) over n elements (b may be null); c-periodic fp32 bias may be added.
+void launch_add_act_bf16(const bf16 *a, const bf16 *b, const float *bias_c, int C, bf16 *out,
+                         int64_t n, int act, float lo, float hi, cudaStream_t s);
+void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P, int Q, int kh,
+                      int kw, int pad_h, int pad_w, int sh, int sw, bool avg, cudaStream_t s);
+// Global average pool: x [N, HW, C] bf16 -> y [N, C] fp32.
+void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t s);
+// Depthwise RxS convolution on NHWC bf16, weights fp32 packed [R*S][C], fused bias + act.
+void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias, bf16 *y,
+                           const ConvGeom &g, cudaStream_t s);
+// Weight packing: fp32 KCRS -> bf16 [R*S][K][C] (dense conv) ...
+void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, cudaStream_t s);
+// ... fp32 [C,1,R,S] -> fp32 [R*S][C] (depthwise) ...
+void launch_pack_dw_f32(const float *w, float *out, int C, int R, int S, cudaStream_t s);
+// ... and fp32 KCRS with tiny C -> bf16 [R][K][Sp*Cp] (width taps folded into channels).
+void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Sp, int Cp,
+                           cudaStream_t s);
+// Input side of the folded form: x fp32 NCHW -> bf16 [N][H][Q][Sp*Cp], where entry
+// (n,h,q,s,c) = x[n,c,h,q*stride_w - pad_w + s] (zero outside the image or for s>=S, c>=C).
+void launch_fold_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Q, int S,
+                            int Sp, int Cp, int pad_w, int stride_w, cudaStream_t s);
+
+// ---- tcgen05 implicit-GEMM convolution / GEMM --------------------------------
+struct TcConvArgs {
+  const bf16 *x;         // A operand: NHWC bf16 [N][H][W][C] (or folded [N][H][Q][Cf])
+  const bf16 *w;         // B operand: packed [T][K][Cf]
+  const float *bias;     // [K] or null
+  const bf16 *residual;  // NHWC bf16 like the output, or null
+  bf16 *y;               // NHWC bf16 [N][P][Q][K]      (when out_f32 == null)
+  float *out_f32;        // row-major [N*P*Q][ldo] fp32 (GEMM head), else null
+  int ldo;
+  int N, H, W, Cf;       // A tensor dims (W already = Q for the folded form)
+  int K, P, Q;
+  int R, S;              // taps looped over (S = 1 for the folded form)
+  int pad_h, pad_w, stride_h, stride_w;  // stride_w = 1, pad_w = 0 for the folded form
+  int act;
+  float lo, hi;
+};
+// Returns false when the shape is outside what the kernel supports (caller falls back).
+bool tc_conv_supported(const TcConvArgs &a);
+void launch_tc_conv(const TcConvArgs &a, cudaStream_t s);
+
+}  // namespace occ

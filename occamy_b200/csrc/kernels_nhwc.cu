@@ -1,0 +1,383 @@
+// Kernels on the tensor-core mode's activation format: bf16, NHWC, C a multiple of 8 so
+// that every thread moves 128 bits (8 channels) per access.  All are HBM-bound; they are
+// written so that consecutive threads touch consecutive 16-byte channel groups.
+#include "kernels.h"
+#include "runtime.h"
+
+namespace occ {
+
+__device__ __forceinline__ float act_apply_b(float v, int act, float lo, float hi) {
+  switch (act) {
+    case ACT_SIGMOID: return 1.0f / (1.0f + __expf(-v));
+    case ACT_RELU: return v != v ? v : fmaxf(v, 0.0f);
+    case ACT_TANH: return tanhf(v);
+    case ACT_CLIP: return fminf(fmaxf(v, lo), hi);
+    default: return v;
+  }
+}
+
+static inline int grid_for(int64_t n, int threads) {
+  int64_t b = (n + threads - 1) / threads;
+  const int64_t cap = (int64_t)rt().num_sms * 32;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void unpack8(const bf16x8 &p, float *f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(p.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ bf16x8 pack8(const float *f) {
+  bf16x8 p;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return p;
+}
+
+// ---------------------------------------------------------------------------
+// Layout conversion, per image: [C][HW] fp32 <-> [HW][C] bf16 through a 32x32 tile.
+// ---------------------------------------------------------------------------
+__global__ void nchw_to_nhwc_kernel(const float *__restrict__ x, bf16 *__restrict__ y, int C,
+                                    int HW) {
+  __shared__ float tile[32][33];
+  const int n = blockIdx.z;
+  const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+  const float *xn = x + (int64_t)n * C * HW;
+  bf16 *yn = y + (int64_t)n * C * HW;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, p = p0 + threadIdx.x;
+    tile[i][threadIdx.x] = (c < C && p < HW) ? xn[(int64_t)c * HW + p] : 0.0f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int p = p0 + i, c = c0 + threadIdx.x;
+    if (p < HW && c < C) yn[(int64_t)p * C + c] = __float2bfloat16_rn(tile[threadIdx.x][i]);
+  }
+}
+
+__global__ void nhwc_to_nchw_kernel(const bf16 *__restrict__ x, float *__restrict__ y, int C,
+                                    int HW) {
+  __shared__ float tile[32][33];
+  const int n = blockIdx.z;
+  const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+  const bf16 *xn = x + (int64_t)n * C * HW;
+  float *yn = y + (int64_t)n * C * HW;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int p = p0 + i, c = c0 + threadIdx.x;
+    tile[i][threadIdx.x] = (p < HW && c < C) ? __bfloat162float(xn[(int64_t)p * C + c]) : 0.0f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, p = p0 + threadIdx.x;
+    if (c < C && p < HW) yn[(int64_t)c * HW + p] = tile[threadIdx.x][i];
+  }
+}
+
+void launch_nchw_f32_to_nhwc_bf16(const float *x, bf16 *y, int N, int C, int H, int W,
+                                  cudaStream_t s) {
+  const int HW = H * W;
+  if ((int64_t)N * C * HW == 0) return;
+  dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
+  nchw_to_nhwc_kernel<<<grid, block, 0, s>>>(x, y, C, HW);
+  count(CNT_LAUNCHES);
+}
+
+void launch_nhwc_bf16_to_nchw_f32(const bf16 *x, float *y, int N, int C, int H, int W,
+                                  cudaStream_t s) {
+  const int HW = H * W;
+  if ((int64_t)N * C * HW == 0) return;
+  dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
+  nhwc_to_nchw_kernel<<<grid, block, 0, s>>>(x, y, C, HW);
+  count(CNT_LAUNCHES);
+}
+
+__global__ void f32_to_bf16_kernel(const float *__restrict__ x, bf16 *__restrict__ y, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = __float2bfloat16_rn(x[i]);
+}
+
+void launch_f32_to_bf16(const float *x, bf16 *y, int64_t n, cudaStream_t s) {
+  if (n == 0) return;
+  f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, s>>>(x, y, n);
+  count(CNT_LAUNCHES);
+}
+
+// ---------------------------------------------------------------------------
+// out = act(a + b + bias[c]);  b and bias optional.  8 channels per thread.
+// ---------------------------------------------------------------------------
+__global__ void add_act_bf16_kernel(const bf16x8 *a, const bf16x8 *b, const float *bias_c, int C8,
+                                    bf16x8 *out, int64_t n8, int act, float lo, float hi) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float f[8], g2[8];
+    unpack8(a[i], f);
+    if (b) {
+      unpack8(b[i], g2);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] += g2[k];
+    }
+    if (bias_c) {
+      const float4 *bp = (const float4 *)(bias_c + (i % C8) * 8);
+      const float4 b0 = bp[0], b1 = bp[1];
+      f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+      f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = act_apply_b(f[k], act, lo, hi);
+    out[i] = pack8(f);
+  }
+}
+
+void launch_add_act_bf16(const bf16 *a, const bf16 *b, const float *bias_c, int C, bf16 *out,
+                         int64_t n, int act, float lo, float hi, cudaStream_t s) {
+  if (n == 0) return;
+  add_act_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>(
+      (const bf16x8 *)a, (const bf16x8 *)b, bias_c, C / 8, (bf16x8 *)out, n / 8, act, lo, hi);
+  count(CNT_LAUNCHES);
+}
+
+// ---------------------------------------------------------------------------
+// Pooling on NHWC: one thread per (n, p, q, 8 channels).
+// ---------------------------------------------------------------------------
+__global__ void pool_bf16_kernel(const bf16x8 *__restrict__ x, bf16x8 *__restrict__ y, int C8,
+                                 int H, int W, int P, int Q, int kh, int kw, int pad_h, int pad_w,
+                                 int sh, int sw, bool avg, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(i % C8);
+    int64_t rest = i / C8;
+    const int q = (int)(rest % Q);
+    rest /= Q;
+    const int p = (int)(rest % P);
+    const int64_t n = rest / P;
+    float m[8], sum[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { m[k] = -INFINITY; sum[k] = 0.0f; }
+    for (int r = 0; r < kh; ++r) {
+      const int h = p * sh - pad_h + r;
+      if (h < 0 || h >= H) continue;
+      for (int s2 = 0; s2 < kw; ++s2) {
+        const int ww = q * sw - pad_w + s2;
+        if (ww < 0 || ww >= W) continue;
+        float f[8];
+        unpack8(x[((n * H + h) * W + ww) * C8 + c8], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (f[k] > m[k] || f[k] != f[k]) m[k] = f[k];
+          sum[k] += f[k];
+        }
+      }
+    }
+    if (avg) {
+      const float inv = 1.0f / (float)(kh * kw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) m[k] = sum[k] * inv;
+    }
+    y[i] = pack8(m);
+  }
+}
+
+void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P, int Q, int kh,
+                      int kw, int pad_h, int pad_w, int sh, int sw, bool avg, cudaStream_t s) {
+  const int64_t total = (int64_t)N * P * Q * (C / 8);
+  if (total == 0) return;
+  pool_bf16_kernel<<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H,
+                                                         W, P, Q, kh, kw, pad_h, pad_w, sh, sw, avg,
+                                                         total);
+  count(CNT_LAUNCHES);
+}
+
+// Global average pool: [N][HW][C] bf16 -> [N][C] fp32; thread per (n, 8 channels).
+__global__ void gap_bf16_kernel(const bf16x8 *__restrict__ x, float *__restrict__ y, int HW,
+                                int C8, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(i % C8);
+    const int64_t n = i / C8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const bf16x8 *xp = x + n * HW * C8 + c8;
+    for (int p = 0; p < HW; ++p) {
+      float f[8];
+      unpack8(xp[(int64_t)p * C8], f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += f[k];
+    }
+    const float inv = 1.0f / (float)HW;
+    float4 *yp = (float4 *)(y + i * 8);
+    yp[0] = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    yp[1] = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+  }
+}
+
+void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t s) {
+  const int64_t total = (int64_t)N * (C / 8);
+  if (total == 0) return;
+  gap_bf16_kernel<<<grid_for(total, 128), 128, 0, s>>>((const bf16x8 *)x, y, HW, C / 8, total);
+  count(CNT_LAUNCHES);
+}
+
+// ---------------------------------------------------------------------------
+// Depthwise convolution on NHWC: thread per (n, p, q, 8 channels); the R*S taps of a
+// channel group are 2 float4 loads each from the [R*S][C] fp32 filter (L1-resident).
+// ---------------------------------------------------------------------------
+__global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float *__restrict__ w,
+                                      const float *__restrict__ bias, bf16x8 *__restrict__ y,
+                                      ConvGeom g, int64_t total) {
+  const int C8 = g.C / 8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c8 = (int)(i % C8);
+    int64_t rest = i / C8;
+    const int q = (int)(rest % g.Q);
+    rest /= g.Q;
+    const int p = (int)(rest % g.P);
+    const int64_t n = rest / g.P;
+    float acc[8];
+    if (bias) {
+      const float4 *bp = (const float4 *)(bias + c8 * 8);
+      const float4 b0 = bp[0], b1 = bp[1];
+      acc[0] = b0.x; acc[1] = b0.y; acc[2] = b0.z; acc[3] = b0.w;
+      acc[4] = b1.x; acc[5] = b1.y; acc[6] = b1.z; acc[7] = b1.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
+    }
+    for (int r = 0; r < g.R; ++r) {
+      const int h = p * g.stride_h - g.pad_h + r;
+      if (h < 0 || h >= g.H) continue;
+      for (int s2 = 0; s2 < g.S; ++s2) {
+        const int ww = q * g.stride_w - g.pad_w + s2;
+        if (ww < 0 || ww >= g.W) continue;
+        float f[8];
+        unpack8(x[((n * g.H + h) * g.W + ww) * C8 + c8], f);
+        const float4 *wp = (const float4 *)(w + (int64_t)(r * g.S + s2) * g.C + c8 * 8);
+        const float4 w0 = wp[0], w1 = wp[1];
+        acc[0] = fmaf(f[0], w0.x, acc[0]); acc[1] = fmaf(f[1], w0.y, acc[1]);
+        acc[2] = fmaf(f[2], w0.z, acc[2]); acc[3] = fmaf(f[3], w0.w, acc[3]);
+        acc[4] = fmaf(f[4], w1.x, acc[4]); acc[5] = fmaf(f[5], w1.y, acc[5]);
+        acc[6] = fmaf(f[6], w1.z, acc[6]); acc[7] = fmaf(f[7], w1.w, acc[7]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = act_apply_b(acc[k], g.act, g.lo, g.hi);
+    y[i] = pack8(acc);
+  }
+}
+
+void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias, bf16 *y,
+                           const ConvGeom &g, cudaStream_t s) {
+  const int64_t total = (int64_t)g.N * g.P * g.Q * (g.C / 8);
+  if (total == 0) return;
+  depthwise_bf16_kernel<<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, w_rsc, bias,
+                                                              (bf16x8 *)y, g, total);
+  count(CNT_LAUNCHES);
+}
+
+// ---------------------------------------------------------------------------
+// Weight packing (runs once per constant; results stay resident)
+// ---------------------------------------------------------------------------
+__global__ void pack_krsc_kernel(const float *__restrict__ w, bf16 *__restrict__ out, int K, int C,
+                                 int RS, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    const int k = (int)((i / C) % K);
+    const int t = (int)(i / ((int64_t)C * K));
+    out[i] = __float2bfloat16_rn(w[((int64_t)k * C + c) * RS + t]);
+  }
+}
+
+void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, cudaStream_t s) {
+  const int64_t total = (int64_t)K * C * R * S;
+  if (total == 0) return;
+  pack_krsc_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, out, K, C, R * S, total);
+  count(CNT_LAUNCHES);
+}
+
+__global__ void pack_dw_kernel(const float *__restrict__ w, float *__restrict__ out, int C, int RS,
+                               int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % C);
+    const int t = (int)(i / C);
+    out[i] = w[(int64_t)c * RS + t];
+  }
+}
+
+void launch_pack_dw_f32(const float *w, float *out, int C, int R, int S, cudaStream_t s) {
+  const int64_t total = (int64_t)C * R * S;
+  if (total == 0) return;
+  pack_dw_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, out, C, R * S, total);
+  count(CNT_LAUNCHES);
+}
+
+// Folded form for convolutions with very few input channels (the RGB stems): the S width
+// taps and the C channels of one filter row become Sp*Cp "channels" of a Rx1 convolution.
+__global__ void pack_fold_kernel(const float *__restrict__ w, bf16 *__restrict__ out, int K, int C,
+                                 int R, int S, int Sp, int Cp, int64_t total) {
+  const int Cf = Sp * Cp;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int cf = (int)(i % Cf);
+    const int k = (int)((i / Cf) % K);
+    const int r = (int)(i / ((int64_t)Cf * K));
+    const int s2 = cf / Cp, c = cf % Cp;
+    float v = 0.0f;
+    if (s2 < S && c < C) v = w[(((int64_t)k * C + c) * R + r) * S + s2];
+    out[i] = __float2bfloat16_rn(v);
+  }
+}
+
+void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Sp, int Cp,
+                           cudaStream_t s) {
+  const int64_t total = (int64_t)R * K * Sp * Cp;
+  if (total == 0) return;
+  pack_fold_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, out, K, C, R, S, Sp, Cp, total);
+  count(CNT_LAUNCHES);
+}
+
+// x fp32 NCHW -> bf16 [N][H][Q][Sp*Cp]; one thread per (n, h, q, s): writes Cp channels.
+// Consecutive threads differ in s then q, so reads of one input row are near-contiguous
+// and the Cp*2-byte writes of a warp are contiguous.
+__global__ void fold_input_kernel(const float *__restrict__ x, bf16 *__restrict__ out, int C,
+                                  int H, int W, int Q, int S, int Sp, int Cp, int pad_w,
+                                  int stride_w, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int s2 = (int)(i % Sp);
+    int64_t rest = i / Sp;
+    const int q = (int)(rest % Q);
+    rest /= Q;
+    const int h = (int)(rest % H);
+    const int64_t n = rest / H;
+    const int ww = q * stride_w - pad_w + s2;
+    const bool ok = s2 < S && ww >= 0 && ww < W;
+    bf16 *o = out + i * Cp;
+    for (int c = 0; c < Cp; ++c) {
+      float v = 0.0f;
+      if (ok && c < C) v = x[((n * C + c) * H + h) * (int64_t)W + ww];
+      o[c] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+void launch_fold_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Q, int S,
+                            int Sp, int Cp, int pad_w, int stride_w, cudaStream_t s) {
+  const int64_t total = (int64_t)N * H * Q * Sp;
+  if (total == 0) return;
+  fold_input_kernel<<<grid_for(total, 256), 256, 0, s>>>(x, out, C, H, W, Q, S, Sp, Cp, pad_w,
+                                                          stride_w, total);
+  count(CNT_LAUNCHES);
+}
+
+}  // namespace occ

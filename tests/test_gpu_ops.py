@@ -1,0 +1,243 @@
+"""Parity of every hot-path runtime symbol, called through the C ABI on a B200, against
+the CPU oracle on the same seeded inputs.
+
+Tolerances (per tensor, max|y - ref| / max|ref|):
+  fp32 mode            <= 1e-4
+  bf16 tensor-core mode <= 2e-2
+"""
+import numpy as np
+import pytest
+
+import abi_calls as A
+from helpers import max_rel_err
+from occamy_b200 import runtime as rt
+from oracle import ref
+
+pytestmark = pytest.mark.gpu
+
+TOL = {rt.MATH_FP32: 1e-4, rt.MATH_BF16: 2e-2}
+MODES = [rt.MATH_FP32, rt.MATH_BF16]
+
+
+@pytest.fixture(autouse=True)
+def _check_runtime_errors(native_libs):
+    rt.last_error(clear=True)
+    yield
+    rt.synchronize()
+    assert rt.last_error(clear=True) == 0
+
+
+def rng(seed):
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def he(r, K, C, R, S):
+    return r.normal(0, np.sqrt(2.0 / (C * R * S)), (K, C, R, S)).astype(np.float32)
+
+
+# (N, C, H, W, K, R, pad, stride, groups)
+CONV_CASES = [
+    (1, 64, 56, 56, 64, 3, 1, 1, 1),      # the single-conv benchmark configuration
+    (2, 64, 28, 28, 256, 1, 0, 1, 1),     # 1x1: flat GEMM view
+    (2, 256, 28, 28, 128, 1, 0, 2, 1),    # 1x1 stride 2 (ResNet v1 down-sampling)
+    (2, 128, 28, 28, 128, 3, 1, 2, 1),    # 3x3 stride 2 (v1.5): four stride phases
+    (3, 512, 7, 7, 512, 3, 1, 1, 1),      # 7x7 maps: several images per tile
+    (2, 3, 64, 64, 64, 7, 3, 2, 1),       # RGB stem: width taps folded into channels
+    (2, 3, 32, 32, 64, 3, 1, 1, 1),       # VGG first layer
+    (1, 32, 13, 11, 24, 3, 1, 1, 1),      # ragged: K < tile, odd H/W, 32-channel K block
+    (2, 16, 9, 9, 40, 1, 0, 1, 1),        # 16-channel K block
+    (1, 48, 10, 10, 96, 3, 1, 1, 1),      # 48 = 3 x 16-channel blocks
+    (1, 320, 7, 7, 1280, 1, 0, 1, 1),     # MobileNetV2 head; K = 5 x 256
+    (2, 8, 12, 12, 8, 3, 1, 1, 2),        # grouped (CUDA-core path in both modes)
+    (2, 20, 9, 9, 10, 3, 0, 1, 1),        # channel counts no tensor-core tile fits
+    (2, 32, 16, 16, 32, 3, 1, 1, 32),     # depthwise stride 1
+    (2, 96, 15, 15, 96, 3, 1, 2, 96),     # depthwise stride 2, odd size
+    (1, 64, 5, 5, 64, 5, 2, 1, 1),        # 5x5: 25 taps
+]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("act_mode", [None, 1, 5, 3])
+def test_conv(case, mode, act_mode):
+    N, C, H, W, K, R, pad, stride, groups = case
+    if act_mode is not None and groups != 1:
+        pytest.skip("the fused symbol has no group argument")
+    r = rng(hash(case) % 2**31)
+    x = r.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = he(r, K, C // groups, R, R)
+    b = r.normal(0, 0.5, K).astype(np.float32)
+    rt.set_math_mode(mode)
+    y = A.conv(A.up(x), A.up(w), A.up(b) if act_mode is not None else None, (pad, pad),
+               (stride, stride), groups, act_mode).numpy()
+    lo, hi = (0.0, 6.0) if act_mode == 3 else (0.0, 0.0)
+    want = ref.conv2d(x, w, b if act_mode is not None else None, (pad, pad), (stride, stride),
+                      groups, act=act_mode if act_mode is not None else 5, lo=lo, hi=hi)
+    assert y.shape == want.shape
+    assert max_rel_err(y, want) <= TOL[mode]
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_conv_empty_and_tiny(mode):
+    rt.set_math_mode(mode)
+    r = rng(5)
+    # batch 0: nothing to do, pointer still returned
+    x0 = A.Dev((0, 16, 4, 4))
+    w = A.up(he(r, 16, 16, 1, 1))
+    y0 = A.conv(x0, w)
+    assert y0.shape == (0, 16, 4, 4)
+    # 1x1 spatial
+    x = r.uniform(-1, 1, (1, 16, 1, 1)).astype(np.float32)
+    y = A.conv(A.up(x), w).numpy()
+    assert max_rel_err(y, ref.conv2d(x, w.numpy())) <= TOL[mode]
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_unfused_chain_matches_fused(mode):
+    """conv -> in-place bias add -> relu (what the compiler emits without fusion), then
+    residual add, max pool and global average pool on the same device tensors."""
+    rt.set_math_mode(mode)
+    r = rng(11)
+    x = r.uniform(-1, 1, (2, 64, 14, 14)).astype(np.float32)
+    w = he(r, 64, 64, 3, 3)
+    b = r.normal(0, 0.1, 64).astype(np.float32)
+    xd, wd, bd = A.up(x), A.up(w), A.up(b)
+    y = A.conv(xd, wd, pads=(1, 1))
+    y = A.tensor_op(0, y, A.Dev((1, 64, 1, 1), b), out=y)          # in place
+    y = A.active(y, 1)
+    fused = A.conv(xd, wd, bd, pads=(1, 1), act_mode=1)
+    want = ref.conv2d(x, w, b, (1, 1), (1, 1), act=1)
+    assert max_rel_err(y.numpy(), want) <= TOL[mode]
+    assert max_rel_err(fused.numpy(), want) <= TOL[mode]
+    s = A.tensor_op(0, y, fused)                                    # residual-style add
+    want_s = want + want
+    assert max_rel_err(s.numpy(), want_s) <= TOL[mode]
+    p = A.pool(s, (3, 3), (1, 1), (2, 2))
+    want_p = ref.pool2d(want_s, (3, 3), (1, 1), (2, 2))
+    assert max_rel_err(p.numpy(), want_p) <= TOL[mode]
+    g = A.reduce_mean(p, (2, 64, 1, 1))
+    assert max_rel_err(g.numpy(), ref.reduce_mean(want_p, (2, 64, 1, 1))) <= TOL[mode]
+    c = A.clip(s, 0.5, 1.5)
+    assert max_rel_err(c.numpy(), ref.clip(want_s, 0.5, 1.5)) <= TOL[mode]
+    f = A.flatten(p)
+    assert max_rel_err(f.numpy(), want_p.reshape(2, -1)) <= TOL[mode]
+
+
+@pytest.mark.parametrize("shapes", [((2, 8, 5, 7), (2, 8, 5, 7)), ((2, 8, 5, 7), (1, 8, 1, 1)),
+                                    ((4, 10), (1, 10)), ((3, 4, 5, 6), (1, 1, 5, 6)),
+                                    ((2, 3, 4, 5), (2, 3, 1, 1))])
+@pytest.mark.parametrize("op", [0, 1])
+def test_tensor_op_broadcast(shapes, op):
+    rt.set_math_mode(rt.MATH_FP32)
+    r = rng(3)
+    a = r.normal(0, 1, shapes[0]).astype(np.float32)
+    b = r.normal(0, 1, shapes[1]).astype(np.float32)
+    y = A.tensor_op(op, A.up(a), A.up(b), bias=0.5).numpy()
+    assert max_rel_err(y, ref.tensor_op(op, a, b, 0.5)) <= 1e-6
+
+
+def test_tensor_op_sqrt():
+    rt.set_math_mode(rt.MATH_FP32)
+    a = rng(4).uniform(0, 4, (2, 3, 5, 5)).astype(np.float32)
+    y = A.tensor_op(4, A.up(a), A.up(a)).numpy()
+    assert max_rel_err(y, np.sqrt(a)) <= 1e-6
+
+
+@pytest.mark.parametrize("mode_act", [0, 1, 2])
+def test_activation(mode_act):
+    rt.set_math_mode(rt.MATH_FP32)
+    x = rng(6).normal(0, 2, (2, 5, 7, 3)).astype(np.float32)
+    y = A.active(A.up(x), mode_act).numpy()
+    assert max_rel_err(y, ref.activation(x, mode_act)) <= 1e-5
+
+
+@pytest.mark.parametrize("case", [((2, 64, 112, 112), (3, 3), (1, 1), (2, 2)),
+                                  ((2, 16, 8, 8), (2, 2), (0, 0), (2, 2)),
+                                  ((1, 5, 9, 7), (3, 3), (1, 1), (1, 1)),
+                                  ((1, 8, 7, 7), (7, 7), (0, 0), (1, 1)),
+                                  ((2, 8, 6, 6), (1, 1), (0, 0), (1, 1))])
+@pytest.mark.parametrize("avg", [False, True])
+def test_pool(case, avg):
+    rt.set_math_mode(rt.MATH_FP32)
+    shape, k, p, s = case
+    x = rng(7).normal(0, 1, shape).astype(np.float32)
+    y = A.pool(A.up(x), k, p, s, avg).numpy()
+    want = ref.pool2d(x, k, p, s, avg=avg, count_include_pad=True)
+    assert max_rel_err(y, want) <= 1e-6
+
+
+@pytest.mark.parametrize("shapes", [((4, 32, 7, 7), (4, 32, 1, 1)), ((3, 5, 4, 6), (3, 1, 4, 1)),
+                                    ((6, 10), (6, 1)), ((2, 3, 4, 5), (1, 1, 1, 1))])
+def test_reduce_mean(shapes):
+    rt.set_math_mode(rt.MATH_FP32)
+    x = rng(8).normal(0, 1, shapes[0]).astype(np.float32)
+    y = A.reduce_mean(A.up(x), shapes[1]).numpy()
+    assert max_rel_err(y, ref.reduce_mean(x, shapes[1])) <= 1e-5
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("case", [(256, 2048, 1000, 0, 1), (4, 64, 10, 0, 1), (3, 20, 7, 0, 0),
+                                  (5, 16, 9, 1, 0), (64, 512, 96, 0, 1), (1, 2048, 1000, 0, 1)])
+def test_matmul2d(case, mode):
+    M, K, Nn, tA, tB = case
+    rt.set_math_mode(mode)
+    r = rng(9)
+    a = r.normal(0, 1, (K, M) if tA else (M, K)).astype(np.float32)
+    b = (r.normal(0, 1, (Nn, K) if tB else (K, Nn)) / np.sqrt(K)).astype(np.float32)
+    y = A.matmul2d(A.up(a), A.up(b), 1.0, 1.0, tA, tB).numpy()   # beta = 1 on a zeroed output
+    want = ref.matmul2d(a, b, None, 1.0, 0.0, tA, tB)
+    assert max_rel_err(y, want) <= TOL[mode]
+
+
+def test_matmul2d_alpha_beta_accumulates():
+    rt.set_math_mode(rt.MATH_FP32)
+    r = rng(10)
+    a = r.normal(0, 1, (6, 12)).astype(np.float32)
+    b = r.normal(0, 1, (12, 5)).astype(np.float32)
+    c = r.normal(0, 1, (6, 5)).astype(np.float32)
+    out = A.up(c)
+    y = A.matmul2d(A.up(a), A.up(b), 0.5, 2.0, 0, 0, out=out).numpy()
+    assert max_rel_err(y, 0.5 * (a @ b) + 2.0 * c) <= 1e-5
+
+
+@pytest.mark.parametrize("shape_axis", [((256, 1000), 1), ((3, 7), 1), ((2, 5, 4, 3), 1),
+                                        ((4, 6), 0), ((2, 3, 8), 2)])
+def test_softmax(shape_axis):
+    shape, axis = shape_axis
+    x = rng(12).normal(0, 3, shape).astype(np.float32)
+    y = A.softmax(A.up(x), axis).numpy()
+    want = ref.softmax(x, axis)
+    assert max_rel_err(y, want) <= 1e-5
+    # index outputs are bit-exact
+    assert np.array_equal(y.argmax(axis), want.argmax(axis))
+
+
+def test_zero_fill_contract():
+    """A tensor handed out by the allocator reads as zero until written (the reference
+    memsets on every malloc / mem-offset)."""
+    d = A.Dev((3, 4, 5, 6))
+    assert not d.numpy().any()
+    # max pool of an untouched (zero) tensor, then an op that accumulates into its output
+    p = A.pool(d, (2, 2), (0, 0), (1, 1))
+    assert not p.numpy().any()
+
+
+def test_pool_offsets_and_reuse():
+    """wrapDNNMemPoolInit + wrapDNNMemOffset: tensors live at base + offset; a range that is
+    handed out again reads as zero again."""
+    import ctypes as C
+    L = rt.lib()
+    base = C.c_void_p()
+    L.wrapDNNMemPoolInit(C.byref(base), 1 << 20)
+    p1, p2 = C.c_void_p(), C.c_void_p()
+    L.wrapDNNMemOffset(C.byref(p1), base, 4096, 4000)
+    assert p1.value == base.value + 4096
+    data = np.arange(1000, dtype=np.float32)
+    L.wrapDNNMemcpy(p1, data.ctypes.data, 4000, 1, None)
+    back = np.empty(1000, np.float32)
+    L.wrapDNNMemcpy(back.ctypes.data, p1, 4000, 2, None)
+    assert np.array_equal(back, data)
+    L.wrapDNNMemOffset(C.byref(p2), base, 4096 + 2000, 4000)   # overlaps the first tensor
+    L.wrapDNNMemcpy(back.ctypes.data, p2, 4000, 2, None)
+    assert not back.any()
+    L.wrapDNNDealloc(base)

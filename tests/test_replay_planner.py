@@ -1,0 +1,138 @@
+"""Host logic of the compiled-model stand-in (no GPU): lowering patterns, fusion, dealloc
+placement and the first-fit pool planner, the latter against an independent Python
+restatement on the same allocation traces."""
+import numpy as np
+import pytest
+
+from occamy_b200 import graphs, replay
+
+
+def first_fit_reference(trace):
+    """trace: list of ('a', id, size) / ('f', id).  Plain first fit over a sorted free list
+    with coalescing; returns ({id: offset}, high-water mark)."""
+    free = [[0, 1 << 62]]
+    live, offsets, hwm = {}, {}, 0
+    for ev in trace:
+        if ev[0] == "a":
+            _, i, size = ev
+            for blk in free:
+                if blk[1] - blk[0] >= size:
+                    offsets[i] = blk[0]
+                    live[i] = (blk[0], size)
+                    blk[0] += size
+                    break
+            hwm = max(hwm, free[-1][0])
+        else:
+            off, size = live.pop(ev[1])
+            if size == 0:
+                continue
+            free.append([off, off + size])
+            free.sort()
+            merged = [free[0]]
+            for blk in free[1:]:
+                if blk[0] == merged[-1][1]:
+                    merged[-1][1] = blk[1]
+                else:
+                    merged.append(blk)
+            free = merged
+    return offsets, hwm
+
+
+def build_chain(sizes, fuse):
+    """A chain of 1x1 convolutions with the given channel counts on a 1-pixel image: gives
+    an allocation trace with weights, workspaces and activations of many sizes."""
+    g = graphs.Graph((1, sizes[0], 1, 1), seed=0)
+    x = 0
+    for cin, cout in zip(sizes[:-1], sizes[1:]):
+        w, b = g.he_conv(cout, cin, 1, 1)
+        x = g.relu(g.conv(x, w, b))
+    g.mark_output(x)
+    p = g.to_program()
+    p.lower(fuse=fuse)
+    return p
+
+
+@pytest.mark.parametrize("fuse", [0, 1])
+def test_planner_matches_first_fit_reference(fuse, native_libs):
+    rng = np.random.default_rng(0)
+    sizes = [int(v) for v in rng.integers(1, 200, 14)]
+    p = build_chain(sizes, fuse)
+    plan = p.plan()
+    # rebuild the trace the planner saw: every malloc, frees in liveness order are internal,
+    # so check the invariants instead plus the high-water mark against a replay of the plan
+    assert all(off % 32 == 0 and size % 32 == 0 for off, size in plan)
+    assert p.pool_bytes >= max(off + size for off, size in plan)
+    assert p.pool_bytes <= p.sum_bytes
+
+
+def test_first_fit_trace_equivalence(native_libs):
+    """Drive the native planner through graphs whose alloc/free order is known exactly."""
+    # conv chain without fusion: per layer  [w][ws][y] conv, [b] add, then [y2] relu;
+    # frees right after last use.  Reconstruct that trace and compare offsets.
+    sizes = [8, 24, 40, 16, 72, 8]
+    p = build_chain(sizes, fuse=0)
+    plan = p.plan()
+    r32 = lambda n: 0 if n <= 0 else ((n - 1) // 32 + 1) * 32
+    trace, ids = [], iter(range(10**6))
+    x_id = next(ids)
+    trace.append(("a", x_id, r32(sizes[0] * 4)))
+    cur = x_id
+    for cin, cout in zip(sizes[:-1], sizes[1:]):
+        w, ws, y, b, y2 = (next(ids) for _ in range(5))
+        trace += [("a", w, r32(cin * cout * 4)), ("a", ws, 0), ("a", y, r32(cout * 4))]
+        # after the conv call: x (if dead), w and ws die
+        trace += [("f", cur), ("f", w), ("f", ws)]
+        trace += [("a", b, r32(cout * 4)), ("f", b)]
+        trace += [("a", y2, r32(cout * 4)), ("f", y)]
+        cur = y2
+    offsets, hwm = first_fit_reference(trace)
+    got = [off for off, _ in plan]
+    want = [offsets[i] for i in sorted(offsets)]
+    assert got == want
+    assert p.pool_bytes == hwm
+
+
+def test_resnet50_lowering_counts(native_libs):
+    g = graphs.resnet50(batch=1, seed=0)
+    p = g.to_program()
+    p.lower(fuse=replay.FUSE_NONE)
+    c = p.instr_counts()
+    # 53 convolutions each followed by an in-place bias add; 16 residual adds; Gemm bias add
+    assert c["conv"] == 53 and c["conv_bias_act"] == 0
+    assert c["tensor_op"] == 53 + 16 + 1
+    assert c["active"] == 49 and c["maxpool"] == 1 and c["reduce"] == 1
+    assert c["matmul"] == 1 and c["softmax"] == 1 and c["flatten"] == 1
+    assert c["h2d_const"] == 108 and c["malloc"] == c["dealloc"]
+    unfused_pool = p.pool_bytes
+    p.lower(fuse=replay.FUSE_REFERENCE)
+    c = p.instr_counts()
+    assert c["conv_bias_act"] == 53 and c["conv"] == 0
+    assert c["tensor_op"] == 17 and c["active"] == 16
+    # liveness-planned pool is far below the sum of all tensors (the paper's point)
+    assert p.pool_bytes < 0.2 * p.sum_bytes
+    assert abs(p.pool_bytes - unfused_pool) < 0.2 * unfused_pool
+
+
+def test_pool_grows_with_batch_and_vgg_peak(native_libs):
+    p1 = graphs.resnet50(batch=1).to_program()
+    p1.lower()
+    g = graphs.resnet50(batch=4)
+    p4 = g.to_program()
+    p4.lower()
+    assert p4.pool_bytes > 2 * p1.pool_bytes
+    v = graphs.vgg16(batch=1, image=64, num_classes=10).to_program()
+    v.lower()
+    live_peak = 2 * 64 * 64 * 64 * 4       # two [1,64,64,64] activations live at once
+    assert v.pool_bytes >= live_peak
+
+
+def test_mobilenet_fusion_variants(native_libs):
+    g = graphs.mobilenet_v2(batch=1, image=64)
+    p = g.to_program()
+    p.lower(fuse=replay.FUSE_REFERENCE)
+    c = p.instr_counts()
+    assert c["conv"] == 17               # depthwise convolutions keep the grouped symbol
+    assert c["conv_bias_act"] == 35 and c["clip"] == 35
+    p.lower(fuse=replay.FUSE_WITH_CLIP)
+    c = p.instr_counts()
+    assert c["clip"] == 17               # only the depthwise ones keep a separate clip
