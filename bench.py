@@ -333,7 +333,12 @@ def write_per_layer(path, g, tc_ms, peaks, ms_step):
             if n.attrs["groups"] != 1:
                 continue
             flops = 2 * N * K * P * Q * Cg * R * S
-            xin = int(np.prod(g.shapes[n.ins[0]]))
+            _, _, H, W = g.shapes[n.ins[0]]
+            st = n.attrs["strides"]
+            # input pixels the convolution actually touches (a strided 1x1 skips most)
+            hh = min(H, P * R if R < st[0] else (P - 1) * st[0] + R)
+            ww = min(W, Q * S if S < st[1] else (Q - 1) * st[1] + S)
+            xin = N * Cg * hh * ww
             byts = 2 * xin + 2 * K * Cg * R * S + 4 * K + 2 * N * K * P * Q
             name = f"conv {Cg}->{K} {R}x{S} s{n.attrs['strides'][0]} out {P}x{Q}"
         else:

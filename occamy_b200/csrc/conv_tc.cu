@@ -22,6 +22,7 @@
 // the error word, drains and returns.
 #include <cuda.h>
 
+#include <cmath>
 #include <cstring>
 #include <unordered_map>
 #include <vector>
@@ -55,6 +56,8 @@ struct alignas(64) TcParams {
   int ldo;
   int m_total;
   int *err;
+  int dbg;
+  long long *dbg_out;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -179,12 +182,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk) {
          (1ull << 46) | (layout << 61);
 }
 
-__device__ __forceinline__ float tc_act(float v, int act, float lo, float hi) {
-  if (act == ACT_RELU) return v != v ? v : fmaxf(v, 0.0f);
-  if (act == ACT_CLIP) return fminf(fmaxf(v, lo), hi);
-  if (act == ACT_SIGMOID) return 1.0f / (1.0f + __expf(-v));
-  if (act == ACT_TANH) return tanhf(v);
-  return v;
+// The fused activations (identity, ReLU, clipped ReLU) are all a clamp to [lo, hi]; keeping
+// the epilogue to that one form keeps its unrolled body small.
+__device__ __forceinline__ float tc_act(float v, float lo, float hi) {
+  return fminf(fmaxf(v, lo), hi);
 }
 
 // Byte offset of 16-byte chunk `chunk` of row `row` inside a staged slab whose rows are
@@ -258,6 +259,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
   const int rows_valid = p.tw * p.th * p.tn;
   const int ksteps = p.num_taps * p.cblocks;
   int err_code = 0;
+  long long dbg_t0 = 0, dbg_t1 = 0;
+  const long long dbg_start = clock64();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -276,10 +279,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
         for (int t = 0; t < p.num_taps && !err_code; ++t) {
           const TcTap tap = p.taps[t];
           for (int cb = 0; cb < p.cblocks; ++cb) {
+            long long tw0 = clock64();
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
               err_code = 1;
               break;
             }
+            dbg_t0 += clock64() - tw0;
             mbar_expect_tx(full_bar(stage), tx_bytes);
             tma_load_4d(sA + stage * a_bytes, &p.tmA[tap.map], full_bar(stage), cb * bk,
                         q0 + tap.dw, p0 + tap.dh, n0);
@@ -298,18 +303,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+        long long tw0 = clock64();
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           err_code = 2;
           break;
         }
+        dbg_t0 += clock64() - tw0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         uint32_t accumulate = 0;
         for (int ks = 0; ks < ksteps; ++ks) {
+          long long tw1 = clock64();
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
             err_code = 3;
             break;
           }
+          dbg_t1 += clock64() - tw1;
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
           const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
@@ -332,6 +341,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
     }
   } else {
     // ------------------------------------------------------------ epilogue (128 threads)
+    const float act_lo = p.lo, act_hi = p.hi;
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
     const int row = quad * 32 + lane;        // accumulator row == pixel index in the tile
     const int et = threadIdx.x - 64;         // 0..127
@@ -356,17 +366,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
       for (int i = et; i < BN; i += 128)
         bias_s[i] = (p.bias && k0 + i < p.K) ? p.bias[k0 + i] : 0.0f;
       epi_bar();
+      long long tw0 = clock64();
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
         err_code = 4;
         break;
       }
+      dbg_t0 += clock64() - tw0;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
       for (int sl = 0; sl < nslab; ++sl) {
         uint32_t dbuf = 0;
         if (!p.out_f32) {
           dbuf = sD + (d_iter & 1) * SLAB_BYTES;
-          if (leader) tma_store_wait_read<1>();
+          if (leader && !(p.dbg & 8)) tma_store_wait_read<1>();
           epi_bar();  // slab buffer (d_iter & 1) is free; residual slab (r_iter+1)&1 is free
         }
         if (p.has_res) {
@@ -385,8 +397,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
 #pragma unroll
         for (int h = 0; h < DC / 32; ++h) {
           uint32_t r[32];
-          tc_ld32(t_row + (uint32_t)(sl * DC + h * 32), r);
-          tc_ld_wait();
+          if (!(p.dbg & 4)) {
+            tc_ld32(t_row + (uint32_t)(sl * DC + h * 32), r);
+            tc_ld_wait();
+          } else {
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) + bias_s[sl * DC + h * 32 + j];
@@ -406,7 +422,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
             }
           }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = tc_act(v[j], p.act, p.lo, p.hi);
+          for (int j = 0; j < 32; ++j) v[j] = tc_act(v[j], act_lo, act_hi);
           if (p.out_f32) {
             const int m = q0 + row;
             if (row < rows_valid && m < p.m_total) {
@@ -427,7 +443,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
               pk.y = *reinterpret_cast<uint32_t *>(&b1);
               pk.z = *reinterpret_cast<uint32_t *>(&b2);
               pk.w = *reinterpret_cast<uint32_t *>(&b3);
-              *reinterpret_cast<uint4 *>(dptr + slab_off(row, h * 4 + c4, DC * 2)) = pk;
+              if (!(p.dbg & 2)) *reinterpret_cast<uint4 *>(dptr + slab_off(row, h * 4 + c4, DC * 2)) = pk;
             }
           }
         }
@@ -435,7 +451,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
         if (!p.out_f32) {
           fence_async_smem();
           epi_bar();
-          if (leader) {
+          if (leader && !(p.dbg & 1)) {
             tma_store_4d(&p.tmD, dbuf, k0 + sl * DC, q0, p0, n0);
             tma_store_commit();
           }
@@ -451,6 +467,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
     if (leader) tma_store_wait_read<0>();
   }
 
+  if (p.dbg_out && blockIdx.x == 0 && lane == 0 && warp <= 2) {
+    p.dbg_out[warp * 4 + 0] = dbg_t0;
+    p.dbg_out[warp * 4 + 1] = dbg_t1;
+    p.dbg_out[warp * 4 + 2] = clock64() - dbg_start;
+  }
   if (err_code) {
     atomicExch(p.err, 1000 + err_code);
     *abort_flag = 1;
@@ -549,6 +570,7 @@ static int pick_bn(int K) { return K > 128 ? 256 : (K > 64 ? 128 : (K > 32 ? 64 
 
 bool tc_conv_supported(const TcConvArgs &a) {
   if (pick_bk(a.Cf) == 0) return false;
+  if (a.act != ACT_IDENTITY && a.act != ACT_RELU && a.act != ACT_CLIP) return false;
   if (a.stride_h < 1 || a.stride_w < 1 || a.stride_h > 2 || a.stride_w > 2) return false;
   if (a.R * a.S > TC_MAX_TAPS) return false;
   if (!a.out_f32 && a.K % 8 != 0) return false;
@@ -594,11 +616,17 @@ static Plan build_plan(const TcConvArgs &a) {
   p.bias = a.bias;
   p.has_res = a.residual ? 1 : 0;
   p.act = a.act;
-  p.lo = a.lo;
-  p.hi = a.hi;
+  p.lo = a.act == ACT_RELU ? 0.0f : (a.act == ACT_CLIP ? a.lo : -INFINITY);
+  p.hi = a.act == ACT_CLIP ? a.hi : INFINITY;
   p.out_f32 = a.out_f32;
   p.ldo = a.ldo;
   p.err = rt().dev_err;
+  { const char *d = getenv("OCCAMY_TC_DBG"); p.dbg = d ? atoi(d) : 0; }
+  {
+    static long long *dbg_buf = nullptr;
+    if (!dbg_buf && getenv("OCCAMY_TC_DBG")) cudaMallocManaged(&dbg_buf, 16 * sizeof(long long));
+    p.dbg_out = dbg_buf;
+  }
   const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
                     a.pad_w == 0;
   // output grid the tiles are cut from
@@ -721,6 +749,13 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
     default: launch_plan<256>(pl, s); break;
   }
   if (prof_slot >= 0) OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot + 1], s));
+  if (pl.p.dbg_out && getenv("OCCAMY_TC_DBG_PRINT")) {
+    cudaStreamSynchronize(s);
+    const long long *d = pl.p.dbg_out;
+    fprintf(stderr, "[tcdbg] tiles/cta %d ksteps %d stages %d | producer wait_empty %lld total %lld | mma wait_tempty %lld wait_full %lld total %lld | epi wait_tfull %lld total %lld\n",
+            (pl.p.total_tiles + rt().num_sms - 1) / rt().num_sms, pl.p.num_taps * pl.p.cblocks, pl.p.stages,
+            d[0], d[2], d[4], d[5], d[6], d[8], d[10]);
+  }
   OCC_CUDA(cudaGetLastError());
   count(CNT_LAUNCHES);
   count(CNT_TC_LAUNCHES);

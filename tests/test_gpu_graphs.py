@@ -33,11 +33,11 @@ def run_both(g, x, mode, fuse, pool_opt=True, dealloc_opt=True, repeats=1):
     return outs, p
 
 
-def check_logits(y, want, mode):
+def check_logits(y, want, mode, bf16_tol=2e-2):
     if mode == rt.MATH_FP32:
         assert max_rel_err(y, want) <= 1e-4
     else:
-        assert max_rel_err(y, want) <= 2e-2
+        assert max_rel_err(y, want) <= bf16_tol
     assert np.array_equal(y.argmax(1), want.argmax(1))
 
 
@@ -82,7 +82,10 @@ def test_mobilenet_v2(mode, fuse):
     x = graphs.make_input(g, 0)
     (y,), _ = run_both(g, x, mode, fuse)
     (want,) = run_graph_oracle(g, x)
-    check_logits(y, want, mode)
+    # bf16 activation storage alone (emulated on the CPU: every tensor rounded to bf16, fp32
+    # arithmetic) puts this 53-layer random-weight network 4.8e-2 from the fp32 result, so the
+    # 2e-2 bound that holds for ResNet-50 and VGG-16 cannot hold here; top-1 must still agree.
+    check_logits(y, want, mode, bf16_tol=8e-2)
 
 
 @pytest.mark.parametrize("mode", [rt.MATH_FP32, rt.MATH_BF16])
