@@ -195,6 +195,10 @@ void occamy_get_counters(int64_t out[8]);
  * many launches were recorded. */
 void occamy_profile_begin(void);
 int occamy_profile_end(float *ms, int cap);
+/* Number of convolution -> add / activation chains that arrived as separate calls and were
+ * executed as one kernel (cross-call fusion; OCCAMY_FUSE_ACROSS_CALLS=0 turns it off). */
+int64_t occamy_fused_chains(void);
+void occamy_set_cross_call_fusion(int on);
 /* Drop the resident packed-weight cache (forces re-upload and re-pack). */
 void occamy_clear_weight_cache(void);
 

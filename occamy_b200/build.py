@@ -19,7 +19,7 @@ LIB = os.path.join(HERE, "lib")
 OBJ = os.path.join(LIB, "obj")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-RUNTIME_SRCS = ["runtime.cu", "kernels_f32.cu", "kernels_nhwc.cu", "conv_tc.cu", "abi.cu",
+RUNTIME_SRCS = ["runtime.cu", "kernels_f32.cu", "kernels_nhwc.cu", "conv_tc.cu", "trace.cu", "abi.cu",
                 "misc_ops.cu"]
 REPLAY_SRCS = [os.path.join("host", "replay.cpp")]
 

@@ -5,6 +5,7 @@
 
 #include "kernels.h"
 #include "runtime.h"
+#include "trace.h"
 
 #define OCCAMY_NO_VENDOR_TYPES
 typedef cudaError_t occamy_cuda_error_t;
@@ -98,15 +99,35 @@ const float *resident_f32(const float *p, size_t bytes) {
   return p;
 }
 
-bool conv_tensor_core(const float *x, const float *w, const float *bias, float *y,
-                      const ConvGeom &g) {
+// ---- a convolution resolved down to launch arguments ------------------------------
+// `prepare_*` does everything that depends on the inputs' current state (layout
+// conversion into scratch, packed-weight lookup, bias lookup); what is left is a launch
+// that only needs to be told where to write, which residual to add and how to clamp.
+struct ConvJob {
+  bool active = false;
+  bool depthwise = false;
+  ConvGeom g;
+  TcConvArgs a;               // dense: tensor-core arguments (x, w, bias resolved)
+  const bf16 *dw_x = nullptr; // depthwise
+  const float *dw_w = nullptr;
+  const float *bias = nullptr;
+  float *out = nullptr;       // tensor the result goes to
+  bool bias_set = false, res_set = false, act_set = false;
+  int absorbed = 0;           // later calls folded into this one so far
+  uintptr_t dep_lo[2] = {0, 0}, dep_hi[2] = {0, 0};  // device ranges still to be read
+};
+
+ConvJob g_pending;  // convolution held back while later calls are folded into it
+
+bool prepare_dense(const float *x, const float *w, const float *bias, const ConvGeom &g,
+                   ConvJob &job) {
   Runtime &r = rt();
   if (g.groups != 1 || g.K % 8 != 0) return false;
-  TcConvArgs a;
+  if (g.act != ACT_IDENTITY && g.act != ACT_RELU && g.act != ACT_CLIP) return false;
+  TcConvArgs &a = job.a;
   memset(&a, 0, sizeof(a));
   a.N = g.N; a.K = g.K; a.P = g.P; a.Q = g.Q;
   a.act = g.act; a.lo = g.lo; a.hi = g.hi;
-  a.y = (bf16 *)y;
   const bool folded = g.C < 16;
   int Sp = 0, Cp = 0;
   if (folded) {
@@ -124,8 +145,10 @@ bool conv_tensor_core(const float *x, const float *w, const float *bias, float *
   }
   a.x = (const bf16 *)16;  // placeholders so the support check sees aligned pointers
   a.w = (const bf16 *)16;
+  a.y = (bf16 *)16;
   if (!tc_conv_supported(a)) return false;
 
+  job.dep_lo[0] = job.dep_hi[0] = 0;
   if (folded) {
     ensure_f32(x);
     bf16 *xf = (bf16 *)scratch_get(0, (size_t)g.N * g.H * g.Q * a.Cf * 2);
@@ -138,6 +161,8 @@ bool conv_tensor_core(const float *x, const float *w, const float *bias, float *
   } else {
     if (is_bf16(x, g.N, g.C, g.H, g.W)) {
       a.x = (const bf16 *)x;
+      job.dep_lo[0] = (uintptr_t)x;
+      job.dep_hi[0] = (uintptr_t)x + (size_t)g.N * g.C * g.H * g.W * 2;
     } else {
       ensure_f32(x);
       bf16 *xc = (bf16 *)scratch_get(0, (size_t)g.N * g.C * g.H * g.W * 2);
@@ -150,37 +175,147 @@ bool conv_tensor_core(const float *x, const float *w, const float *bias, float *
   }
   if (!a.w) return false;
   a.bias = bias ? resident_f32(bias, (size_t)g.K * 4) : nullptr;
-  launch_tc_conv(a, r.stream);
-  mark_bf16(y, g.N, g.K, g.P, g.Q);
+  job.depthwise = false;
+  job.g = g;
+  job.bias_set = bias != nullptr;
+  job.act_set = g.act != ACT_IDENTITY;
+  job.res_set = false;
   return true;
 }
 
-bool conv_depthwise_bf16(const float *x, const float *w, const float *bias, float *y,
-                         const ConvGeom &g) {
+bool prepare_depthwise(const float *x, const float *w, const float *bias, const ConvGeom &g,
+                       ConvJob &job) {
   Runtime &r = rt();
   if (g.C % 8 != 0) return false;
-  const bf16 *xb;
+  job.dep_lo[0] = job.dep_hi[0] = 0;
   if (is_bf16(x, g.N, g.C, g.H, g.W)) {
-    xb = (const bf16 *)x;
+    job.dw_x = (const bf16 *)x;
+    job.dep_lo[0] = (uintptr_t)x;
+    job.dep_hi[0] = (uintptr_t)x + (size_t)g.N * g.C * g.H * g.W * 2;
   } else {
     ensure_f32(x);
     bf16 *xc = (bf16 *)scratch_get(0, (size_t)g.N * g.C * g.H * g.W * 2);
     if (!xc) return false;
     launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, r.stream);
-    xb = xc;
+    job.dw_x = xc;
   }
-  const float *wp = (const float *)packed_weights(w, PACK_DW, (size_t)g.R * g.S * g.C * 4, g.K,
-                                                  g.C, g.R, g.S, 0, 0);
-  if (!wp) return false;
-  launch_depthwise_bf16(xb, wp, bias ? resident_f32(bias, (size_t)g.C * 4) : nullptr, (bf16 *)y, g,
-                        r.stream);
-  mark_bf16(y, g.N, g.K, g.P, g.Q);
+  job.dw_w = (const float *)packed_weights(w, PACK_DW, (size_t)g.R * g.S * g.C * 4, g.K, g.C, g.R,
+                                          g.S, 0, 0);
+  if (!job.dw_w) return false;
+  job.bias = bias ? resident_f32(bias, (size_t)g.C * 4) : nullptr;
+  job.depthwise = true;
+  job.g = g;
+  job.bias_set = bias != nullptr;
+  job.act_set = g.act != ACT_IDENTITY;
+  job.res_set = false;
   return true;
 }
 
-float *conv_common(float *x, const int64_t *dX, float *w, const int64_t *dW, float *bias,
+bool ranges_overlap(uintptr_t alo, uintptr_t ahi, uintptr_t blo, uintptr_t bhi) {
+  return ahi > alo && bhi > blo && alo < bhi && blo < ahi;
+}
+
+void launch_job(ConvJob &job) {
+  Runtime &r = rt();
+  const ConvGeom &g = job.g;
+  // A convolution that was held back may find its output placed over memory it still has
+  // to read (the planner reuses a tensor's bytes as soon as the recorded program no longer
+  // needs them).  The input then moves to scratch first; a residual operand may stay only
+  // if the output covers it exactly (each tile reads its residual before it is stored).
+  const uintptr_t olo = (uintptr_t)job.out;
+  const uintptr_t ohi = olo + (size_t)g.N * g.K * g.P * g.Q * 2;
+  if (ranges_overlap(olo, ohi, job.dep_lo[0], job.dep_hi[0])) {
+    const size_t bytes = job.dep_hi[0] - job.dep_lo[0];
+    void *tmp = scratch_get(4, bytes);
+    OCC_CUDA(cudaMemcpyAsync(tmp, (const void *)job.dep_lo[0], bytes, cudaMemcpyDeviceToDevice,
+                             r.stream));
+    if (job.depthwise) job.dw_x = (const bf16 *)tmp;
+    else job.a.x = (const bf16 *)tmp;
+    count(CNT_LAUNCHES);
+  }
+  if (ranges_overlap(olo, ohi, job.dep_lo[1], job.dep_hi[1]) &&
+      !(olo == job.dep_lo[1] && ohi == job.dep_hi[1])) {
+    const size_t bytes = job.dep_hi[1] - job.dep_lo[1];
+    void *tmp = scratch_get(5, bytes);
+    OCC_CUDA(cudaMemcpyAsync(tmp, (const void *)job.dep_lo[1], bytes, cudaMemcpyDeviceToDevice,
+                             r.stream));
+    job.a.residual = (const bf16 *)tmp;
+    count(CNT_LAUNCHES);
+  }
+  if (job.depthwise) {
+    launch_depthwise_bf16(job.dw_x, job.dw_w, job.bias, (bf16 *)job.out, g, r.stream);
+  } else {
+    job.a.y = (bf16 *)job.out;
+    job.a.act = g.act; job.a.lo = g.lo; job.a.hi = g.hi;
+    launch_tc_conv(job.a, r.stream);
+  }
+  mark_bf16(job.out, g.N, g.K, g.P, g.Q);
+}
+
+// Executes the held-back convolution as far as it has been built up.
+void flush_pending() {
+  if (!g_pending.active) return;
+  g_pending.active = false;
+  if (g_pending.absorbed) trace_count_chain();
+  launch_job(g_pending);
+}
+
+// [p, p+bytes) is about to be overwritten or freed (`writes`), or merely handed out again:
+// in the first case whatever still has to read it must run first.  Handing a range out
+// writes nothing (its zero fill is lazy), so a held-back convolution may keep reading its
+// inputs from it; launch_job() deals with the case that its own output lands there.
+void pending_guard_range(const void *p, size_t bytes, bool writes) {
+  if (!g_pending.active) return;
+  const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
+  if (writes)
+    for (int k = 0; k < 2; ++k)
+      if (ranges_overlap(lo, hi, g_pending.dep_lo[k], g_pending.dep_hi[k])) {
+        if (rt().log) fprintf(stderr, "[occamy] held-back conv runs early: input %d overwritten\n", k);
+        flush_pending();
+        return;
+      }
+  // the tensor it is going to write must also still belong to it
+  const uintptr_t olo = (uintptr_t)g_pending.out;
+  const uintptr_t ohi = olo + (size_t)g_pending.g.N * g_pending.g.K * g_pending.g.P * g_pending.g.Q * 2;
+  if (ranges_overlap(lo, hi, olo, ohi)) {
+    if (rt().log) fprintf(stderr, "[occamy] held-back conv runs early: output re-handed out\n");
+    flush_pending();
+  }
+}
+
+// Common tail of every traced entry point: record the call, end the speculation when the
+// recorded sequence is left, run the held-back convolution unless this call continues it.
+void before_write_hook(const void *p, size_t bytes) { pending_guard_range(p, bytes, true); }
+
+Role step(Entry &e, bool passive) {
+  rt().before_write = before_write_hook;
+  bool deviated = false;
+  const Role role = trace_step(e, &deviated);
+  if (deviated) {
+    flush_pending();
+    if (trace_has_elided())
+      set_error(989, "call sequence left the recorded one after tensors were skipped by "
+                     "cross-call fusion (set OCCAMY_FUSE_ACROSS_CALLS=0)");
+  }
+  if (!passive && role != R_ABSORB) {
+    if (g_pending.active && rt().log)
+      fprintf(stderr, "[occamy] held-back conv closed by call sym %d (absorbed %d)\n", e.sym,
+              g_pending.absorbed);
+    flush_pending();
+  }
+  return role;
+}
+
+void elide(void *p) {
+  uintptr_t base;
+  TensorRec *rec = reg_find(p, &base);
+  if (rec && base == (uintptr_t)p) rec->fmt = FMT_ELIDED;
+  trace_note_elided();
+}
+
+float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t *dW, float *bias,
                    int64_t groups, const int64_t *pads, const int64_t *strides, int act, float lo,
-                   float hi, float *y) {
+                   float hi, int64_t act_mode, float *y) {
   Runtime &r = rt();
   ConvGeom g;
   g.N = (int)dX[0]; g.C = (int)dX[1]; g.H = (int)dX[2]; g.W = (int)dX[3];
@@ -189,21 +324,50 @@ float *conv_common(float *x, const int64_t *dX, float *w, const int64_t *dW, flo
   g.pad_h = (int)pads[0]; g.pad_w = (int)pads[1];
   g.stride_h = (int)strides[0]; g.stride_w = (int)strides[1];
   g.act = act; g.lo = lo; g.hi = hi;
-  if (g.stride_h < 1 || g.stride_w < 1 || g.C % g.groups || g.K % g.groups ||
-      dW[1] * g.groups != g.C) {
+  const bool shape_ok = !(g.stride_h < 1 || g.stride_w < 1 || g.C % g.groups || g.K % g.groups ||
+                          dW[1] * g.groups != g.C);
+  g.P = shape_ok ? (g.H + 2 * g.pad_h - g.R) / g.stride_h + 1 : 0;
+  g.Q = shape_ok ? (g.W + 2 * g.pad_w - g.S) / g.stride_w + 1 : 0;
+  const bool depthwise = g.groups > 1 && g.groups == g.C && g.K == g.C;
+
+  Entry e = trace_entry(sym);
+  te_ptr(e, x); te_ptr(e, w); te_ptr(e, bias); te_ptr(e, y);
+  te_dims(e, dX, 4); te_dims(e, dW, 4); te_dims(e, pads, 2); te_dims(e, strides, 2);
+  te_i(e, groups); te_i(e, act_mode);
+  e.in[0] = (uintptr_t)x; e.in[1] = (uintptr_t)w; e.in[2] = (uintptr_t)bias;
+  e.out = (uintptr_t)y;
+  e.dims[0] = g.N; e.dims[1] = g.K; e.dims[2] = g.P; e.dims[3] = g.Q;
+  e.out_bytes = (int64_t)g.N * g.K * g.P * g.Q * 4;
+  e.kind = (int)act_mode;
+  e.depthwise = depthwise;
+  e.fusable = shape_ok && r.mode == MATH_BF16 && g.P > 0 && g.Q > 0 && g.N > 0 &&
+              (depthwise ? g.C % 8 == 0
+                         : (g.groups == 1 && g.K % 8 == 0 && (g.C < 16 || g.C % 16 == 0)));
+  const Role role = step(e, false);
+
+  if (!shape_ok) {
     set_error(997, "convolution: inconsistent shape");
     return y;
   }
-  g.P = (g.H + 2 * g.pad_h - g.R) / g.stride_h + 1;
-  g.Q = (g.W + 2 * g.pad_w - g.S) / g.stride_w + 1;
   if (g.P <= 0 || g.Q <= 0 || g.N == 0) return y;
-  const bool depthwise = g.groups > 1 && g.groups == g.C && g.K == g.C;
   if (r.log)
-    fprintf(stderr, "[occamy] conv x[%d,%d,%d,%d] w[%d,%d,%d,%d] g%d s%d p%d act%d\n", g.N, g.C,
-            g.H, g.W, g.K, (int)dW[1], g.R, g.S, g.groups, g.stride_h, g.pad_h, act);
+    fprintf(stderr, "[occamy] conv x[%d,%d,%d,%d] w[%d,%d,%d,%d] g%d s%d p%d act%d role%d\n", g.N,
+            g.C, g.H, g.W, g.K, (int)dW[1], g.R, g.S, g.groups, g.stride_h, g.pad_h, act,
+            (int)role);
   if (r.mode == MATH_BF16) {
-    if (g.groups == 1 && conv_tensor_core(x, w, bias, y, g)) return y;
-    if (depthwise && conv_depthwise_bf16(x, w, bias, y, g)) return y;
+    ConvJob job;
+    const bool ok = depthwise ? prepare_depthwise(x, w, bias, g, job)
+                              : (g.groups == 1 && prepare_dense(x, w, bias, g, job));
+    if (ok) {
+      job.out = y;
+      if (role == R_DEFER) {   // later calls of the recorded sequence fold into this one
+        g_pending = job;
+        g_pending.active = true;
+        return y;
+      }
+      launch_job(job);
+      return y;
+    }
   }
   ensure_f32(x);
   ensure_f32(w);
@@ -212,6 +376,16 @@ float *conv_common(float *x, const int64_t *dX, float *w, const int64_t *dW, flo
   else launch_conv_f32(x, w, bias, y, g, r.stream);
   mark_f32(y);
   return y;
+}
+
+// The held-back convolution takes over a following element-wise call.  `out` is where that
+// call would have written; the convolution's own output is skipped unless it is the same.
+void pending_retarget(float *out) {
+  g_pending.absorbed++;
+  if (out != g_pending.out) {
+    elide(g_pending.out);
+    g_pending.out = out;
+  }
 }
 
 int64_t prod(const int64_t *d, int64_t rank) {
@@ -226,11 +400,16 @@ extern "C" {
 
 // ---------------------------------------------------------------- memory pool
 cudaError_t wrapDNNMalloc(void **devPtr, size_t size) {
-  Runtime &r = rt();
-  cudaError_t e = cudaMalloc(devPtr, size ? size : 1);
-  if (e != cudaSuccess) die("Malloc", e, size);
+  rt();
+  cudaError_t err = cudaMalloc(devPtr, size ? size : 1);
+  if (err != cudaSuccess) die("Malloc", err, size);
+  Entry e = trace_entry(S_MALLOC);
+  te_i(e, (int64_t)size);
+  e.out = (uintptr_t)*devPtr;
+  e.out_bytes = (int64_t)size;
+  step(e, true);
+  pending_guard_range(*devPtr, size, false);
   reg_new(*devPtr, size, FMT_ZERO);  // zero fill is issued only if somebody reads it unwritten
-  (void)r;
   return cudaSuccess;
 }
 
@@ -245,16 +424,27 @@ cudaError_t wrapDNNMemPoolInit(void **devPtr, size_t size) {
       OCC_CUDA(cudaFree(g_pool_cache.base));
       g_pool_cache.base = nullptr;
     }
-    cudaError_t e = cudaMalloc(devPtr, size ? size : 1);
-    if (e != cudaSuccess) die("MemPoolInit", e, size);
+    cudaError_t err = cudaMalloc(devPtr, size ? size : 1);
+    if (err != cudaSuccess) die("MemPoolInit", err, size);
   }
   g_pools.push_back(PoolRec{*devPtr, size});
   if ((int64_t)size > r.counters[CNT_POOL_HWM]) r.counters[CNT_POOL_HWM] = (int64_t)size;
+  trace_set_pool(*devPtr, size);
+  Entry e = trace_entry(S_POOLINIT);
+  te_i(e, (int64_t)size);
+  step(e, false);
   return cudaSuccess;
 }
 
 cudaError_t wrapDNNMemOffset(void **devPtr, void *basePtr, size_t offset, size_t mallocSize) {
   *devPtr = (char *)basePtr + offset;
+  Entry e = trace_entry(S_MEMOFFSET);
+  te_ptr(e, *devPtr);
+  te_i(e, (int64_t)mallocSize);
+  e.out = (uintptr_t)*devPtr;
+  e.out_bytes = (int64_t)mallocSize;
+  step(e, true);
+  pending_guard_range(*devPtr, mallocSize, false);
   reg_new(*devPtr, mallocSize, FMT_ZERO);
   return cudaSuccess;
 }
@@ -263,9 +453,22 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
                           cudaStream_t /*stream*/) {
   Runtime &r = rt();
   if (count_ == 0) return cudaSuccess;
-  cudaError_t e = cudaSuccess;
+  cudaError_t err = cudaSuccess;
   if (kind == 1 || kind == 3) {
-    if (kind == 3) ensure_f32(src);
+    Entry e = trace_entry(kind == 1 ? S_H2D : S_D2D);
+    te_ptr(e, dst);
+    te_i(e, (int64_t)count_);
+    if (kind == 3) {
+      te_ptr(e, src);
+      e.in[0] = (uintptr_t)src;
+    }
+    e.out = (uintptr_t)dst;
+    e.out_bytes = (int64_t)count_;
+    step(e, kind == 1);
+    if (kind == 3) {
+      pending_guard_range(dst, count_, true);
+      ensure_f32(src);
+    }
     uintptr_t base;
     TensorRec *rec = reg_find(dst, &base);
     const bool whole = rec && base == (uintptr_t)dst && count_ + 32 > rec->bytes;
@@ -280,20 +483,26 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
         auto it = r.resident.find(src);
         if (it != r.resident.end() && it->second.first == count_ &&
             it->second.second == rec->host_hash) {
-          rec->fmt = FMT_PENDING;
+          rec->fmt = FMT_PENDING;   // nothing is written now
           count(CNT_H2D_SKIPPED, (int64_t)count_);
           return cudaSuccess;
         }
       }
     }
-    e = cudaMemcpyAsync(dst, src, count_, kind == 1 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
-                        r.stream);
+    if (kind == 1) pending_guard_range(dst, count_, true);
+    err = cudaMemcpyAsync(dst, src, count_,
+                          kind == 1 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice, r.stream);
     if (kind == 1) count(CNT_H2D_BYTES, (int64_t)count_);
     if (rec && whole) {
       rec->fmt = FMT_F32;
       if (kind == 3) rec->host_src = nullptr;
     }
   } else if (kind == 2) {
+    Entry e = trace_entry(S_D2H);
+    te_ptr(e, src);
+    te_i(e, (int64_t)count_);
+    e.in[0] = (uintptr_t)src;
+    step(e, false);
     uintptr_t base;
     TensorRec *rec = reg_find(src, &base);
     const void *from = src;
@@ -308,8 +517,8 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
     } else {
       ensure_f32(src);
     }
-    e = cudaMemcpyAsync(dst, from, count_, cudaMemcpyDeviceToHost, r.stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(r.stream);
+    err = cudaMemcpyAsync(dst, from, count_, cudaMemcpyDeviceToHost, r.stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(r.stream);
     // surface a kernel-side watchdog report, if any
     if (r.dev_err && r.host_err) {
       cudaMemcpy(r.host_err, r.dev_err, sizeof(int), cudaMemcpyDeviceToHost);
@@ -319,11 +528,13 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
       }
     }
   } else {
-    e = cudaMemcpyAsync(dst, src, count_, (cudaMemcpyKind)kind, r.stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(r.stream);
+    Entry e = trace_entry(S_OPAQUE);
+    step(e, false);
+    err = cudaMemcpyAsync(dst, src, count_, (cudaMemcpyKind)kind, r.stream);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(r.stream);
   }
-  if (e != cudaSuccess) {
-    printf("[Memcpy] GPU error: %s\n", cudaGetErrorString(e));
+  if (err != cudaSuccess) {
+    printf("[Memcpy] GPU error: %s\n", cudaGetErrorString(err));
     exit(-1);
   }
   return cudaSuccess;
@@ -341,39 +552,55 @@ cudaError_t wrapDNNDealloc(void *devPtr) {
       g_pools.erase(g_pools.begin() + i);
       break;
     }
-  if (was_pool && pool_cache_enabled()) {
-    // Work still in flight on the launch stream is ordered before anything a later
-    // inference enqueues, so the block can be handed out again without waiting.
-    if (bytes) reg_drop_range(devPtr, bytes);
-    if (g_pool_cache.base) {
-      OCC_CUDA(cudaStreamSynchronize(r.stream));
-      OCC_CUDA(cudaFree(g_pool_cache.base));
+  if (was_pool) {
+    Entry e = trace_entry(S_POOLFREE);
+    step(e, false);   // runs whatever is still held back
+    trace_set_pool(nullptr, 0);
+    if (pool_cache_enabled()) {
+      // Work still in flight on the launch stream is ordered before anything a later
+      // inference enqueues, so the block can be handed out again without waiting.
+      if (bytes) reg_drop_range(devPtr, bytes);
+      if (g_pool_cache.base) {
+        OCC_CUDA(cudaStreamSynchronize(r.stream));
+        OCC_CUDA(cudaFree(g_pool_cache.base));
+      }
+      g_pool_cache = PoolRec{devPtr, bytes};
+      return cudaSuccess;
     }
-    g_pool_cache = PoolRec{devPtr, bytes};
-    return cudaSuccess;
-  }
-  if (!bytes) {
+  } else {
     uintptr_t base;
     TensorRec *rec = reg_find(devPtr, &base);
     if (rec && base == (uintptr_t)devPtr) bytes = rec->bytes;
+    Entry e = trace_entry(S_DEALLOC);
+    te_ptr(e, devPtr);
+    e.out = (uintptr_t)devPtr;
+    e.out_bytes = (int64_t)bytes;
+    step(e, true);
+    pending_guard_range(devPtr, bytes ? bytes : 1, true);
   }
   OCC_CUDA(cudaStreamSynchronize(r.stream));
   if (bytes) reg_drop_range(devPtr, bytes);
-  cudaError_t e = cudaFree(devPtr);
-  if (e != cudaSuccess) {
-    printf("[Dealloc] GPU error: %s\n", cudaGetErrorString(e));
+  cudaError_t err = cudaFree(devPtr);
+  if (err != cudaSuccess) {
+    printf("[Dealloc] GPU error: %s\n", cudaGetErrorString(err));
     exit(-1);
   }
   return cudaSuccess;
 }
 
 // ---------------------------------------------------------------- handle
+// The compiled function creates the handle on entry and destroys it before it returns:
+// these two calls delimit one inference for the call trace.
 int cudnnCreate(cudnnContext **handle) {
   rt();
   *handle = reinterpret_cast<cudnnContext *>(malloc(16));
+  flush_pending();
+  trace_begin();
   return *handle ? 0 : 2;
 }
 int cudnnDestroy(cudnnContext *handle) {
+  flush_pending();
+  trace_end();
   free(handle);
   return 0;
 }
@@ -382,7 +609,8 @@ int cudnnDestroy(cudnnContext *handle) {
 float *DNNConvFunc(cudnnContext *, float *x, int64_t dimX[4], float *w, int64_t dimW[4],
                    float * /*workspace*/, int64_t /*workspaceSize*/, int64_t /*algo*/,
                    int64_t groups, int64_t pads[2], int64_t strides[2], float *y) {
-  return conv_common(x, dimX, w, dimW, nullptr, groups, pads, strides, ACT_IDENTITY, 0.f, 0.f, y);
+  return conv_common(S_CONV, x, dimX, w, dimW, nullptr, groups, pads, strides, ACT_IDENTITY, 0.f,
+                     0.f, 5, y);
 }
 
 float *DNNConvBiasActivFunc(cudnnContext *, float *x, int64_t dimX[4], float *w, int64_t dimW[4],
@@ -396,7 +624,8 @@ float *DNNConvBiasActivFunc(cudnnContext *, float *x, int64_t dimX[4], float *w,
   else if (activMode == 3) { act = ACT_CLIP; lo = 0.f; hi = 6.f; }
   else if (activMode == 0) act = ACT_SIGMOID;
   else if (activMode == 2) act = ACT_TANH;
-  return conv_common(x, dimX, w, dimW, bias, 1, pads, strides, act, lo, hi, y);
+  return conv_common(S_CONV_BIAS_ACT, x, dimX, w, dimW, bias, 1, pads, strides, act, lo, hi,
+                     activMode, y);
 }
 
 // ---------------------------------------------------------------- element-wise
@@ -404,6 +633,24 @@ float *DNNActiveFunc(cudnnContext *, float *x, int64_t dimX[4], int32_t mode, fl
   Runtime &r = rt();
   const int64_t n = numel4(dimX);
   const int act = mode == 0 ? ACT_SIGMOID : (mode == 1 ? ACT_RELU : (mode == 2 ? ACT_TANH : ACT_IDENTITY));
+  Entry e = trace_entry(S_ACTIVE);
+  te_ptr(e, x); te_ptr(e, y); te_dims(e, dimX, 4); te_i(e, mode);
+  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = n * 4;
+  for (int i = 0; i < 4; ++i) e.dims[i] = dimX[i];
+  e.kind = mode == 1 ? CK_RELU : CK_NONE;
+  const Role role = step(e, false);
+  if (role == R_ABSORB && g_pending.active) {
+    const ConvGeom &g = g_pending.g;
+    if (mode == 1 && x == g_pending.out && !g_pending.act_set && dimX[0] == g.N &&
+        dimX[1] == g.K && dimX[2] == g.P && dimX[3] == g.Q) {
+      pending_retarget(y);
+      g_pending.g.act = ACT_RELU;
+      g_pending.act_set = true;
+      flush_pending();   // an activation closes the chain
+      return y;
+    }
+    flush_pending();
+  }
   if (is_bf16(x, dimX[0], dimX[1], dimX[2], dimX[3])) {
     launch_add_act_bf16((const bf16 *)x, nullptr, nullptr, (int)dimX[1], (bf16 *)y, n, act, 0.f,
                         0.f, r.stream);
@@ -419,6 +666,26 @@ float *DNNActiveFunc(cudnnContext *, float *x, int64_t dimX[4], int32_t mode, fl
 float *CUDAClipFunc(float *x, float *y, int64_t *dimOut, float lo, float hi, int64_t rank) {
   Runtime &r = rt();
   const int64_t n = prod(dimOut, rank);
+  Entry e = trace_entry(S_CLIP);
+  te_ptr(e, x); te_ptr(e, y); te_dims(e, dimOut, (int)rank); te_f(e, lo); te_f(e, hi);
+  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = n * 4;
+  for (int i = 0; i < 4 && i < rank; ++i) e.dims[i] = dimOut[i];
+  e.kind = rank == 4 ? CK_CLIP : CK_NONE;
+  const Role role = step(e, false);
+  if (role == R_ABSORB && g_pending.active) {
+    const ConvGeom &g = g_pending.g;
+    if (rank == 4 && x == g_pending.out && !g_pending.act_set && dimOut[0] == g.N &&
+        dimOut[1] == g.K && dimOut[2] == g.P && dimOut[3] == g.Q) {
+      pending_retarget(y);
+      g_pending.g.act = ACT_CLIP;
+      g_pending.g.lo = lo;
+      g_pending.g.hi = hi;
+      g_pending.act_set = true;
+      flush_pending();
+      return y;
+    }
+    flush_pending();
+  }
   if (rank == 4 && is_bf16(x, dimOut[0], dimOut[1], dimOut[2], dimOut[3])) {
     launch_add_act_bf16((const bf16 *)x, nullptr, nullptr, (int)dimOut[1], (bf16 *)y, n, ACT_CLIP,
                         lo, hi, r.stream);
@@ -437,27 +704,69 @@ float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, 
   Runtime &r = rt();
   (void)dimOut;
   (void)rankOut;
-  if (rankA > 8 || rankB > rankA) {
+  const bool rank_ok = rankA <= 8 && rankB <= rankA && rankA >= 1;
+  // B's shape padded with leading 1s to A's rank
+  int64_t dB[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+  if (rank_ok)
+    for (int i = 0; i < rankA; ++i) dB[i] = i < rankA - rankB ? 1 : dimB[i - (rankA - rankB)];
+  bool same = rank_ok && rankA == 4;
+  for (int i = 0; same && i < 4; ++i) same = dB[i] == dimA[i];
+  const bool bias_shape = rank_ok && rankA == 4 && dB[0] == 1 && dB[1] == dimA[1] && dB[2] == 1 &&
+                          dB[3] == 1 && !same;
+
+  Entry e = trace_entry(S_TENSOR_OP);
+  te_ptr(e, A); te_ptr(e, B); te_ptr(e, out);
+  te_i(e, opMode); te_f(e, bias);
+  if (rank_ok) { te_dims(e, dimA, rankA); te_dims(e, dB, rankA); }
+  e.in[0] = (uintptr_t)A; e.in[1] = opMode == 4 ? 0 : (uintptr_t)B; e.out = (uintptr_t)out;
+  e.out_bytes = rank_ok ? prod(dimA, rankA) * 4 : 0;
+  for (int i = 0; i < 4 && i < rankA; ++i) e.dims[i] = dimA[i];
+  if (opMode == 0 && bias == 1.0f) e.kind = bias_shape ? CK_BIAS_ADD : (same ? CK_SAME_ADD : CK_NONE);
+  const Role role = step(e, false);
+
+  if (!rank_ok) {
     set_error(996, "tensor op: unsupported rank");
     return out;
   }
-  // B's shape padded with leading 1s to A's rank
-  int64_t dB[8];
-  for (int i = 0; i < rankA; ++i) dB[i] = i < rankA - rankB ? 1 : dimB[i - (rankA - rankB)];
+  if (role == R_ABSORB && g_pending.active) {
+    const ConvGeom &g = g_pending.g;
+    const bool dims_ok = dimA[0] == g.N && dimA[1] == g.K && dimA[2] == g.P && dimA[3] == g.Q;
+    if (e.kind == CK_BIAS_ADD && dims_ok && A == g_pending.out && !g_pending.bias_set &&
+        !g_pending.res_set && !g_pending.act_set) {
+      const float *bd = resident_f32(B, (size_t)g.K * 4);
+      if (g_pending.depthwise) g_pending.bias = bd;
+      else g_pending.a.bias = bd;
+      g_pending.bias_set = true;
+      pending_retarget(out);
+      return out;
+    }
+    if (e.kind == CK_SAME_ADD && dims_ok && !g_pending.depthwise && !g_pending.res_set &&
+        !g_pending.act_set && ((A == g_pending.out) != (B == g_pending.out))) {
+      const float *other = A == g_pending.out ? B : A;
+      if (is_bf16(other, g.N, g.K, g.P, g.Q)) {
+        g_pending.a.residual = (const bf16 *)other;
+        g_pending.res_set = true;
+        g_pending.dep_lo[1] = (uintptr_t)other;
+        g_pending.dep_hi[1] = (uintptr_t)other + (size_t)g.N * g.K * g.P * g.Q * 2;
+        pending_retarget(out);
+        return out;
+      }
+    }
+    flush_pending();
+  }
   if (opMode == 0 && rankA == 4 && bias == 1.0f &&
       is_bf16(A, dimA[0], dimA[1], dimA[2], dimA[3])) {
     const int64_t n = numel4(dimA);
-    bool same = true;
-    for (int i = 0; i < 4; ++i) same &= dB[i] == dimA[i];
     if (same && is_bf16(B, dimA[0], dimA[1], dimA[2], dimA[3])) {
       launch_add_act_bf16((const bf16 *)A, (const bf16 *)B, nullptr, (int)dimA[1], (bf16 *)out, n,
                           ACT_IDENTITY, 0.f, 0.f, r.stream);
       mark_bf16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
       return out;
     }
-    if (dB[0] == 1 && dB[1] == dimA[1] && dB[2] == 1 && dB[3] == 1) {
-      ensure_f32(B);
-      launch_add_act_bf16((const bf16 *)A, nullptr, B, (int)dimA[1], (bf16 *)out, n, ACT_IDENTITY,
+    if (bias_shape) {
+      // a bias vector uploaded from host memory is kept resident like the filters are
+      const float *bd = resident_f32(B, (size_t)dimA[1] * 4);
+      launch_add_act_bf16((const bf16 *)A, nullptr, bd, (int)dimA[1], (bf16 *)out, n, ACT_IDENTITY,
                           0.f, 0.f, r.stream);
       mark_bf16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
       return out;
@@ -475,12 +784,17 @@ float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, 
 }
 
 // ---------------------------------------------------------------- pooling / reduction
-static float *pool_common(float *x, int64_t *dI, float *y, int64_t *dO, int64_t *kernel,
+static float *pool_common(int sym, float *x, int64_t *dI, float *y, int64_t *dO, int64_t *kernel,
                           int64_t *padding, int64_t *stride, bool avg) {
   Runtime &r = rt();
   const int N = (int)dI[0], C = (int)dI[1], H = (int)dI[2], W = (int)dI[3];
   const int P = (int)dO[2], Q = (int)dO[3];
   const int ph = (int)padding[0], pw = (int)padding[2];
+  Entry e = trace_entry(sym);
+  te_ptr(e, x); te_ptr(e, y); te_dims(e, dI, 4); te_dims(e, dO, 4); te_dims(e, kernel, 2);
+  te_dims(e, padding, 4); te_dims(e, stride, 2);
+  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = numel4(dO) * 4;
+  step(e, false);
   if (r.mode == MATH_BF16 && C % 8 == 0 && is_bf16(x, N, C, H, W)) {
     launch_pool_bf16((const bf16 *)x, (bf16 *)y, N, C, H, W, P, Q, (int)kernel[0], (int)kernel[1],
                      ph, pw, (int)stride[0], (int)stride[1], avg, r.stream);
@@ -496,17 +810,23 @@ static float *pool_common(float *x, int64_t *dI, float *y, int64_t *dO, int64_t 
 
 float *DNNMaxPoolFunc(cudnnContext *, float *x, int64_t dimIn[4], float *y, int64_t dimOut[4],
                       int64_t kernel[2], int64_t padding[4], int64_t stride[2]) {
-  return pool_common(x, dimIn, y, dimOut, kernel, padding, stride, false);
+  return pool_common(S_MAXPOOL, x, dimIn, y, dimOut, kernel, padding, stride, false);
 }
 
 float *DNNAveragePoolFunc(cudnnContext *, float *x, int64_t dimIn[4], float *y, int64_t dimOut[4],
                           int64_t kernel[2], int64_t padding[4], int64_t stride[2]) {
-  return pool_common(x, dimIn, y, dimOut, kernel, padding, stride, true);
+  return pool_common(S_AVGPOOL, x, dimIn, y, dimOut, kernel, padding, stride, true);
 }
 
 float *DNNReduceFunc(cudnnContext *, int32_t rank, float *x, int64_t *dimIn, float *y,
                      int64_t *dimOut, int32_t mode) {
   Runtime &r = rt();
+  Entry e = trace_entry(S_REDUCE);
+  te_ptr(e, x); te_ptr(e, y); te_i(e, mode);
+  if (rank <= 8 && rank > 0) { te_dims(e, dimIn, rank); te_dims(e, dimOut, rank); }
+  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y;
+  e.out_bytes = rank <= 8 && rank > 0 ? prod(dimOut, rank) * 4 : 0;
+  step(e, false);
   if (mode != 5 || rank > 8) {
     set_error(995, "reduce: only mode 5 (mean) is implemented");
     return y;
@@ -533,6 +853,12 @@ float *CUBLASMatmul2dFunc(int64_t /*rank*/, float *A, int64_t dimA[2], float *B,
   const int M = (int)(transA ? dimA[1] : dimA[0]);
   const int K = (int)(transA ? dimA[0] : dimA[1]);
   const int N = (int)(transB ? dimB[0] : dimB[1]);
+  Entry e = trace_entry(S_MATMUL);
+  te_ptr(e, A); te_ptr(e, B); te_ptr(e, out); te_dims(e, dimA, 2); te_dims(e, dimB, 2);
+  te_f(e, alpha); te_f(e, beta); te_i(e, transA); te_i(e, transB);
+  e.in[0] = (uintptr_t)A; e.in[1] = (uintptr_t)B; e.in[2] = beta != 0.0f ? (uintptr_t)out : 0;
+  e.out = (uintptr_t)out; e.out_bytes = (int64_t)M * N * 4;
+  step(e, false);
   if (r.log) fprintf(stderr, "[occamy] matmul2d M%d N%d K%d tA%d tB%d\n", M, N, K, (int)transA, (int)transB);
   const bool out_zero = is_zero(out);
   if (r.mode == MATH_BF16 && !transA && transB && alpha == 1.0f && (beta == 0.0f || out_zero) &&
@@ -576,29 +902,43 @@ float *CUDASoftmaxFunc(float *x, int64_t *dimIn, float *y, int64_t * /*dimOut*/,
   int64_t outer = 1, inner = 1;
   for (int64_t i = 0; i < axis; ++i) outer *= dimIn[i];
   for (int64_t i = axis + 1; i < rank; ++i) inner *= dimIn[i];
+  Entry e = trace_entry(S_SOFTMAX);
+  te_ptr(e, x); te_ptr(e, y); te_dims(e, dimIn, (int)rank); te_i(e, axis);
+  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = prod(dimIn, rank) * 4;
+  step(e, false);
   ensure_f32(x);
   launch_softmax_f32(x, y, outer, dimIn[axis], inner, r.stream);
   mark_f32(y);
   return y;
 }
 
-float *CUDAFlattenFunc(float *x, int64_t *dimIn, float *y, int64_t * /*dimOut*/, int32_t /*axis*/,
-                       int64_t rank) {
+static float *copy_common(int sym, float *x, int64_t *dimIn, int64_t rank, float *y) {
   Runtime &r = rt();
   const int64_t n = prod(dimIn, rank);
+  Entry e = trace_entry(sym);
+  te_ptr(e, x); te_ptr(e, y); te_dims(e, dimIn, (int)rank);
+  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = n * 4;
+  step(e, false);
   ensure_f32(x);
   OCC_CUDA(cudaMemcpyAsync(y, x, (size_t)n * 4, cudaMemcpyDeviceToDevice, r.stream));
   mark_f32(y);
   return y;
 }
 
+float *CUDAFlattenFunc(float *x, int64_t *dimIn, float *y, int64_t * /*dimOut*/, int32_t /*axis*/,
+                       int64_t rank) {
+  return copy_common(S_FLATTEN, x, dimIn, rank, y);
+}
+
 float *CUDAReshapeFunc(float *x, int64_t *dimIn, int64_t rank, float *y) {
-  Runtime &r = rt();
-  const int64_t n = prod(dimIn, rank);
-  ensure_f32(x);
-  OCC_CUDA(cudaMemcpyAsync(y, x, (size_t)n * 4, cudaMemcpyDeviceToDevice, r.stream));
-  mark_f32(y);
-  return y;
+  return copy_common(S_RESHAPE, x, dimIn, rank, y);
+}
+
+// Called by the entry points outside this file: they take part in no chain and their
+// reads are not tracked, so they end the speculation for this inference.
+void occamy_internal_opaque_call(void) {
+  Entry e = trace_entry(S_OPAQUE);
+  step(e, false);
 }
 
 // ---------------------------------------------------------------- controls
@@ -614,6 +954,7 @@ int occamy_last_error(int clear) {
 
 int occamy_synchronize(void) {
   Runtime &r = rt();
+  flush_pending();
   cudaError_t e = cudaStreamSynchronize(r.stream);
   if (e != cudaSuccess) set_error((int)e, "synchronize");
   if (r.dev_err && r.host_err) {
@@ -633,6 +974,8 @@ void occamy_get_counters(int64_t out[8]) {
   for (int i = 0; i < 8; ++i) out[i] = r.counters[i];
 }
 
+int64_t occamy_fused_chains(void) { return trace_fused_chains(); }
+
 void occamy_profile_begin(void) {
   Runtime &r = rt();
   r.prof_count = 0;
@@ -641,6 +984,7 @@ void occamy_profile_begin(void) {
 
 int occamy_profile_end(float *ms, int cap) {
   Runtime &r = rt();
+  flush_pending();
   r.profiling = false;
   OCC_CUDA(cudaStreamSynchronize(r.stream));
   const int n = r.prof_count;
@@ -653,8 +997,14 @@ int occamy_profile_end(float *ms, int cap) {
   return n;
 }
 
+void occamy_set_cross_call_fusion(int on) {
+  flush_pending();
+  trace_set_enabled(on != 0);
+}
+
 void occamy_clear_weight_cache(void) {
   Runtime &r = rt();
+  flush_pending();
   OCC_CUDA(cudaStreamSynchronize(r.stream));
   for (auto &kv : r.wcache)
     if (kv.second.dev) cudaFree(kv.second.dev);

@@ -9,6 +9,8 @@
 
 using namespace occ;
 
+extern "C" void occamy_internal_opaque_call(void);
+
 namespace {
 
 inline int64_t prod(const int64_t *d, int64_t rank) {
@@ -45,6 +47,7 @@ __global__ void unary_kernel(const float *x, float *y, int64_t n, int op, float 
 
 float *unary(float *in, float *out, const int64_t *dim, int64_t rank, int op, float a,
              const float *dev_scalar) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   const int64_t n = prod(dim, rank);
   ensure_f32(in);
@@ -84,6 +87,7 @@ __global__ void permute_kernel(const T *x, T *y, PermShape ps, int64_t n) {
 
 template <typename T>
 T *transpose(T *in, const int64_t *dimIn, T *out, const int64_t *perm, int64_t rank) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   if (rank > 8) {
     set_error(994, "transpose: rank > 8");
@@ -121,6 +125,7 @@ __global__ void concat_copy_kernel(const T *x, T *y, int64_t inner_in, int64_t i
 template <typename T>
 T *concat(T **inList, int64_t **dimInList, T *out, const int64_t *dimOut, int64_t axis,
           int64_t inputNum, int32_t rank) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   if (axis < 0) axis += rank;
   int64_t inner_out = 1;
@@ -159,6 +164,7 @@ __global__ void gather_kernel(const T *x, const int64_t *idx, T *y, int64_t axis
 template <typename T>
 T *gather(T *in, const int64_t *dimIn, int64_t inRank, T *out, int64_t *indices,
           const int64_t *dimIdx, int64_t idxRank, int64_t axis) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   if (axis < 0) axis += inRank;
   int64_t outer = 1, inner = 1;
@@ -206,6 +212,7 @@ __global__ void nonzero_kernel(const T *x, T *y, int64_t n) {
 
 template <typename T>
 T *nonzero(T *in, const int64_t *dimIn, T *out, int64_t rank) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   const int64_t n = prod(dimIn, rank);
   ensure_f32(in);
@@ -219,6 +226,7 @@ T *nonzero(T *in, const int64_t *dimIn, T *out, int64_t rank) {
 
 template <typename T>
 T *plain_copy(T *in, const int64_t *dimIn, int64_t rank, T *out) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   const int64_t n = prod(dimIn, rank);
   ensure_f32(in);
@@ -247,6 +255,7 @@ __global__ void matmul_nd_kernel(const float *A, const float *B, float *out, int
 extern "C" {
 
 int64_t *CUDACastI64toFloatFunc(int64_t *in, float *out, int64_t *dimOut, int64_t rank) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   const int64_t n = prod(dimOut, rank);
   ensure_f32(in);
@@ -304,6 +313,7 @@ int64_t *CUDAGatherInt64Func(int64_t *in, int64_t *dimIn, int64_t inRank, int64_
 
 float *CUDAMatmulNdFunc(float *A, int64_t *dimA, int32_t rankA, float *B, int64_t *dimB,
                         int32_t rankB, float *out, int64_t *dimOut, int32_t rankOut) {
+  occamy_internal_opaque_call();
   Runtime &r = rt();
   if (rankA < 2 || rankB < 2) {
     set_error(993, "matmulNd: rank < 2");

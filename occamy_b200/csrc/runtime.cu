@@ -135,7 +135,15 @@ void ensure_f32(const void *p) {
   TensorRec *rec = reg_find(p, &base);
   if (!rec || rec->fmt == FMT_F32) return;
   Runtime &r = rt();
-  if (rec->fmt == FMT_ZERO) {
+  if (rec->fmt != FMT_ELIDED && r.before_write) {
+    const Fmt keep = rec->fmt;
+    r.before_write((const void *)base, rec->bytes);
+    rec = reg_find(p, &base);          // the hook may have launched work that re-tags tensors
+    if (!rec || rec->fmt != keep) return ensure_f32(p);
+  }
+  if (rec->fmt == FMT_ELIDED) {
+    set_error(990, "read of a tensor that cross-call fusion skipped (set OCCAMY_FUSE_ACROSS_CALLS=0)");
+  } else if (rec->fmt == FMT_ZERO) {
     OCC_CUDA(cudaMemsetAsync((void *)base, 0, rec->bytes, r.stream));
   } else if (rec->fmt == FMT_PENDING) {
     OCC_CUDA(cudaMemcpyAsync((void *)base, rec->host_src, rec->host_bytes, cudaMemcpyHostToDevice,

@@ -22,7 +22,8 @@ enum Fmt {
   FMT_F32 = 0,        // what the ABI says: dense fp32, NCHW
   FMT_ZERO = 1,       // freshly handed out; reads as zero, memset not yet issued
   FMT_BF16_NHWC = 2,  // produced by a tensor-core-mode kernel: bf16, NHWC, dims below
-  FMT_PENDING = 3     // host->device upload deferred (constant already packed on device)
+  FMT_PENDING = 3,    // host->device upload deferred (constant already packed on device)
+  FMT_ELIDED = 4      // never written: a cross-call fusion skipped it (reading it is an error)
 };
 
 struct TensorRec {
@@ -77,12 +78,15 @@ struct Runtime {
   std::unordered_map<WeightKey, PackedWeight, WeightKeyHash> wcache;
   // host sources whose packed form is resident: source -> (bytes, fingerprint)
   std::unordered_map<const void *, std::pair<size_t, uint64_t>> resident;
-  void *scratch[4] = {nullptr, nullptr, nullptr, nullptr};
-  size_t scratch_bytes[4] = {0, 0, 0, 0};
+  void *scratch[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t scratch_bytes[6] = {0, 0, 0, 0, 0, 0};
   int *dev_err = nullptr;   // device word the kernels' bounded waits report into
   int *host_err = nullptr;  // pinned mirror
   bool log = false;
   bool cache_weights = true;
+  // called before the runtime itself writes into a caller-owned range (lazy zero fill,
+  // deferred upload, layout conversion), so that a held-back kernel can read it first
+  void (*before_write)(const void *p, size_t bytes) = nullptr;
   // optional CUDA-event pair around every tensor-core launch (occamy_profile_begin/end)
   bool profiling = false;
   int prof_count = 0;

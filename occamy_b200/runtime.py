@@ -81,6 +81,8 @@ _SIGNATURES = {
     "occamy_stream": (C.c_void_p, []),
     "occamy_get_counters": (None, [_i64p]),
     "occamy_clear_weight_cache": (None, []),
+    "occamy_fused_chains": (C.c_int64, []),
+    "occamy_set_cross_call_fusion": (None, [C.c_int]),
     "occamy_profile_begin": (None, []),
     "occamy_profile_end": (C.c_int, [C.POINTER(C.c_float), C.c_int]),
 }
