@@ -22,17 +22,40 @@ struct PoolRec {
   size_t bytes;
 };
 std::vector<PoolRec> g_pools;
-// The pool of the previous inference, kept so that the next wrapDNNMemPoolInit of the same
-// size costs no cudaMalloc / cudaFree (a compiled model creates and frees its pool on
-// every call).  OCCAMY_POOL_CACHE=0 turns this off.
-PoolRec g_pool_cache = {nullptr, 0};
-bool pool_cache_enabled() {
+// Pool blocks of finished inferences, kept so that the next wrapDNNMemPoolInit of the same
+// size costs no cudaMalloc / cudaFree (a compiled model creates and frees its pool on every
+// call).  Up to OCCAMY_POOL_BLOCKS (default 2, 0 = off) blocks of one size are kept and
+// handed out in turn: consecutive inferences then live in different blocks, and the input
+// upload of the next one can run on the copy stream while the kernels of the current one
+// are still executing.
+struct CachedPool {
+  void *base;
+  size_t bytes;
+  cudaEvent_t done;   // recorded on the launch stream when the block's last user finished
+};
+std::vector<CachedPool> g_pool_cache;   // oldest first
+cudaEvent_t g_block_ready = nullptr;    // `done` of the block the current inference lives in
+void *g_cur_pool = nullptr;
+size_t g_cur_pool_bytes = 0;
+cudaStream_t g_copy_stream = nullptr;
+int64_t g_launches_at_pool_init = 0;   // kernel + copy count when the current pool was set up
+
+int pool_cache_blocks() {
   static int v = -1;
   if (v < 0) {
-    const char *e = getenv("OCCAMY_POOL_CACHE");
-    v = (e && !strcmp(e, "0")) ? 0 : 1;
+    const char *e = getenv("OCCAMY_POOL_BLOCKS");
+    if (!e) e = getenv("OCCAMY_POOL_CACHE");
+    v = e ? atoi(e) : 2;
+    if (v < 0) v = 0;
+    if (v > 4) v = 4;
   }
-  return v == 1;
+  return v;
+}
+
+void free_cached_pool(CachedPool &c) {
+  OCC_CUDA(cudaEventSynchronize(c.done));
+  OCC_CUDA(cudaFree(c.base));
+  OCC_CUDA(cudaEventDestroy(c.done));
 }
 
 void die(const char *what, cudaError_t e, size_t size) {
@@ -415,18 +438,42 @@ cudaError_t wrapDNNMalloc(void **devPtr, size_t size) {
 
 cudaError_t wrapDNNMemPoolInit(void **devPtr, size_t size) {
   Runtime &r = rt();
-  if (g_pool_cache.base && g_pool_cache.bytes == size) {
-    *devPtr = g_pool_cache.base;
-    g_pool_cache.base = nullptr;
+  *devPtr = nullptr;
+  cudaEvent_t ready = nullptr;
+  int same = 0;
+  for (const CachedPool &c : g_pool_cache) same += c.bytes == size;
+  if (same >= pool_cache_blocks() && same > 0) {
+    for (size_t i = 0; i < g_pool_cache.size(); ++i)   // the oldest block of this size
+      if (g_pool_cache[i].bytes == size) {
+        *devPtr = g_pool_cache[i].base;
+        ready = g_pool_cache[i].done;
+        g_pool_cache.erase(g_pool_cache.begin() + i);
+        break;
+      }
   } else {
-    if (g_pool_cache.base) {
-      OCC_CUDA(cudaStreamSynchronize(r.stream));
-      OCC_CUDA(cudaFree(g_pool_cache.base));
-      g_pool_cache.base = nullptr;
-    }
+    // blocks of other sizes make room first
+    for (size_t i = 0; i < g_pool_cache.size();)
+      if (g_pool_cache[i].bytes != size) {
+        free_cached_pool(g_pool_cache[i]);
+        g_pool_cache.erase(g_pool_cache.begin() + i);
+      } else {
+        ++i;
+      }
     cudaError_t err = cudaMalloc(devPtr, size ? size : 1);
-    if (err != cudaSuccess) die("MemPoolInit", err, size);
+    if (err != cudaSuccess && !g_pool_cache.empty()) {   // no room for a second block
+      cudaGetLastError();
+      *devPtr = g_pool_cache[0].base;
+      ready = g_pool_cache[0].done;
+      g_pool_cache.erase(g_pool_cache.begin());
+    } else if (err != cudaSuccess) {
+      die("MemPoolInit", err, size);
+    }
   }
+  if (g_block_ready) OCC_CUDA(cudaEventDestroy(g_block_ready));
+  g_block_ready = ready;
+  g_cur_pool = *devPtr;
+  g_cur_pool_bytes = size;
+  g_launches_at_pool_init = r.counters[CNT_LAUNCHES] + r.main_copies;
   g_pools.push_back(PoolRec{*devPtr, size});
   if ((int64_t)size > r.counters[CNT_POOL_HWM]) r.counters[CNT_POOL_HWM] = (int64_t)size;
   trace_set_pool(*devPtr, size);
@@ -490,8 +537,36 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
       }
     }
     if (kind == 1) pending_guard_range(dst, count_, true);
-    err = cudaMemcpyAsync(dst, src, count_,
-                          kind == 1 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice, r.stream);
+    const bool in_pool = g_cur_pool && (uintptr_t)dst >= (uintptr_t)g_cur_pool &&
+                         (uintptr_t)dst + count_ <= (uintptr_t)g_cur_pool + g_cur_pool_bytes;
+    if (kind == 1 && whole && in_pool && count_ >= (1u << 20) && pool_cache_blocks() >= 2) {
+      // Large upload into a fresh tensor of this inference's pool block: nothing enqueued
+      // for this inference touches these bytes yet, and the block's previous user is done
+      // once `g_block_ready` has fired, so the copy need not queue behind the kernels of
+      // the previous inference.  Later work on the launch stream waits for it.
+      if (!g_copy_stream) OCC_CUDA(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking));
+      if (g_block_ready) OCC_CUDA(cudaStreamWaitEvent(g_copy_stream, g_block_ready, 0));
+      if (r.counters[CNT_LAUNCHES] + r.main_copies != g_launches_at_pool_init) {
+        // work of this inference is already queued and may still read bytes that the pool
+        // plan has recycled for this tensor: the copy goes behind it
+        cudaEvent_t before;
+        OCC_CUDA(cudaEventCreateWithFlags(&before, cudaEventDisableTiming));
+        OCC_CUDA(cudaEventRecord(before, r.stream));
+        OCC_CUDA(cudaStreamWaitEvent(g_copy_stream, before, 0));
+        OCC_CUDA(cudaEventDestroy(before));
+      }
+      err = cudaMemcpyAsync(dst, src, count_, cudaMemcpyHostToDevice, g_copy_stream);
+      cudaEvent_t ev;
+      OCC_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+      OCC_CUDA(cudaEventRecord(ev, g_copy_stream));
+      OCC_CUDA(cudaStreamWaitEvent(r.stream, ev, 0));
+      OCC_CUDA(cudaEventDestroy(ev));
+    } else {
+      err = cudaMemcpyAsync(dst, src, count_,
+                            kind == 1 ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
+                            r.stream);
+      r.main_copies++;
+    }
     if (kind == 1) count(CNT_H2D_BYTES, (int64_t)count_);
     if (rec && whole) {
       rec->fmt = FMT_F32;
@@ -556,15 +631,23 @@ cudaError_t wrapDNNDealloc(void *devPtr) {
     Entry e = trace_entry(S_POOLFREE);
     step(e, false);   // runs whatever is still held back
     trace_set_pool(nullptr, 0);
-    if (pool_cache_enabled()) {
+    if (devPtr == g_cur_pool) {
+      g_cur_pool = nullptr;
+      g_cur_pool_bytes = 0;
+    }
+    if (pool_cache_blocks() > 0) {
       // Work still in flight on the launch stream is ordered before anything a later
-      // inference enqueues, so the block can be handed out again without waiting.
+      // inference enqueues there, so the block can be handed out again without waiting;
+      // the event lets the copy stream know when its bytes are really free.
       if (bytes) reg_drop_range(devPtr, bytes);
-      if (g_pool_cache.base) {
-        OCC_CUDA(cudaStreamSynchronize(r.stream));
-        OCC_CUDA(cudaFree(g_pool_cache.base));
+      CachedPool c{devPtr, bytes, nullptr};
+      OCC_CUDA(cudaEventCreateWithFlags(&c.done, cudaEventDisableTiming));
+      OCC_CUDA(cudaEventRecord(c.done, r.stream));
+      g_pool_cache.push_back(c);
+      while ((int)g_pool_cache.size() > pool_cache_blocks()) {
+        free_cached_pool(g_pool_cache[0]);
+        g_pool_cache.erase(g_pool_cache.begin());
       }
-      g_pool_cache = PoolRec{devPtr, bytes};
       return cudaSuccess;
     }
   } else {

@@ -32,7 +32,9 @@
 
 namespace occ {
 
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;      // 1 producer warp + 1 MMA warp + 8 epilogue warps
+constexpr int TC_EPI_THREADS = 256;
+constexpr int TC_DBUF = 3;           // output slab buffers in shared memory
 constexpr int TC_MAX_TAPS = 32;
 constexpr int TC_SMEM_LIMIT = 232448;  // 227 KB
 
@@ -51,13 +53,12 @@ struct alignas(64) TcParams {
   int tw, th, tn, K;
   const float *bias;
   int has_res, act;
+  int gq, gp, gn;        // extents of the output grid the tiles are cut from
   float lo, hi;
   float *out_f32;
   int ldo;
   int m_total;
   int *err;
-  int dbg;
-  long long *dbg_out;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -167,10 +168,25 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+template <int W>
+__device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t *r) {
+  if constexpr (W == 32) tc_ld32(taddr, r);
+  else tc_ld16(taddr, r);
+}
 __device__ __forceinline__ void tc_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Shared-memory matrix descriptor for a K-major bf16 tile whose rows are `bk` elements
 // (32 / 64 / 128 bytes, swizzled with the matching 32B / 64B / 128B pattern): 8-row groups
@@ -200,6 +216,7 @@ __device__ __forceinline__ uint32_t slab_off(int row, int chunk, int row_bytes) 
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_constant__ TcParams p) {
   constexpr int DC = BN < 64 ? BN : 64;        // channels per staged output slab
+  constexpr int CW = DC / 2;                   // channels one epilogue thread handles per slab
   constexpr int NSLAB = BN / DC;
   constexpr int SLAB_BYTES = 128 * DC * 2;
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
@@ -213,9 +230,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
   const uint32_t a_bytes = 128u * bk * 2u, b_bytes = (uint32_t)BN * bk * 2u;
   const uint32_t sA = base;
   const uint32_t sB = sA + stages * a_bytes;
-  const uint32_t sD = sB + stages * b_bytes;           // 2 slabs
-  const uint32_t sR = sD + 2 * SLAB_BYTES;             // 2 slabs (only if has_res)
-  const uint32_t sMisc = sR + (p.has_res ? 2 * SLAB_BYTES : 0);
+  const uint32_t sD = sB + stages * b_bytes;                    // TC_DBUF output slabs
+  const uint32_t sMisc = sD + TC_DBUF * SLAB_BYTES;
   uint8_t *misc_ptr = base_ptr + (sMisc - base);
   float *bias_s = reinterpret_cast<float *>(misc_ptr);                  // BN floats
   uint64_t *bars = reinterpret_cast<uint64_t *>(misc_ptr + BN * 4);     // barriers
@@ -226,8 +242,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
   auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * stages + 2 + s); };
   auto rfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + 4 + s); };
   volatile uint32_t *tmem_holder =
-      reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 6);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 7);
+      reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 4 + TC_DBUF);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 5 + TC_DBUF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -238,9 +254,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), 128);
-      mbar_init(rfull_bar(s), 1);
+      mbar_init(tempty_bar(s), TC_EPI_THREADS);
     }
+    for (int s = 0; s < TC_DBUF; ++s) mbar_init(rfull_bar(s), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -259,8 +275,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
   const int rows_valid = p.tw * p.th * p.tn;
   const int ksteps = p.num_taps * p.cblocks;
   int err_code = 0;
-  long long dbg_t0 = 0, dbg_t1 = 0;
-  const long long dbg_start = clock64();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -279,12 +293,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
         for (int t = 0; t < p.num_taps && !err_code; ++t) {
           const TcTap tap = p.taps[t];
           for (int cb = 0; cb < p.cblocks; ++cb) {
-            long long tw0 = clock64();
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
               err_code = 1;
               break;
             }
-            dbg_t0 += clock64() - tw0;
             mbar_expect_tx(full_bar(stage), tx_bytes);
             tma_load_4d(sA + stage * a_bytes, &p.tmA[tap.map], full_bar(stage), cb * bk,
                         q0 + tap.dw, p0 + tap.dh, n0);
@@ -303,22 +315,18 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-        long long tw0 = clock64();
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           err_code = 2;
           break;
         }
-        dbg_t0 += clock64() - tw0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         uint32_t accumulate = 0;
         for (int ks = 0; ks < ksteps; ++ks) {
-          long long tw1 = clock64();
           if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
             err_code = 3;
             break;
           }
-          dbg_t1 += clock64() - tw1;
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
           const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
@@ -340,138 +348,148 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (128 threads)
+    // ------------------------------------------------------------ epilogue (8 warps)
+    // Two warps share each TMEM lane quadrant and split a slab's channels between them.
     const float act_lo = p.lo, act_hi = p.hi;
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;        // which half of the slab's channels
     const int row = quad * 32 + lane;        // accumulator row == pixel index in the tile
-    const int et = threadIdx.x - 64;         // 0..127
+    const int et = threadIdx.x - 64;         // 0..255
     const bool leader = et == 0;
     int acc = 0;
     uint32_t acc_phase = 0;
-    uint32_t d_iter = 0, r_iter = 0;
+    uint32_t d_iter = 0;
+    // Residual slabs are TMA-loaded into the output slab buffers ahead of time (the
+    // epilogue then adds in place).  `pf_*` walks the same (tile, slab) sequence as the
+    // main loop, up to TC_DBUF - 1 slabs ahead; only the leader uses it.
+    uint32_t r_issued = 0;
+    int pf_tile = blockIdx.x, pf_sl = 0;
+    auto prefetch_residual = [&](uint32_t upto) {
+      while (r_issued <= upto && pf_tile < p.total_tiles) {
+        const int kt = pf_tile % p.tiles_k;
+        int sp = pf_tile / p.tiles_k;
+        const int q0 = (sp % p.tiles_w) * p.tw;
+        sp /= p.tiles_w;
+        const int p0 = (sp % p.tiles_h) * p.th;
+        const int n0 = (sp / p.tiles_h) * p.tn;
+        const int k0 = kt * BN;
+        const int ns = min(NSLAB, (p.K - k0 + DC - 1) / DC);
+        const uint32_t b = r_issued % TC_DBUF;
+        mbar_expect_tx(rfull_bar(b), (uint32_t)rows_valid * DC * 2u);
+        tma_load_4d(sD + b * SLAB_BYTES, &p.tmR, rfull_bar(b), k0 + pf_sl * DC, q0, p0, n0);
+        ++r_issued;
+        if (++pf_sl == ns) {
+          pf_sl = 0;
+          pf_tile += gridDim.x;
+        }
+      }
+    };
+    if (p.has_res && leader) prefetch_residual(TC_DBUF - 1);
     for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
       const int kt = tile % p.tiles_k;
       int sp = tile / p.tiles_k;
-      const int wt = sp % p.tiles_w;
-      const int q0 = wt * p.tw;
+      const int q0 = (sp % p.tiles_w) * p.tw;
       sp /= p.tiles_w;
       const int p0 = (sp % p.tiles_h) * p.th;
       const int n0 = (sp / p.tiles_h) * p.tn;
       const int k0 = kt * BN;
       const int nslab = min(NSLAB, (p.K - k0 + DC - 1) / DC);
-      if (p.has_res && leader) {
-        mbar_expect_tx(rfull_bar(r_iter & 1), (uint32_t)rows_valid * DC * 2u);
-        tma_load_4d(sR + (r_iter & 1) * SLAB_BYTES, &p.tmR, rfull_bar(r_iter & 1), k0, q0, p0, n0);
-      }
-      for (int i = et; i < BN; i += 128)
+      for (int i = et; i < BN; i += TC_EPI_THREADS)
         bias_s[i] = (p.bias && k0 + i < p.K) ? p.bias[k0 + i] : 0.0f;
       epi_bar();
-      long long tw0 = clock64();
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
         err_code = 4;
         break;
       }
-      dbg_t0 += clock64() - tw0;
       tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-      for (int sl = 0; sl < nslab; ++sl) {
-        uint32_t dbuf = 0;
-        if (!p.out_f32) {
-          dbuf = sD + (d_iter & 1) * SLAB_BYTES;
-          if (leader && !(p.dbg & 8)) tma_store_wait_read<1>();
-          epi_bar();  // slab buffer (d_iter & 1) is free; residual slab (r_iter+1)&1 is free
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) +
+                             (uint32_t)(acc * BN + half * CW);
+      uint32_t rr[2][CW];
+      tc_ld<CW>(t_row, rr[0]);
+#pragma unroll
+      for (int sl = 0; sl < NSLAB; ++sl) {
+        if (sl >= nslab) break;
+        tc_ld_wait();
+        if (sl + 1 < nslab) {
+          tc_ld<CW>(t_row + (uint32_t)((sl + 1) * DC), rr[(sl + 1) & 1]);
+        } else {
+          // every TMEM read of this tile has landed: the MMA warp may overwrite the buffer
+          tc_fence_before();
+          mbar_arrive(tempty_bar(acc));
         }
+        const uint32_t *r = rr[sl & 1];
+        const int cbase = sl * DC + half * CW;   // first of this thread's channels in the tile
+        float v[CW];
+#pragma unroll
+        for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]) + bias_s[cbase + j];
+        const uint32_t dbuf = sD + (d_iter % TC_DBUF) * SLAB_BYTES;
+        uint8_t *dptr = base_ptr + (dbuf - base);
         if (p.has_res) {
-          if (leader && sl + 1 < nslab) {
-            mbar_expect_tx(rfull_bar((r_iter + 1) & 1), (uint32_t)rows_valid * DC * 2u);
-            tma_load_4d(sR + ((r_iter + 1) & 1) * SLAB_BYTES, &p.tmR, rfull_bar((r_iter + 1) & 1),
-                        k0 + (sl + 1) * DC, q0, p0, n0);
-          }
-          if (!mbar_wait(rfull_bar(r_iter & 1), (r_iter >> 1) & 1u, abort_flag)) {
+          if (!mbar_wait(rfull_bar(d_iter % TC_DBUF), (d_iter / TC_DBUF) & 1u, abort_flag)) {
             err_code = 5;
             break;
           }
-        }
-        const uint8_t *rbuf = base_ptr + (sR + (r_iter & 1) * SLAB_BYTES - base);
-        uint8_t *dptr = base_ptr + (dbuf - base);
 #pragma unroll
-        for (int h = 0; h < DC / 32; ++h) {
-          uint32_t r[32];
-          if (!(p.dbg & 4)) {
-            tc_ld32(t_row + (uint32_t)(sl * DC + h * 32), r);
-            tc_ld_wait();
-          } else {
-            for (int j = 0; j < 32; ++j) r[j] = 0;
-          }
-          float v[32];
+          for (int c4 = 0; c4 < CW / 8; ++c4) {
+            const uint4 rv = *reinterpret_cast<const uint4 *>(
+                dptr + slab_off(row, half * (CW / 8) + c4, DC * 2));
+            const uint32_t w4[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) + bias_s[sl * DC + h * 32 + j];
-          if (p.has_res) {
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              const uint4 rv = *reinterpret_cast<const uint4 *>(
-                  rbuf + slab_off(row, h * 4 + c4, DC * 2));
-              const uint32_t w4[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f =
-                    __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w4[e]));
-                v[c4 * 8 + e * 2] += f.x;
-                v[c4 * 8 + e * 2 + 1] += f.y;
-              }
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = tc_act(v[j], act_lo, act_hi);
-          if (p.out_f32) {
-            const int m = q0 + row;
-            if (row < rows_valid && m < p.m_total) {
-              float *o = p.out_f32 + (int64_t)m * p.ldo + k0 + sl * DC + h * 32;
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (k0 + sl * DC + h * 32 + j < p.K) o[j] = v[j];
-            }
-          } else {
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              uint4 pk;
-              __nv_bfloat162 b0 = __floats2bfloat162_rn(v[c4 * 8 + 0], v[c4 * 8 + 1]);
-              __nv_bfloat162 b1 = __floats2bfloat162_rn(v[c4 * 8 + 2], v[c4 * 8 + 3]);
-              __nv_bfloat162 b2 = __floats2bfloat162_rn(v[c4 * 8 + 4], v[c4 * 8 + 5]);
-              __nv_bfloat162 b3 = __floats2bfloat162_rn(v[c4 * 8 + 6], v[c4 * 8 + 7]);
-              pk.x = *reinterpret_cast<uint32_t *>(&b0);
-              pk.y = *reinterpret_cast<uint32_t *>(&b1);
-              pk.z = *reinterpret_cast<uint32_t *>(&b2);
-              pk.w = *reinterpret_cast<uint32_t *>(&b3);
-              if (!(p.dbg & 2)) *reinterpret_cast<uint4 *>(dptr + slab_off(row, h * 4 + c4, DC * 2)) = pk;
+            for (int e = 0; e < 4; ++e) {
+              const float2 f =
+                  __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w4[e]));
+              v[c4 * 8 + e * 2] += f.x;
+              v[c4 * 8 + e * 2 + 1] += f.y;
             }
           }
         }
-        if (p.has_res) ++r_iter;
-        if (!p.out_f32) {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) v[j] = tc_act(v[j], act_lo, act_hi);
+        if (p.out_f32) {
+          const int m = q0 + row;
+          if (row < rows_valid && m < p.m_total) {
+            float *o = p.out_f32 + (int64_t)m * p.ldo + k0 + cbase;
+#pragma unroll
+            for (int j = 0; j < CW; ++j)
+              if (k0 + cbase + j < p.K) o[j] = v[j];
+          }
+        } else {
+          // Slab buffer d_iter % TC_DBUF is free: its previous store (d_iter - TC_DBUF) was
+          // waited for by the leader before it arrived at the barrier of slab d_iter - 1.
+#pragma unroll
+          for (int c4 = 0; c4 < CW / 8; ++c4) {
+            uint4 pk;
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(v[c4 * 8 + 0], v[c4 * 8 + 1]);
+            __nv_bfloat162 b1 = __floats2bfloat162_rn(v[c4 * 8 + 2], v[c4 * 8 + 3]);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(v[c4 * 8 + 4], v[c4 * 8 + 5]);
+            __nv_bfloat162 b3 = __floats2bfloat162_rn(v[c4 * 8 + 6], v[c4 * 8 + 7]);
+            pk.x = *reinterpret_cast<uint32_t *>(&b0);
+            pk.y = *reinterpret_cast<uint32_t *>(&b1);
+            pk.z = *reinterpret_cast<uint32_t *>(&b2);
+            pk.w = *reinterpret_cast<uint32_t *>(&b3);
+            *reinterpret_cast<uint4 *>(dptr + slab_off(row, half * (CW / 8) + c4, DC * 2)) = pk;
+          }
           fence_async_smem();
           epi_bar();
-          if (leader && !(p.dbg & 1)) {
+          if (leader) {
             tma_store_4d(&p.tmD, dbuf, k0 + sl * DC, q0, p0, n0);
             tma_store_commit();
+            tma_store_wait_read<TC_DBUF - 2>();
+            // the buffer of slab d_iter - 1 has been read out: the residual of slab
+            // d_iter + TC_DBUF - 1 may land there
+            if (p.has_res) prefetch_residual(d_iter + TC_DBUF - 1);
           }
           ++d_iter;
         }
       }
       if (err_code) break;
-      tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
+      if (p.out_f32) epi_bar();   // bias_s is rewritten at the top of the next tile
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
     if (leader) tma_store_wait_read<0>();
   }
 
-  if (p.dbg_out && blockIdx.x == 0 && lane == 0 && warp <= 2) {
-    p.dbg_out[warp * 4 + 0] = dbg_t0;
-    p.dbg_out[warp * 4 + 1] = dbg_t1;
-    p.dbg_out[warp * 4 + 2] = clock64() - dbg_start;
-  }
   if (err_code) {
     atomicExch(p.err, 1000 + err_code);
     *abort_flag = 1;
@@ -621,12 +639,6 @@ static Plan build_plan(const TcConvArgs &a) {
   p.out_f32 = a.out_f32;
   p.ldo = a.ldo;
   p.err = rt().dev_err;
-  { const char *d = getenv("OCCAMY_TC_DBG"); p.dbg = d ? atoi(d) : 0; }
-  {
-    static long long *dbg_buf = nullptr;
-    if (!dbg_buf && getenv("OCCAMY_TC_DBG")) cudaMallocManaged(&dbg_buf, 16 * sizeof(long long));
-    p.dbg_out = dbg_buf;
-  }
   const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
                     a.pad_w == 0;
   // output grid the tiles are cut from
@@ -637,6 +649,9 @@ static Plan build_plan(const TcConvArgs &a) {
     Ng = 1;
   }
   p.m_total = Qg;
+  p.gq = Qg;
+  p.gp = Pg;
+  p.gn = Ng;
   choose_box(Qg, Pg, Ng, &p.tw, &p.th, &p.tn);
   p.tiles_w = (Qg + p.tw - 1) / p.tw;
   p.tiles_h = (Pg + p.th - 1) / p.th;
@@ -692,7 +707,7 @@ static Plan build_plan(const TcConvArgs &a) {
   }
   // shared memory: ring + output slabs (+ residual slabs) + bias + barriers + alignment
   const size_t stage_bytes = 128 * bk * 2 + (size_t)bn * bk * 2;
-  const size_t fixed = 1024 + 2 * 128 * dc * 2 * (a.residual ? 2 : 1) + bn * 4 + 8 * 80;
+  const size_t fixed = 1024 + (size_t)TC_DBUF * 128 * dc * 2 + bn * 4 + 8 * 80;
   int stages = (int)((TC_SMEM_LIMIT - fixed) / stage_bytes);
   if (stages > 8) stages = 8;
   if (stages < 2) ok = false;
@@ -749,13 +764,6 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
     default: launch_plan<256>(pl, s); break;
   }
   if (prof_slot >= 0) OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot + 1], s));
-  if (pl.p.dbg_out && getenv("OCCAMY_TC_DBG_PRINT")) {
-    cudaStreamSynchronize(s);
-    const long long *d = pl.p.dbg_out;
-    fprintf(stderr, "[tcdbg] tiles/cta %d ksteps %d stages %d | producer wait_empty %lld total %lld | mma wait_tempty %lld wait_full %lld total %lld | epi wait_tfull %lld total %lld\n",
-            (pl.p.total_tiles + rt().num_sms - 1) / rt().num_sms, pl.p.num_taps * pl.p.cblocks, pl.p.stages,
-            d[0], d[2], d[4], d[5], d[6], d[8], d[10]);
-  }
   OCC_CUDA(cudaGetLastError());
   count(CNT_LAUNCHES);
   count(CNT_TC_LAUNCHES);

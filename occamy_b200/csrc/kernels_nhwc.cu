@@ -18,7 +18,7 @@ __device__ __forceinline__ float act_apply_b(float v, int act, float lo, float h
 
 static inline int grid_for(int64_t n, int threads) {
   int64_t b = (n + threads - 1) / threads;
-  const int64_t cap = (int64_t)rt().num_sms * 32;
+  const int64_t cap = (int64_t)rt().num_sms * 64;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return (int)b;
@@ -147,11 +147,15 @@ void launch_add_act_bf16(const bf16 *a, const bf16 *b, const float *bias_c, int 
 }
 
 // ---------------------------------------------------------------------------
-// Pooling on NHWC: one thread per (n, p, q, 8 channels).
+// Pooling on NHWC: one thread per (n, p, q, 8 channels); consecutive threads take
+// consecutive channel groups, so every access of a warp is one contiguous run.
 // ---------------------------------------------------------------------------
-__global__ void pool_bf16_kernel(const bf16x8 *__restrict__ x, bf16x8 *__restrict__ y, int C8,
-                                 int H, int W, int P, int Q, int kh, int kw, int pad_h, int pad_w,
-                                 int sh, int sw, bool avg, int64_t total) {
+template <bool AVG>
+__global__ void __launch_bounds__(256) pool_bf16_kernel(const bf16x8 *__restrict__ x,
+                                                        bf16x8 *__restrict__ y, int C8, int H,
+                                                        int W, int P, int Q, int kh, int kw,
+                                                        int pad_h, int pad_w, int sh, int sw,
+                                                        int64_t total) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int c8 = (int)(i % C8);
@@ -160,30 +164,35 @@ __global__ void pool_bf16_kernel(const bf16x8 *__restrict__ x, bf16x8 *__restric
     rest /= Q;
     const int p = (int)(rest % P);
     const int64_t n = rest / P;
-    float m[8], sum[8];
+    const int h0 = max(p * sh - pad_h, 0), h1 = min(p * sh - pad_h + kh, H);
+    const int w0 = max(q * sw - pad_w, 0), w1 = min(q * sw - pad_w + kw, W);
+    if (AVG) {
+      float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int h = h0; h < h1; ++h)
+        for (int ww = w0; ww < w1; ++ww) {
+          float f[8];
+          unpack8(x[((n * H + h) * W + ww) * C8 + c8], f);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) { m[k] = -INFINITY; sum[k] = 0.0f; }
-    for (int r = 0; r < kh; ++r) {
-      const int h = p * sh - pad_h + r;
-      if (h < 0 || h >= H) continue;
-      for (int s2 = 0; s2 < kw; ++s2) {
-        const int ww = q * sw - pad_w + s2;
-        if (ww < 0 || ww >= W) continue;
-        float f[8];
-        unpack8(x[((n * H + h) * W + ww) * C8 + c8], f);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          if (f[k] > m[k] || f[k] != f[k]) m[k] = f[k];
-          sum[k] += f[k];
+          for (int k = 0; k < 8; ++k) sum[k] += f[k];
         }
-      }
-    }
-    if (avg) {
       const float inv = 1.0f / (float)(kh * kw);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) m[k] = sum[k] * inv;
+      for (int k = 0; k < 8; ++k) sum[k] *= inv;
+      y[i] = pack8(sum);
+    } else {
+      // max of bf16 pairs directly (NaN-propagating), no conversion round trip
+      const __nv_bfloat162 ninf = __float2bfloat162_rn(-INFINITY);
+      bf16x8 m;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) m.v[k] = ninf;
+      for (int h = h0; h < h1; ++h)
+        for (int ww = w0; ww < w1; ++ww) {
+          const bf16x8 v = x[((n * H + h) * W + ww) * C8 + c8];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) m.v[k] = __hmax2_nan(m.v[k], v.v[k]);
+        }
+      y[i] = m;
     }
-    y[i] = pack8(m);
   }
 }
 
@@ -191,9 +200,13 @@ void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P,
                       int kw, int pad_h, int pad_w, int sh, int sw, bool avg, cudaStream_t s) {
   const int64_t total = (int64_t)N * P * Q * (C / 8);
   if (total == 0) return;
-  pool_bf16_kernel<<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H,
-                                                         W, P, Q, kh, kw, pad_h, pad_w, sh, sw, avg,
-                                                         total);
+  const int grid = grid_for(total, 256);
+  if (avg)
+    pool_bf16_kernel<true><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, P, Q,
+                                                kh, kw, pad_h, pad_w, sh, sw, total);
+  else
+    pool_bf16_kernel<false><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, P, Q,
+                                                 kh, kw, pad_h, pad_w, sh, sw, total);
   count(CNT_LAUNCHES);
 }
 
@@ -346,37 +359,54 @@ void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S
   count(CNT_LAUNCHES);
 }
 
-// x fp32 NCHW -> bf16 [N][H][Q][Sp*Cp]; one thread per (n, h, q, s): writes Cp channels.
-// Consecutive threads differ in s then q, so reads of one input row are near-contiguous
-// and the Cp*2-byte writes of a warp are contiguous.
+// x fp32 NCHW -> bf16 [N][H][Q][Sp*Cp].  One CTA per (n, h) image row: the C input rows
+// are staged in shared memory with coalesced loads, then every thread assembles the
+// Sp*Cp-channel vectors of its output columns and writes them as 16-byte pieces, so a warp
+// writes one contiguous run.
 __global__ void fold_input_kernel(const float *__restrict__ x, bf16 *__restrict__ out, int C,
                                   int H, int W, int Q, int S, int Sp, int Cp, int pad_w,
-                                  int stride_w, int64_t total) {
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int s2 = (int)(i % Sp);
-    int64_t rest = i / Sp;
-    const int q = (int)(rest % Q);
-    rest /= Q;
-    const int h = (int)(rest % H);
-    const int64_t n = rest / H;
-    const int ww = q * stride_w - pad_w + s2;
-    const bool ok = s2 < S && ww >= 0 && ww < W;
-    bf16 *o = out + i * Cp;
-    for (int c = 0; c < Cp; ++c) {
-      float v = 0.0f;
-      if (ok && c < C) v = x[((n * C + c) * H + h) * (int64_t)W + ww];
-      o[c] = __float2bfloat16_rn(v);
+                                  int stride_w) {
+  extern __shared__ float srow[];  // [C][W]
+  const int h = blockIdx.x % H;
+  const int64_t n = blockIdx.x / H;
+  for (int i = threadIdx.x; i < C * W; i += blockDim.x) {
+    const int c = i / W, w = i % W;
+    srow[i] = x[((n * C + c) * H + h) * (int64_t)W + w];
+  }
+  __syncthreads();
+  const int Cf = Sp * Cp;           // multiple of 8
+  const int pieces = Cf / 8;        // 16-byte pieces per output pixel
+  bf16 *orow = out + ((n * H + h) * (int64_t)Q) * Cf;
+  for (int i = threadIdx.x; i < Q * pieces; i += blockDim.x) {
+    const int q = i / pieces, pc = i % pieces;
+    __nv_bfloat162 v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float f[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int cf = pc * 8 + e * 2 + u;
+        const int s2 = cf / Cp, c = cf % Cp;
+        const int ww = q * stride_w - pad_w + s2;
+        f[u] = (s2 < S && c < C && ww >= 0 && ww < W) ? srow[c * W + ww] : 0.0f;
+      }
+      v[e] = __floats2bfloat162_rn(f[0], f[1]);
     }
+    uint4 pk;
+    pk.x = *reinterpret_cast<uint32_t *>(&v[0]);
+    pk.y = *reinterpret_cast<uint32_t *>(&v[1]);
+    pk.z = *reinterpret_cast<uint32_t *>(&v[2]);
+    pk.w = *reinterpret_cast<uint32_t *>(&v[3]);
+    *reinterpret_cast<uint4 *>(orow + (int64_t)i * 8) = pk;
   }
 }
 
 void launch_fold_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Q, int S,
                             int Sp, int Cp, int pad_w, int stride_w, cudaStream_t s) {
-  const int64_t total = (int64_t)N * H * Q * Sp;
-  if (total == 0) return;
-  fold_input_kernel<<<grid_for(total, 256), 256, 0, s>>>(x, out, C, H, W, Q, S, Sp, Cp, pad_w,
-                                                          stride_w, total);
+  if ((int64_t)N * H * Q == 0) return;
+  const size_t smem = (size_t)C * W * sizeof(float);
+  fold_input_kernel<<<(unsigned)(N * H), 256, smem, s>>>(x, out, C, H, W, Q, S, Sp, Cp, pad_w,
+                                                        stride_w);
   count(CNT_LAUNCHES);
 }
 

@@ -145,9 +145,11 @@ void ensure_f32(const void *p) {
     set_error(990, "read of a tensor that cross-call fusion skipped (set OCCAMY_FUSE_ACROSS_CALLS=0)");
   } else if (rec->fmt == FMT_ZERO) {
     OCC_CUDA(cudaMemsetAsync((void *)base, 0, rec->bytes, r.stream));
+    r.main_copies++;
   } else if (rec->fmt == FMT_PENDING) {
     OCC_CUDA(cudaMemcpyAsync((void *)base, rec->host_src, rec->host_bytes, cudaMemcpyHostToDevice,
                              r.stream));
+    r.main_copies++;
     count(CNT_H2D_BYTES, (int64_t)rec->host_bytes);
   } else if (rec->fmt == FMT_BF16_NHWC) {
     const size_t elems = (size_t)(rec->n * rec->c * rec->h * rec->w);

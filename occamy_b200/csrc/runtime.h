@@ -74,6 +74,7 @@ struct Runtime {
   MathMode mode = MATH_BF16;
   int last_error = 0;
   int64_t counters[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  int64_t main_copies = 0;  // copies / memsets enqueued on the launch stream (not kernels)
   std::map<uintptr_t, TensorRec> recs;  // keyed by device base pointer
   std::unordered_map<WeightKey, PackedWeight, WeightKeyHash> wcache;
   // host sources whose packed form is resident: source -> (bytes, fingerprint)
