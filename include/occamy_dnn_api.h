@@ -202,6 +202,26 @@ void occamy_set_cross_call_fusion(int on);
 /* Drop the resident packed-weight cache (forces re-upload and re-pack). */
 void occamy_clear_weight_cache(void);
 
+/* ---- fused convolution for callers that must not allocate ---------------------- */
+/* No counterpart in the reference.  Same arithmetic as DNNConvBiasActivFunc in the bf16
+ * tensor-core mode (y = act(x (*) w + b), fp32 NCHW in and out, activMode 1 / 3 / 5), for
+ * hosts that cannot call cudaMalloc where they call the runtime: processes that run inside
+ * a device-memory budget fixed before start-up, and latency-critical loops that must stay
+ * out of the driver's allocator (it takes process-wide locks and may synchronise the
+ * device).  All working copies live in a fixed 32 MiB device array that is part of the
+ * library image (so every GPU that loads the library carries it until exit); a problem
+ * whose copies (NHWC bf16 forms of x and y plus the packed filter) do not fit is refused
+ * with -2 and nothing is launched.  Needs C % 16 == 0 and K % 8 == 0 (-3 otherwise).
+ * Work is enqueued on `stream`; the call does not wait for it.  All calls share the one
+ * array: calls whose kernels may overlap on the GPU race, so keep them on one stream or
+ * order them with events.  The first call on each device also looks up the array's device
+ * address; make it outside any stream capture.  Returns 0, a negative code as above, or a
+ * cudaError_t value. */
+int occamy_conv_bias_act_noalloc(const float *x, const int64_t dimX[4], const float *w,
+                                 const int64_t dimW[4], const float *bias, const int64_t pads[2],
+                                 const int64_t strides[2], int64_t activMode, float *y,
+                                 cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

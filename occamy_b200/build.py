@@ -20,7 +20,7 @@ OBJ = os.path.join(LIB, "obj")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 RUNTIME_SRCS = ["runtime.cu", "kernels_f32.cu", "kernels_nhwc.cu", "conv_tc.cu", "trace.cu", "abi.cu",
-                "misc_ops.cu"]
+                "misc_ops.cu", "no_alloc.cu"]
 REPLAY_SRCS = [os.path.join("host", "replay.cpp")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

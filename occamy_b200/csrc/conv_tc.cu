@@ -533,6 +533,10 @@ static CUtensorMapSwizzle swizzle_for(int row_bytes) {
 
 // bf16 tensor map of rank `rank` (<= 4): dims/box innermost first, strides in bytes for
 // dims 1..rank-1.
+// Off only while a plan is built for the allocation-free entry point, which must not touch
+// the lazily initialised runtime state.
+static bool g_count_encodes = true;
+
 static bool make_map(CUtensorMap *m, const void *ptr, int rank, const uint64_t *dims,
                      const uint64_t *strides, const uint32_t *box, int row_bytes) {
   EncodeTiledFn fn = encode_fn();
@@ -548,7 +552,7 @@ static bool make_map(CUtensorMap *m, const void *ptr, int rank, const uint64_t *
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(ptr),
                   gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(row_bytes),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  count(CNT_TMAP_ENCODES);
+  if (g_count_encodes) count(CNT_TMAP_ENCODES);
   if (r != CUDA_SUCCESS) {
     set_error(2000 + (int)r, "cuTensorMapEncodeTiled");
     return false;
@@ -622,7 +626,7 @@ struct Plan {
 
 static int floordiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
-static Plan build_plan(const TcConvArgs &a) {
+static Plan build_plan(const TcConvArgs &a, int *err_word) {
   Plan pl;
   memset(&pl, 0, sizeof(pl));
   TcParams &p = pl.p;
@@ -638,7 +642,7 @@ static Plan build_plan(const TcConvArgs &a) {
   p.hi = a.act == ACT_CLIP ? a.hi : INFINITY;
   p.out_f32 = a.out_f32;
   p.ldo = a.ldo;
-  p.err = rt().dev_err;
+  p.err = err_word;
   const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
                     a.pad_w == 0;
   // output grid the tiles are cut from
@@ -719,14 +723,22 @@ static Plan build_plan(const TcConvArgs &a) {
 }
 
 template <int BN>
+static void launch_plan_on(const Plan &pl, int num_sms, cudaStream_t s);
+
+template <int BN>
 static void launch_plan(const Plan &pl, cudaStream_t s) {
+  launch_plan_on<BN>(pl, rt().num_sms, s);
+}
+
+template <int BN>
+static void launch_plan_on(const Plan &pl, int num_sms, cudaStream_t s) {
   static bool attr_set = false;
   if (!attr_set) {
     OCC_CUDA(cudaFuncSetAttribute(tc_conv_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   TC_SMEM_LIMIT));
     attr_set = true;
   }
-  int grid = pl.p.total_tiles < rt().num_sms ? pl.p.total_tiles : rt().num_sms;
+  int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
   tc_conv_kernel<BN><<<grid, TC_THREADS, pl.smem, s>>>(pl.p);
 }
 
@@ -738,7 +750,7 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
   auto it = plans.find(key);
   if (it == plans.end()) {
     if (plans.size() > 4096) plans.clear();
-    it = plans.emplace(key, build_plan(a)).first;
+    it = plans.emplace(key, build_plan(a, rt().dev_err)).first;
   }
   const Plan &pl = it->second;
   if (!pl.ok) {
@@ -767,6 +779,24 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
   OCC_CUDA(cudaGetLastError());
   count(CNT_LAUNCHES);
   count(CNT_TC_LAUNCHES);
+}
+
+// Launch without touching the runtime's state or any cache: the plan (tensor maps) is
+// rebuilt on every call, the kernel's error word and the SM count come from the caller.
+// Used by the entry point that must not allocate.
+bool launch_tc_conv_stateless(const TcConvArgs &a, int *err_word, int num_sms, cudaStream_t s) {
+  g_count_encodes = false;
+  const Plan pl = build_plan(a, err_word);
+  g_count_encodes = true;
+  if (!pl.ok) return false;
+  if (pl.p.total_tiles == 0) return true;
+  switch (pl.bn) {
+    case 32: launch_plan_on<32>(pl, num_sms, s); break;
+    case 64: launch_plan_on<64>(pl, num_sms, s); break;
+    case 128: launch_plan_on<128>(pl, num_sms, s); break;
+    default: launch_plan_on<256>(pl, num_sms, s); break;
+  }
+  return cudaGetLastError() == cudaSuccess;
 }
 
 }  // namespace occ

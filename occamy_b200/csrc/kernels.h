@@ -91,5 +91,7 @@ struct TcConvArgs {
 // Returns false when the shape is outside what the kernel supports (caller falls back).
 bool tc_conv_supported(const TcConvArgs &a);
 void launch_tc_conv(const TcConvArgs &a, cudaStream_t s);
+// Same kernel, no runtime state, no caches, no allocation; false when the plan fails.
+bool launch_tc_conv_stateless(const TcConvArgs &a, int *err_word, int num_sms, cudaStream_t s);
 
 }  // namespace occ

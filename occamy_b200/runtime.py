@@ -81,6 +81,8 @@ _SIGNATURES = {
     "occamy_stream": (C.c_void_p, []),
     "occamy_get_counters": (None, [_i64p]),
     "occamy_clear_weight_cache": (None, []),
+    "occamy_conv_bias_act_noalloc": (C.c_int, [_f32p, _i64p, _f32p, _i64p, _f32p, _i64p, _i64p,
+                                               C.c_int64, _f32p, C.c_void_p]),
     "occamy_fused_chains": (C.c_int64, []),
     "occamy_set_cross_call_fusion": (None, [C.c_int]),
     "occamy_profile_begin": (None, []),
