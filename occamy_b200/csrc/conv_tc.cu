@@ -588,7 +588,30 @@ static void choose_box(int Q, int P, int N, int *tw, int *th, int *tn) {
 }
 
 static int pick_bk(int Cf) { return Cf % 64 == 0 ? 64 : (Cf % 32 == 0 ? 32 : (Cf % 16 == 0 ? 16 : 0)); }
-static int pick_bn(int K) { return K > 128 ? 256 : (K > 64 ? 128 : (K > 32 ? 64 : 32)); }
+// Output-channel tile.  Wide tiles re-read the activations less and keep the tensor pipe
+// busier per instruction, but when a layer has few pixels they leave SMs idle; pick the
+// width with the lowest modelled time: waves x (k-steps x cost per k-step + epilogue slabs).
+static int pick_bn(int K, long sp_tiles, int ksteps, int num_sms) {
+  const int cand[4] = {256, 128, 64, 32};
+  const double kcost[4] = {560.0, 330.0, 230.0, 210.0};  // cycles per 64-deep k-step
+  int widest = 32;
+  while (widest < K && widest < 256) widest *= 2;
+  int best = widest;
+  double best_cost = -1.0;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cand[i];
+    if (bn > widest) continue;
+    const long tiles = sp_tiles * ((K + bn - 1) / bn);
+    const long waves = (tiles + num_sms - 1) / num_sms;
+    const int slabs = bn >= 64 ? bn / 64 : 1;
+    const double cost = (double)waves * (ksteps * kcost[i] + slabs * 700.0);
+    if (best_cost < 0 || cost < best_cost * 0.97) {   // ties go to the wider tile
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
 
 bool tc_conv_supported(const TcConvArgs &a) {
   if (pick_bk(a.Cf) == 0) return false;
@@ -626,12 +649,11 @@ struct Plan {
 
 static int floordiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
-static Plan build_plan(const TcConvArgs &a, int *err_word) {
+static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
   Plan pl;
   memset(&pl, 0, sizeof(pl));
   TcParams &p = pl.p;
-  const int bk = pick_bk(a.Cf), bn = pick_bn(a.K);
-  pl.bn = bn;
+  const int bk = pick_bk(a.Cf);
   p.bk = bk;
   p.cblocks = a.Cf / bk;
   p.K = a.K;
@@ -660,6 +682,10 @@ static Plan build_plan(const TcConvArgs &a, int *err_word) {
   p.tiles_w = (Qg + p.tw - 1) / p.tw;
   p.tiles_h = (Pg + p.th - 1) / p.th;
   p.tiles_n = (Ng + p.tn - 1) / p.tn;
+  const int nsm = num_sms > 0 ? num_sms : 148;
+  const int bn = pick_bn(a.K, (long)p.tiles_w * p.tiles_h * p.tiles_n,
+                         (a.R * a.S * a.Cf + 63) / 64, nsm);
+  pl.bn = bn;
   p.tiles_k = (a.K + bn - 1) / bn;
   p.total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_k;
 
@@ -750,7 +776,7 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
   auto it = plans.find(key);
   if (it == plans.end()) {
     if (plans.size() > 4096) plans.clear();
-    it = plans.emplace(key, build_plan(a, rt().dev_err)).first;
+    it = plans.emplace(key, build_plan(a, rt().dev_err, rt().num_sms)).first;
   }
   const Plan &pl = it->second;
   if (!pl.ok) {
@@ -786,7 +812,7 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
 // Used by the entry point that must not allocate.
 bool launch_tc_conv_stateless(const TcConvArgs &a, int *err_word, int num_sms, cudaStream_t s) {
   g_count_encodes = false;
-  const Plan pl = build_plan(a, err_word);
+  const Plan pl = build_plan(a, err_word, num_sms);
   g_count_encodes = true;
   if (!pl.ok) return false;
   if (pl.p.total_tiles == 0) return true;
