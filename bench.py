@@ -302,7 +302,10 @@ def main():
         "gpu_launches": int(c1["launches"] - c0["launches"]),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak if peak else None, "traffic": None,
+                     "frac": achieved / peak if peak else None,
+                     "traffic": profiled_traffic(per_rank, args.graph) if world == 1 else None,
+                     "traffic_note": "DRAM read+write bytes of the 54 launches of one step "
+                                     "(ncu, profiles/tc_conv_traffic_resnet50_b256.txt)",
                      "kernel": "tc_conv_kernel", "launches_per_step": per_step,
                      "kernel_ms_per_step": tc_total_ms, "peak_source": peaks["source"] +
                      " (sustained cuBLAS bf16)"},
@@ -317,6 +320,18 @@ def main():
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def profiled_traffic(batch, graph):
+    """DRAM bytes per step of the dominant kernel, from the committed ncu summary of this
+    workload (profiles/); None when the run is a different workload."""
+    path = os.path.join(ROOT, "profiles", "tc_conv_traffic_resnet50_b256.txt")
+    if graph != "resnet50" or batch != GLOBAL_BATCH or not os.path.exists(path):
+        return None
+    for line in open(path):
+        if line.startswith("dram_bytes_per_step:"):
+            return float(line.split(":")[1])
+    return None
 
 
 def write_per_layer(path, g, tc_ms, peaks, ms_step):
