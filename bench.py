@@ -166,7 +166,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from occamy_b200 import graphs, replay
+    from occamy_b200 import graphs, replay, sharding
     from occamy_b200 import runtime as rt
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -177,8 +177,8 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    assert args.batch % world == 0, "global batch must divide over the ranks"
-    per_rank = args.batch // world
+    lo_img, hi_img = sharding.shard_range(args.batch, rank, world)
+    per_rank = hi_img - lo_img
 
     rt.set_math_mode(rt.MATH_BF16 if args.math == "bf16" else rt.MATH_FP32)
     builder = getattr(graphs, args.graph)
@@ -203,14 +203,13 @@ def main():
         prog.run_raw(binding, x_dev.data_ptr(), 3, [out_dev.data_ptr()], 3)
         if world > 1:
             with torch.cuda.stream(stream):
-                dist.all_gather_into_tensor(gathered, out_dev)
+                sharding.gather_logits(out_dev, gathered)
 
     def step_e2e():
         prog.run_raw(binding, x_host.data_ptr(), 1, [out_dev.data_ptr()], 3)
         with torch.cuda.stream(stream):
             if world > 1:
-                dist.all_gather_into_tensor(gathered, out_dev)
-                src = gathered
+                src = sharding.gather_logits(out_dev, gathered)
             else:
                 src = out_dev
             if rank == 0:
