@@ -147,12 +147,47 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_incumbent_arm(args):
+    """--impl incumbent (not part of the driver's contract): the reference's own GPU runtime
+    -- its cuDNN / cuBLASLt wrappers compiled unchanged into oracle/_ref -- replaying the same
+    call program on this GPU, host batch in, host logits out, wall-clock timed (its work runs
+    on the legacy default stream and every inference ends in a blocking copy)."""
+    import torch
+    from occamy_b200 import graphs, replay
+    from oracle import build as obuild
+    if not os.path.exists(obuild.REF_SO):
+        print(json.dumps({"impl": "incumbent", "unavailable": "oracle/_ref not built"}))
+        return
+    torch.cuda.set_device(0)
+    g = getattr(graphs, args.graph)(batch=args.batch, seed=0)
+    prog = g.to_program()
+    prog.lower(fuse=args.fuse, workspace_bytes=256 << 20)
+    binding = replay.Binding(obuild.REF_SO)
+    x = torch.from_numpy(graphs.make_input(g, 0)).pin_memory()
+    out = torch.empty(g.shapes[g.outputs[0]], dtype=torch.float32).pin_memory()
+    for _ in range(max(args.warmup, 1)):
+        prog.run_raw(binding, x.data_ptr(), 1, [out.data_ptr()], 1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        prog.run_raw(binding, x.data_ptr(), 1, [out.data_ptr()], 1)
+    torch.cuda.synchronize()
+    ms = 1000.0 * (time.perf_counter() - t0) / args.steps
+    print(json.dumps({"impl": "incumbent", "metric": METRIC, "value": args.batch / (ms / 1000.0),
+                      "unit": "images/s", "n_gpus": 1, "steps": args.steps, "ms_per_step": ms,
+                      "dtype": "f32 (cuDNN default math)", "data": "synthetic",
+                      "config": {"workload": f"{g.name} batch {args.batch}, reference wrappers "
+                                             f"(cuDNN {torch.backends.cudnn.version()}), "
+                                             f"fuse={args.fuse}, weights re-uploaded every "
+                                             "inference as the compiled model does"}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "incumbent"])
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch")
     ap.add_argument("--math", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--graph", default="resnet50", choices=["resnet50", "mobilenet_v2", "vgg16"])
@@ -162,6 +197,9 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.impl == "incumbent":
+        run_incumbent_arm(args)
         return
 
     import torch

@@ -725,7 +725,9 @@ int occ_run(void *h, void *api_h, const float *input, int input_kind, float **ou
                             copy_out == 3 ? 3 : 2, stream);
         break;
       case I_CONV:
-        api.DNNConvFunc(handle, b0, in.dA, b1, in.dB, b3, in.ws_bytes, 1, in.groups, in.pads,
+        // algorithm 0 (implicit GEMM) needs no workspace, whatever size the plan reserved; the
+        // real compiler passes whichever algorithm cuDNN's search picked on its machine
+        api.DNNConvFunc(handle, b0, in.dA, b1, in.dB, b3, in.ws_bytes, 0, in.groups, in.pads,
                         in.strides, o);
         break;
       case I_CONV_BIAS_ACT:

@@ -82,11 +82,14 @@ def build_reference_wrappers(reference_root: str = "/root/reference", force: boo
         if r.returncode != 0:
             return None, "nvcc failed: " + r.stderr.decode("utf-8", "replace")[-600:]
         objs.append(obj)
-    cmd = ["nvcc", "-shared", "-o", REF_SO] + objs + [
+    # shared cudart so that cudaStreamCreate & co. resolve through the library, as they do
+    # for a compiled model that links -lcudart
+    cmd = ["nvcc", "-shared", "-cudart", "shared", "-o", REF_SO] + objs + [
         "-L", os.path.join(cudnn, "lib"), "-L", os.path.join(cublas, "lib"),
         "-l:" + os.path.basename(cudnn_lib[0]), "-l:" + os.path.basename(cublas_lib[0]),
         "-Xlinker", "-rpath," + os.path.join(cudnn, "lib"),
-        "-Xlinker", "-rpath," + os.path.join(cublas, "lib")]
+        "-Xlinker", "-rpath," + os.path.join(cublas, "lib"),
+        "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
     r = subprocess.run(cmd, capture_output=True)
     if r.returncode != 0:
         return None, "link failed: " + r.stderr.decode("utf-8", "replace")[-600:]
