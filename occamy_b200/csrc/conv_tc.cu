@@ -125,6 +125,9 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, uint32_t src,
       "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
@@ -248,6 +251,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    // descriptor fetches are off the critical path of the first loads / stores
+    tma_prefetch_map(&p.tmA[0]);
+    tma_prefetch_map(&p.tmB);
+    if (!p.out_f32) tma_prefetch_map(&p.tmD);
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
