@@ -58,6 +58,7 @@ struct alignas(64) TcParams {
   float *out_f32;
   int ldo;
   int m_total;
+  int n_mma;             // pixel-N variant: N of the MMA (pixels per tile rounded up to 16)
   int *err;
 };
 
@@ -216,9 +217,8 @@ __device__ __forceinline__ uint32_t slab_off(int row, int chunk, int row_bytes) 
 }
 
 // ------------------------------------------------------------------ the kernel
-template <int BN>
+template <int BN, int DC>   // DC: channels per staged output slab (64; 32 trades slab size for ring depth)
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_constant__ TcParams p) {
-  constexpr int DC = BN < 64 ? BN : 64;        // channels per staged output slab
   constexpr int CW = DC / 2;                   // channels one epilogue thread handles per slab
   constexpr int NSLAB = BN / DC;
   constexpr int SLAB_BYTES = 128 * DC * 2;
@@ -512,6 +512,242 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_con
   }
 }
 
+// ------------------------------------------------------------------ pixel-N variant
+// One tcgen05.mma takes the same ~155 cycles whatever its N, so a layer with few output
+// channels wastes most of the tensor pipe when the channels are the N dimension.  This
+// variant swaps the operands: the filter tile (128 output channels x BK) is the M side, up
+// to 256 pixels are the N side, D^T[channel, pixel] lands in TMEM with one channel per lane.
+// The epilogue thread of a lane owns that channel (bias is a scalar), walks the pixels and
+// transposes through the staged NHWC slabs with 2-byte stores (a warp writes 64 contiguous
+// bytes of one pixel), which TMA then stores as before.  Used for K <= 128.
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_constant__ TcParams p) {
+  constexpr int SLAB_BYTES = 256 * 128;   // 256 pixel rows x 64 channels of bf16
+  constexpr uint32_t TMEM_COLS = 512;     // two accumulators of 256 pixel columns
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const int bk = p.bk, stages = p.stages;
+  const uint32_t w_bytes = 128u * bk * 2u, x_bytes = 256u * bk * 2u;
+  const uint32_t sW = base;
+  const uint32_t sX = sW + stages * w_bytes;
+  const uint32_t sD = sX + stages * x_bytes;            // 2 slabs: channels 0-63, 64-127
+  const uint32_t sMisc = sD + 2 * SLAB_BYTES;
+  uint8_t *misc_ptr = base_ptr + (sMisc - base);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(misc_ptr);
+  const uint32_t bar0 = sMisc;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
+  auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + s); };
+  auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * stages + 2 + s); };
+  const uint32_t rfull_bar = bar0 + 8u * (2 * stages + 4);
+  volatile uint32_t *tmem_holder = reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 5);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 6);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), TC_EPI_THREADS);
+    }
+    mbar_init(rfull_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32((const void *)tmem_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int rows_valid = p.tw * p.th * p.tn;   // pixels per tile (<= 256)
+  const int ksteps = p.num_taps * p.cblocks;
+  int err_code = 0;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + w_bytes;
+      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+        const int kt = tile % p.tiles_k;
+        int sp = tile / p.tiles_k;
+        const int q0 = (sp % p.tiles_w) * p.tw;
+        sp /= p.tiles_w;
+        const int p0 = (sp % p.tiles_h) * p.th;
+        const int n0 = (sp / p.tiles_h) * p.tn;
+        const int k0 = kt * 128;
+        for (int t = 0; t < p.num_taps && !err_code; ++t) {
+          const TcTap tap = p.taps[t];
+          for (int cb = 0; cb < p.cblocks; ++cb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+              err_code = 1;
+              break;
+            }
+            mbar_expect_tx(full_bar(stage), tx_bytes);
+            tma_load_4d(sX + stage * x_bytes, &p.tmA[tap.map], full_bar(stage), cb * bk,
+                        q0 + tap.dw, p0 + tap.dh, n0);
+            tma_load_3d(sW + stage * w_bytes, &p.tmB, full_bar(stage), cb * bk, k0, t);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                             ((uint32_t)(p.n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          err_code = 2;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+        uint32_t accumulate = 0;
+        for (int ks = 0; ks < ksteps; ++ks) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            err_code = 3;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t wdesc = make_smem_desc(sW + stage * w_bytes, bk);
+          const uint64_t xdesc = make_smem_desc(sX + stage * x_bytes, bk);
+          for (int kk = 0; kk < bk / 16; ++kk) {
+            tc_mma_bf16(d_tmem, wdesc + (uint64_t)(2 * kk), xdesc + (uint64_t)(2 * kk), idesc,
+                        accumulate);
+            accumulate = 1;
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (err_code) break;
+        tc_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    const float act_lo = p.lo, act_hi = p.hi;
+    const int quad = warp & 3;                 // TMEM lane quadrant = 32 output channels
+    const int half = (warp - 2) >> 2;          // which 128 of the 256 pixel columns
+    const int c_local = quad * 32 + lane;      // this thread's channel within the 128-tile
+    const int slab = c_local >> 6, cin = c_local & 63;
+    const bool leader = threadIdx.x == 64;
+    int acc = 0;
+    uint32_t acc_phase = 0, r_phase = 0;
+    // With at most 64 output channels only one slab is used per tile, so the two slab
+    // buffers alternate and a tile's store need not have drained before the next one writes.
+    const bool one_slab = p.K <= 64;
+    uint32_t flip = 0;
+    for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+      const int kt = tile % p.tiles_k;
+      int sp = tile / p.tiles_k;
+      const int q0 = (sp % p.tiles_w) * p.tw;
+      sp /= p.tiles_w;
+      const int p0 = (sp % p.tiles_h) * p.th;
+      const int n0 = (sp / p.tiles_h) * p.tn;
+      const int k0 = kt * 128;
+      const int nslab = min(2, (p.K - k0 + 63) / 64);
+      const int ch = k0 + c_local;
+      const float bias = (p.bias && ch < p.K) ? p.bias[ch] : 0.0f;
+      const uint32_t sDt = sD + (one_slab ? flip * SLAB_BYTES : 0u);
+      if (leader) {
+        // the stores that last read the slab(s) about to be written have drained
+        if (one_slab) tma_store_wait_read<1>();
+        else tma_store_wait_read<0>();
+        if (p.has_res) {
+          mbar_expect_tx(rfull_bar, (uint32_t)(nslab * rows_valid) * 128u);
+          for (int sl = 0; sl < nslab; ++sl)
+            tma_load_4d(sDt + sl * SLAB_BYTES, &p.tmR, rfull_bar, k0 + sl * 64, q0, p0, n0);
+        }
+      }
+      epi_bar();
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+        err_code = 4;
+        break;
+      }
+      tc_fence_after();
+      if (p.has_res) {
+        if (!mbar_wait(rfull_bar, r_phase, abort_flag)) {
+          err_code = 5;
+          break;
+        }
+        r_phase ^= 1u;
+      }
+      const bool active = slab < nslab;        // warp-uniform (a warp covers 32 channels)
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) +
+                              (uint32_t)(acc * 256 + half * 128);
+      uint8_t *dslab = base_ptr + (sDt + slab * SLAB_BYTES - base);
+      const int col_end = min(128, p.n_mma - half * 128);   // columns of this half in use
+      if (active && col_end > 0) {
+        uint32_t rr[2][32];
+        tc_ld32(t_addr, rr[0]);
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          if (c4 * 32 >= col_end) break;
+          tc_ld_wait();
+          if ((c4 + 1) * 32 < col_end) tc_ld32(t_addr + (uint32_t)((c4 + 1) * 32), rr[(c4 + 1) & 1]);
+          const uint32_t *r = rr[c4 & 1];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int pix = half * 128 + c4 * 32 + j;
+            __nv_bfloat16 *cell = reinterpret_cast<__nv_bfloat16 *>(
+                dslab + slab_off(pix, cin >> 3, 128) + (cin & 7) * 2);
+            float v = __uint_as_float(r[j]) + bias;
+            if (p.has_res) v += __bfloat162float(*cell);
+            *cell = __float2bfloat16_rn(tc_act(v, act_lo, act_hi));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(tempty_bar(acc));
+      fence_async_smem();
+      epi_bar();
+      if (leader) {
+        for (int sl = 0; sl < nslab; ++sl)
+          tma_store_4d(&p.tmD, sDt + sl * SLAB_BYTES, k0 + sl * 64, q0, p0, n0);
+        tma_store_commit();
+      }
+      flip ^= 1u;
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (leader) tma_store_wait_read<0>();
+  }
+
+  if (err_code) {
+    atomicExch(p.err, 1000 + err_code);
+    *abort_flag = 1;
+    for (int i = 0; i < 50; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -567,15 +803,15 @@ static bool make_map(CUtensorMap *m, const void *ptr, int rank, const uint64_t *
   return true;
 }
 
-// Pixel box (tw x th x tn <= 128) that covers a Q x P x N output grid with the fewest tiles.
-static void choose_box(int Q, int P, int N, int *tw, int *th, int *tn) {
+// Pixel box (tw x th x tn <= limit) that covers a Q x P x N output grid with the fewest tiles.
+static void choose_box(int Q, int P, int N, int limit, int *tw, int *th, int *tn) {
   long best = -1;
   int bw = 1, bh = 1, bn = 1;
-  for (int w = 1; w <= (Q < 128 ? Q : 128); ++w) {
+  for (int w = 1; w <= (Q < limit ? Q : limit); ++w) {
     const long cw = (Q + w - 1) / w;
-    for (int h = 1; h <= P && w * h <= 128; ++h) {
+    for (int h = 1; h <= P && h <= 256 && w * h <= limit; ++h) {
       const long ch = (P + h - 1) / h;
-      int n = 128 / (w * h);
+      int n = limit / (w * h);
       if (n > N) n = N;
       // any n in [1, n] is legal; fewer tiles with the largest, but try divisors too
       for (int nn = n; nn >= 1; nn = (nn > 8 ? nn / 2 : nn - 1)) {
@@ -599,8 +835,12 @@ static int pick_bk(int Cf) { return Cf % 64 == 0 ? 64 : (Cf % 32 == 0 ? 32 : (Cf
 // busier per instruction, but when a layer has few pixels they leave SMs idle; pick the
 // width with the lowest modelled time: waves x (k-steps x cost per k-step + epilogue slabs).
 static int pick_bn(int K, long sp_tiles, int ksteps, int num_sms) {
+  if (const char *f = getenv("OCCAMY_TC_BN")) {   // tuning aid: force the tile width
+    const int v = atoi(f);
+    if (v == 32 || v == 64 || v == 128 || v == 256) return v;
+  }
   const int cand[4] = {256, 128, 64, 32};
-  const double kcost[4] = {560.0, 330.0, 230.0, 210.0};  // cycles per 64-deep k-step
+  const double kcost[4] = {900.0, 780.0, 715.0, 700.0};  // cycles per 64-deep k-step
   int widest = 32;
   while (widest < K && widest < 256) widest *= 2;
   int best = widest;
@@ -650,6 +890,8 @@ struct ArgsKeyHash {
 struct Plan {
   TcParams p;
   int bn;
+  int dc;    // channels per output slab
+  bool pn;   // pixel-N variant
   size_t smem;
   bool ok;
 };
@@ -685,13 +927,21 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
   p.gq = Qg;
   p.gp = Pg;
   p.gn = Ng;
-  choose_box(Qg, Pg, Ng, &p.tw, &p.th, &p.tn);
+  static const bool pn_allowed = !(getenv("OCCAMY_TC_PIXEL_N") && !strcmp(getenv("OCCAMY_TC_PIXEL_N"), "0"));
+  // worth it only where the tensor pipe is the limit: the transposing epilogue is slower
+  // than the plain one, which hurts the HBM-bound 1x1 layers
+  const bool pn = pn_allowed && !a.out_f32 && a.K <= 128 && a.R * a.S > 1 &&
+                  a.R * a.S * a.Cf >= 9 * 64;
+  pl.pn = pn;
+  choose_box(Qg, Pg, Ng, pn ? 256 : 128, &p.tw, &p.th, &p.tn);
+  p.n_mma = (p.tw * p.th * p.tn + 15) / 16 * 16;
   p.tiles_w = (Qg + p.tw - 1) / p.tw;
   p.tiles_h = (Pg + p.th - 1) / p.th;
   p.tiles_n = (Ng + p.tn - 1) / p.tn;
   const int nsm = num_sms > 0 ? num_sms : 148;
-  const int bn = pick_bn(a.K, (long)p.tiles_w * p.tiles_h * p.tiles_n,
-                         (a.R * a.S * a.Cf + 63) / 64, nsm);
+  const int bn = pn ? 128
+                    : pick_bn(a.K, (long)p.tiles_w * p.tiles_h * p.tiles_n,
+                              (a.R * a.S * a.Cf + 63) / 64, nsm);
   pl.bn = bn;
   p.tiles_k = (a.K + bn - 1) / bn;
   p.total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_k;
@@ -734,7 +984,11 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
     const uint32_t box[3] = {(uint32_t)bk, (uint32_t)bn, 1};
     ok &= make_map(&p.tmB, a.w, 3, dims, st, box, bk * 2);
   }
-  const int dc = bn < 64 ? bn : 64;
+  // For 256-wide tiles with a long reduction, 32-channel slabs free enough shared memory
+  // for a fourth ring stage, which those layers need more than a cheap epilogue.
+  const int ksteps64 = (a.R * a.S * a.Cf + 63) / 64;
+  const int dc = pn ? 64 : (bn < 64 ? bn : (bn == 256 && bk == 64 && ksteps64 >= 16 ? 32 : 64));
+  pl.dc = dc;
   if (!a.out_f32) {
     const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
     const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};
@@ -743,36 +997,60 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
     if (a.residual) ok &= make_map(&p.tmR, a.residual, 4, dims, st, box, dc * 2);
   }
   // shared memory: ring + output slabs (+ residual slabs) + bias + barriers + alignment
-  const size_t stage_bytes = 128 * bk * 2 + (size_t)bn * bk * 2;
-  const size_t fixed = 1024 + (size_t)TC_DBUF * 128 * dc * 2 + bn * 4 + 8 * 80;
+  const size_t stage_bytes = pn ? (size_t)(128 + 256) * bk * 2 : 128 * bk * 2 + (size_t)bn * bk * 2;
+  const size_t fixed = pn ? 1024 + 2 * 256 * 128 + 8 * 80
+                          : 1024 + (size_t)TC_DBUF * 128 * dc * 2 + bn * 4 + 8 * 80;
   int stages = (int)((TC_SMEM_LIMIT - fixed) / stage_bytes);
   if (stages > 8) stages = 8;
   if (stages < 2) ok = false;
   p.stages = stages;
   pl.smem = fixed + stages * stage_bytes;
   if (pl.smem < 120 * 1024) pl.smem = 120 * 1024;  // keep one CTA per SM (TMEM is per SM)
+  if (getenv("OCCAMY_TC_PLAN_LOG"))
+    fprintf(stderr, "[tcplan] K %d Cf %d RS %d px %dx%dx%d box %dx%dx%d bn %d dc %d pn %d bk %d stages %d tiles %d smem %zu\n",
+            a.K, a.Cf, a.R * a.S, Qg, Pg, Ng, p.tw, p.th, p.tn, bn, dc, (int)pn, bk, stages,
+            p.total_tiles, pl.smem);
   pl.ok = ok;
   return pl;
 }
 
-template <int BN>
-static void launch_plan_on(const Plan &pl, int num_sms, cudaStream_t s);
-
-template <int BN>
-static void launch_plan(const Plan &pl, cudaStream_t s) {
-  launch_plan_on<BN>(pl, rt().num_sms, s);
-}
-
-template <int BN>
+template <int BN, int DC>
 static void launch_plan_on(const Plan &pl, int num_sms, cudaStream_t s) {
   static bool attr_set = false;
   if (!attr_set) {
-    OCC_CUDA(cudaFuncSetAttribute(tc_conv_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    OCC_CUDA(cudaFuncSetAttribute(tc_conv_kernel<BN, DC>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT));
+    attr_set = true;
+  }
+  int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
+  tc_conv_kernel<BN, DC><<<grid, TC_THREADS, pl.smem, s>>>(pl.p);
+}
+
+static void launch_plan_pn(const Plan &pl, int num_sms, cudaStream_t s) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    OCC_CUDA(cudaFuncSetAttribute(tc_conv_pn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   TC_SMEM_LIMIT));
     attr_set = true;
   }
   int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
-  tc_conv_kernel<BN><<<grid, TC_THREADS, pl.smem, s>>>(pl.p);
+  tc_conv_pn_kernel<<<grid, TC_THREADS, pl.smem, s>>>(pl.p);
+}
+
+static void launch_any(const Plan &pl, int num_sms, cudaStream_t s) {
+  if (pl.pn) {
+    launch_plan_pn(pl, num_sms, s);
+    return;
+  }
+  switch (pl.bn) {
+    case 32: launch_plan_on<32, 32>(pl, num_sms, s); break;
+    case 64: launch_plan_on<64, 64>(pl, num_sms, s); break;
+    case 128: launch_plan_on<128, 64>(pl, num_sms, s); break;
+    default:
+      if (pl.dc == 32) launch_plan_on<256, 32>(pl, num_sms, s);
+      else launch_plan_on<256, 64>(pl, num_sms, s);
+      break;
+  }
 }
 
 void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
@@ -802,12 +1080,7 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
     }
     OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot], s));
   }
-  switch (pl.bn) {
-    case 32: launch_plan<32>(pl, s); break;
-    case 64: launch_plan<64>(pl, s); break;
-    case 128: launch_plan<128>(pl, s); break;
-    default: launch_plan<256>(pl, s); break;
-  }
+  launch_any(pl, r.num_sms, s);
   if (prof_slot >= 0) OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot + 1], s));
   OCC_CUDA(cudaGetLastError());
   count(CNT_LAUNCHES);
@@ -823,12 +1096,7 @@ bool launch_tc_conv_stateless(const TcConvArgs &a, int *err_word, int num_sms, c
   g_count_encodes = true;
   if (!pl.ok) return false;
   if (pl.p.total_tiles == 0) return true;
-  switch (pl.bn) {
-    case 32: launch_plan_on<32>(pl, num_sms, s); break;
-    case 64: launch_plan_on<64>(pl, num_sms, s); break;
-    case 128: launch_plan_on<128>(pl, num_sms, s); break;
-    default: launch_plan_on<256>(pl, num_sms, s); break;
-  }
+  launch_any(pl, num_sms, s);
   return cudaGetLastError() == cudaSuccess;
 }
 
