@@ -19,12 +19,14 @@ LIB = os.path.join(HERE, "lib")
 OBJ = os.path.join(LIB, "obj")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-RUNTIME_SRCS = ["runtime.cu", "kernels_f32.cu", "kernels_nhwc.cu", "conv_tc.cu", "trace.cu", "abi.cu",
-                "misc_ops.cu", "no_alloc.cu"]
+RUNTIME_SRCS = ["runtime.cu", "kernels_f32.cu", "kernels_nhwc.cu", "conv_tc.cu", "conv_tc_inst_256_64.cu",
+                "conv_tc_inst_256_32.cu", "conv_tc_inst_128_64.cu", "conv_tc_inst_64_64.cu",
+                "conv_tc_inst_32_32.cu", "trace.cu", "abi.cu", "misc_ops.cu", "no_alloc.cu"]
 REPLAY_SRCS = [os.path.join("host", "replay.cpp")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-I", CSRC, "-I", INCLUDE]
+NVCC_FLAGS += os.environ.get("OCCAMY_NVCC_EXTRA", "").split()   # e.g. -DOCCAMY_TC_TIMERS
 
 RUNTIME_SO = os.path.join(LIB, "liboccamy_dnn.so")
 RUNTIME_A = os.path.join(LIB, "libcd_dnn_wrapper.a")
@@ -35,7 +37,7 @@ def _deps_mtime() -> float:
     t = os.path.getmtime(__file__)
     for root, _, files in os.walk(CSRC):
         for f in files:
-            if f.endswith((".h", ".hpp")):
+            if f.endswith((".h", ".hpp", ".cuh")):
                 t = max(t, os.path.getmtime(os.path.join(root, f)))
     for f in os.listdir(INCLUDE):
         t = max(t, os.path.getmtime(os.path.join(INCLUDE, f)))

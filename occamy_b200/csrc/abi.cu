@@ -152,14 +152,20 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
   a.N = g.N; a.K = g.K; a.P = g.P; a.Q = g.Q;
   a.act = g.act; a.lo = g.lo; a.hi = g.hi;
   const bool folded = g.C < 16;
-  int Sp = 0, Cp = 0;
+  int Sp = 0, Cp = 0, Wp = 0;
   if (folded) {
-    Cp = g.C <= 4 ? 4 : (g.C <= 8 ? 8 : 16);
+    // channels padded so that one output column's step along the row is a multiple of 16 bytes
+    Cp = g.C <= 4 ? (g.stride_w % 2 == 0 ? 4 : 8) : (g.C <= 8 ? 8 : 16);
     const int unit = 16 / Cp;
     Sp = (g.S + unit - 1) / unit * unit;
+    Wp = g.pad_w + g.W;
+    if (Wp < (g.Q - 1) * g.stride_w + Sp) Wp = (g.Q - 1) * g.stride_w + Sp;
+    Wp = (Wp + 7) / 8 * 8;
     a.H = g.H; a.W = g.Q; a.Cf = Sp * Cp;
     a.R = g.R; a.S = 1;
     a.pad_h = g.pad_h; a.pad_w = 0; a.stride_h = g.stride_h; a.stride_w = 1;
+    a.w_step = g.stride_w * Cp;
+    a.row_elems = Wp * Cp;
   } else {
     if (g.C % 16 != 0) return false;
     a.H = g.H; a.W = g.W; a.Cf = g.C;
@@ -174,10 +180,9 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
   job.dep_lo[0] = job.dep_hi[0] = 0;
   if (folded) {
     ensure_f32(x);
-    bf16 *xf = (bf16 *)scratch_get(0, (size_t)g.N * g.H * g.Q * a.Cf * 2);
+    bf16 *xf = (bf16 *)scratch_get(0, (size_t)g.N * g.H * Wp * Cp * 2);
     if (!xf) return false;
-    launch_fold_input_bf16(x, xf, g.N, g.C, g.H, g.W, g.Q, g.S, Sp, Cp, g.pad_w, g.stride_w,
-                           r.stream);
+    launch_pad_input_bf16(x, xf, g.N, g.C, g.H, g.W, Wp, Cp, g.pad_w, r.stream);
     a.x = xf;
     a.w = (const bf16 *)packed_weights(w, PACK_FOLD, (size_t)g.R * g.K * a.Cf * 2, g.K, g.C, g.R,
                                        g.S, Sp, Cp);

@@ -10,507 +10,21 @@
 // maps whose strides are the convolution stride (h = stride*(p + a) + b for tap offset
 // stride*a + b), so the same shifted-box scheme applies.
 //
-// One persistent CTA per SM, 192 threads:
-//   warp 0     : TMA producer (one elected lane) - fills a ring of {A, B} stages
-//   warp 1     : MMA issuer  (one elected lane) - tcgen05.mma, 128 x BN x 16 per issue,
-//                fp32 accumulators in TMEM, two accumulator buffers
-//   warps 2..5 : epilogue - tcgen05.ld the finished accumulator, add bias / residual,
-//                activation, convert to bf16, stage 64-channel slabs in swizzled shared
-//                memory and TMA-store them (stores clip at the image edge), while the MMA
-//                warp already works on the next tile.
-// Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in
-// the error word, drains and returns.
-#include <cuda.h>
-
+// The kernels run one persistent CTA per SM with warp-specialised roles (TMA producer, MMA
+// issuer, epilogue warps, slab store); the pixel-M kernel template lives in conv_tc_dev.cuh,
+// the pixel-N variant and the host-side planning (tile shapes, tensor maps, shared-memory
+// budget) in this file.  Every wait on an mbarrier is bounded; when a bound is hit the
+// kernel records a code in the error word, drains and returns.
 #include <cmath>
 #include <cstring>
 #include <unordered_map>
 #include <vector>
 
+#include "conv_tc_dev.cuh"
 #include "kernels.h"
 #include "runtime.h"
 
 namespace occ {
-
-constexpr int TC_THREADS = 320;      // 1 producer warp + 1 MMA warp + 8 epilogue warps
-constexpr int TC_EPI_THREADS = 256;
-constexpr int TC_DBUF = 3;           // output slab buffers in shared memory
-constexpr int TC_MAX_TAPS = 32;
-constexpr int TC_SMEM_LIMIT = 232448;  // 227 KB
-
-struct TcTap {
-  int map, dw, dh;
-};
-
-struct alignas(64) TcParams {
-  CUtensorMap tmA[4];
-  CUtensorMap tmB;
-  CUtensorMap tmD;
-  CUtensorMap tmR;
-  TcTap taps[TC_MAX_TAPS];
-  int num_taps, cblocks, bk, stages;
-  int tiles_w, tiles_h, tiles_n, tiles_k, total_tiles;
-  int tw, th, tn, K;
-  const float *bias;
-  int has_res, act;
-  int gq, gp, gn;        // extents of the output grid the tiles are cut from
-  float lo, hi;
-  float *out_f32;
-  int ldo;
-  int m_total;
-  int n_mma;             // pixel-N variant: N of the MMA (pixels per tile rounded up to 16)
-  int *err;
-};
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t cnt) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(cnt));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t a) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(a), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up after ~2 s of polling or as soon as another role has given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag) {
-  if (mbar_try(a, parity)) return true;
-  const long long t0 = clock64();
-  int it = 0;
-  while (!mbar_try(a, parity)) {
-    if ((++it & 15) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > 4000000000LL) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
-                                            int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
-      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
-                                            int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, uint32_t src, int c0, int c1,
-                                             int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(m),
-      "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *m) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-template <int W>
-__device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t *r) {
-  if constexpr (W == 32) tc_ld32(taddr, r);
-  else tc_ld16(taddr, r);
-}
-__device__ __forceinline__ void tc_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
-// Shared-memory matrix descriptor for a K-major bf16 tile whose rows are `bk` elements
-// (32 / 64 / 128 bytes, swizzled with the matching 32B / 64B / 128B pattern): 8-row groups
-// are 8*bk*2 bytes apart; descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk) {
-  const uint32_t sbo = (uint32_t)(8 * bk * 2);
-  const uint64_t layout = bk == 64 ? 2ull : (bk == 32 ? 4ull : 6ull);
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(sbo >> 4) << 32) |
-         (1ull << 46) | (layout << 61);
-}
-
-// The fused activations (identity, ReLU, clipped ReLU) are all a clamp to [lo, hi]; keeping
-// the epilogue to that one form keeps its unrolled body small.
-__device__ __forceinline__ float tc_act(float v, float lo, float hi) {
-  return fminf(fmaxf(v, lo), hi);
-}
-
-// Byte offset of 16-byte chunk `chunk` of row `row` inside a staged slab whose rows are
-// `row_bytes` (64 or 128) long, with the TMA swizzle of that width applied.
-__device__ __forceinline__ uint32_t slab_off(int row, int chunk, int row_bytes) {
-  const uint32_t off = (uint32_t)(row * row_bytes + chunk * 16);
-  const uint32_t mask = (uint32_t)(row_bytes / 16 - 1);
-  return off ^ (((off >> 7) & mask) << 4);
-}
-
-// ------------------------------------------------------------------ the kernel
-template <int BN, int DC>   // DC: channels per staged output slab (64; 32 trades slab size for ring depth)
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_kernel(const __grid_constant__ TcParams p) {
-  constexpr int CW = DC / 2;                   // channels one epilogue thread handles per slab
-  constexpr int NSLAB = BN / DC;
-  constexpr int SLAB_BYTES = 128 * DC * 2;
-  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                             ((uint32_t)(128 >> 4) << 24);
-  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const int bk = p.bk, stages = p.stages;
-  const uint32_t a_bytes = 128u * bk * 2u, b_bytes = (uint32_t)BN * bk * 2u;
-  const uint32_t sA = base;
-  const uint32_t sB = sA + stages * a_bytes;
-  const uint32_t sD = sB + stages * b_bytes;                    // TC_DBUF output slabs
-  const uint32_t sMisc = sD + TC_DBUF * SLAB_BYTES;
-  uint8_t *misc_ptr = base_ptr + (sMisc - base);
-  float *bias_s = reinterpret_cast<float *>(misc_ptr);                  // BN floats
-  uint64_t *bars = reinterpret_cast<uint64_t *>(misc_ptr + BN * 4);     // barriers
-  const uint32_t bar0 = sMisc + BN * 4;
-  auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
-  auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + s); };
-  auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * stages + 2 + s); };
-  auto rfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + 4 + s); };
-  volatile uint32_t *tmem_holder =
-      reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 4 + TC_DBUF);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 5 + TC_DBUF);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    // descriptor fetches are off the critical path of the first loads / stores
-    tma_prefetch_map(&p.tmA[0]);
-    tma_prefetch_map(&p.tmB);
-    if (!p.out_f32) tma_prefetch_map(&p.tmD);
-    for (int s = 0; s < stages; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), TC_EPI_THREADS);
-    }
-    for (int s = 0; s < TC_DBUF; ++s) mbar_init(rfull_bar(s), 1);
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32((const void *)tmem_holder)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;
-
-  const int rows_valid = p.tw * p.th * p.tn;
-  const int ksteps = p.num_taps * p.cblocks;
-  int err_code = 0;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + b_bytes;
-      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-        const int kt = tile % p.tiles_k;
-        int sp = tile / p.tiles_k;
-        const int q0 = (sp % p.tiles_w) * p.tw;
-        sp /= p.tiles_w;
-        const int p0 = (sp % p.tiles_h) * p.th;
-        const int n0 = (sp / p.tiles_h) * p.tn;
-        const int k0 = kt * BN;
-        for (int t = 0; t < p.num_taps && !err_code; ++t) {
-          const TcTap tap = p.taps[t];
-          for (int cb = 0; cb < p.cblocks; ++cb) {
-            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
-              err_code = 1;
-              break;
-            }
-            mbar_expect_tx(full_bar(stage), tx_bytes);
-            tma_load_4d(sA + stage * a_bytes, &p.tmA[tap.map], full_bar(stage), cb * bk,
-                        q0 + tap.dw, p0 + tap.dh, n0);
-            tma_load_3d(sB + stage * b_bytes, &p.tmB, full_bar(stage), cb * bk, k0, t);
-            if (++stage == stages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          err_code = 2;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        uint32_t accumulate = 0;
-        for (int ks = 0; ks < ksteps; ++ks) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-            err_code = 3;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
-          const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
-          for (int kk = 0; kk < bk / 16; ++kk) {
-            tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
-                        accumulate);
-            accumulate = 1;
-          }
-          tc_commit(empty_bar(stage));
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-        if (err_code) break;
-        tc_commit(tfull_bar(acc));
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-      }
-    }
-  } else {
-    // ------------------------------------------------------------ epilogue (8 warps)
-    // Two warps share each TMEM lane quadrant and split a slab's channels between them.
-    const float act_lo = p.lo, act_hi = p.hi;
-    const int quad = warp & 3;               // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;        // which half of the slab's channels
-    const int row = quad * 32 + lane;        // accumulator row == pixel index in the tile
-    const int et = threadIdx.x - 64;         // 0..255
-    const bool leader = et == 0;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    uint32_t d_iter = 0;
-    // Residual slabs are TMA-loaded into the output slab buffers ahead of time (the
-    // epilogue then adds in place).  `pf_*` walks the same (tile, slab) sequence as the
-    // main loop, up to TC_DBUF - 1 slabs ahead; only the leader uses it.
-    uint32_t r_issued = 0;
-    int pf_tile = blockIdx.x, pf_sl = 0;
-    auto prefetch_residual = [&](uint32_t upto) {
-      while (r_issued <= upto && pf_tile < p.total_tiles) {
-        const int kt = pf_tile % p.tiles_k;
-        int sp = pf_tile / p.tiles_k;
-        const int q0 = (sp % p.tiles_w) * p.tw;
-        sp /= p.tiles_w;
-        const int p0 = (sp % p.tiles_h) * p.th;
-        const int n0 = (sp / p.tiles_h) * p.tn;
-        const int k0 = kt * BN;
-        const int ns = min(NSLAB, (p.K - k0 + DC - 1) / DC);
-        const uint32_t b = r_issued % TC_DBUF;
-        mbar_expect_tx(rfull_bar(b), (uint32_t)rows_valid * DC * 2u);
-        tma_load_4d(sD + b * SLAB_BYTES, &p.tmR, rfull_bar(b), k0 + pf_sl * DC, q0, p0, n0);
-        ++r_issued;
-        if (++pf_sl == ns) {
-          pf_sl = 0;
-          pf_tile += gridDim.x;
-        }
-      }
-    };
-    if (p.has_res && leader) prefetch_residual(TC_DBUF - 1);
-    for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-      const int kt = tile % p.tiles_k;
-      int sp = tile / p.tiles_k;
-      const int q0 = (sp % p.tiles_w) * p.tw;
-      sp /= p.tiles_w;
-      const int p0 = (sp % p.tiles_h) * p.th;
-      const int n0 = (sp / p.tiles_h) * p.tn;
-      const int k0 = kt * BN;
-      const int nslab = min(NSLAB, (p.K - k0 + DC - 1) / DC);
-      for (int i = et; i < BN; i += TC_EPI_THREADS)
-        bias_s[i] = (p.bias && k0 + i < p.K) ? p.bias[k0 + i] : 0.0f;
-      epi_bar();
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
-        err_code = 4;
-        break;
-      }
-      tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) +
-                             (uint32_t)(acc * BN + half * CW);
-      uint32_t rr[2][CW];
-      tc_ld<CW>(t_row, rr[0]);
-#pragma unroll
-      for (int sl = 0; sl < NSLAB; ++sl) {
-        if (sl >= nslab) break;
-        tc_ld_wait();
-        if (sl + 1 < nslab) {
-          tc_ld<CW>(t_row + (uint32_t)((sl + 1) * DC), rr[(sl + 1) & 1]);
-        } else {
-          // every TMEM read of this tile has landed: the MMA warp may overwrite the buffer
-          tc_fence_before();
-          mbar_arrive(tempty_bar(acc));
-        }
-        const uint32_t *r = rr[sl & 1];
-        const int cbase = sl * DC + half * CW;   // first of this thread's channels in the tile
-        float v[CW];
-#pragma unroll
-        for (int j = 0; j < CW; ++j) v[j] = __uint_as_float(r[j]) + bias_s[cbase + j];
-        const uint32_t dbuf = sD + (d_iter % TC_DBUF) * SLAB_BYTES;
-        uint8_t *dptr = base_ptr + (dbuf - base);
-        if (p.has_res) {
-          if (!mbar_wait(rfull_bar(d_iter % TC_DBUF), (d_iter / TC_DBUF) & 1u, abort_flag)) {
-            err_code = 5;
-            break;
-          }
-#pragma unroll
-          for (int c4 = 0; c4 < CW / 8; ++c4) {
-            const uint4 rv = *reinterpret_cast<const uint4 *>(
-                dptr + slab_off(row, half * (CW / 8) + c4, DC * 2));
-            const uint32_t w4[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f =
-                  __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w4[e]));
-              v[c4 * 8 + e * 2] += f.x;
-              v[c4 * 8 + e * 2 + 1] += f.y;
-            }
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < CW; ++j) v[j] = tc_act(v[j], act_lo, act_hi);
-        if (p.out_f32) {
-          const int m = q0 + row;
-          if (row < rows_valid && m < p.m_total) {
-            float *o = p.out_f32 + (int64_t)m * p.ldo + k0 + cbase;
-#pragma unroll
-            for (int j = 0; j < CW; ++j)
-              if (k0 + cbase + j < p.K) o[j] = v[j];
-          }
-        } else {
-          // Slab buffer d_iter % TC_DBUF is free: its previous store (d_iter - TC_DBUF) was
-          // waited for by the leader before it arrived at the barrier of slab d_iter - 1.
-#pragma unroll
-          for (int c4 = 0; c4 < CW / 8; ++c4) {
-            uint4 pk;
-            __nv_bfloat162 b0 = __floats2bfloat162_rn(v[c4 * 8 + 0], v[c4 * 8 + 1]);
-            __nv_bfloat162 b1 = __floats2bfloat162_rn(v[c4 * 8 + 2], v[c4 * 8 + 3]);
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(v[c4 * 8 + 4], v[c4 * 8 + 5]);
-            __nv_bfloat162 b3 = __floats2bfloat162_rn(v[c4 * 8 + 6], v[c4 * 8 + 7]);
-            pk.x = *reinterpret_cast<uint32_t *>(&b0);
-            pk.y = *reinterpret_cast<uint32_t *>(&b1);
-            pk.z = *reinterpret_cast<uint32_t *>(&b2);
-            pk.w = *reinterpret_cast<uint32_t *>(&b3);
-            *reinterpret_cast<uint4 *>(dptr + slab_off(row, half * (CW / 8) + c4, DC * 2)) = pk;
-          }
-          fence_async_smem();
-          epi_bar();
-          if (leader) {
-            tma_store_4d(&p.tmD, dbuf, k0 + sl * DC, q0, p0, n0);
-            tma_store_commit();
-            tma_store_wait_read<TC_DBUF - 2>();
-            // the buffer of slab d_iter - 1 has been read out: the residual of slab
-            // d_iter + TC_DBUF - 1 may land there
-            if (p.has_res) prefetch_residual(d_iter + TC_DBUF - 1);
-          }
-          ++d_iter;
-        }
-      }
-      if (err_code) break;
-      if (p.out_f32) epi_bar();   // bias_s is rewritten at the top of the next tile
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
-    }
-    if (leader) tma_store_wait_read<0>();
-  }
-
-  if (err_code) {
-    atomicExch(p.err, 1000 + err_code);
-    *abort_flag = 1;
-    // let copies that are still in flight land before shared memory is given back
-    for (int i = 0; i < 50; ++i) __nanosleep(20000);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(TMEM_COLS)
-                 : "memory");
-  }
-}
 
 // ------------------------------------------------------------------ pixel-N variant
 // One tcgen05.mma takes the same ~155 cycles whatever its N, so a layer with few output
@@ -590,7 +104,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
         for (int t = 0; t < p.num_taps && !err_code; ++t) {
           const TcTap tap = p.taps[t];
           for (int cb = 0; cb < p.cblocks; ++cb) {
-            if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            if (!mbar_wait_hot(empty_bar(stage), phase ^ 1u, abort_flag)) {
               err_code = 1;
               break;
             }
@@ -613,7 +127,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+        if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           err_code = 2;
           break;
         }
@@ -621,7 +135,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
         uint32_t accumulate = 0;
         for (int ks = 0; ks < ksteps; ++ks) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+          if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
             err_code = 3;
             break;
           }
@@ -681,13 +195,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
         }
       }
       epi_bar();
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+      if (!mbar_wait_hot(tfull_bar(acc), acc_phase, abort_flag)) {
         err_code = 4;
         break;
       }
       tc_fence_after();
       if (p.has_res) {
-        if (!mbar_wait(rfull_bar, r_phase, abort_flag)) {
+        if (!mbar_wait_hot(rfull_bar, r_phase, abort_flag)) {
           err_code = 5;
           break;
         }
@@ -864,6 +378,7 @@ bool tc_conv_supported(const TcConvArgs &a) {
   if (pick_bk(a.Cf) == 0) return false;
   if (a.act != ACT_IDENTITY && a.act != ACT_RELU && a.act != ACT_CLIP) return false;
   if (a.stride_h < 1 || a.stride_w < 1 || a.stride_h > 2 || a.stride_w > 2) return false;
+  if (a.w_step && ((a.w_step * 2) % 16 || (a.row_elems * 2) % 16 || a.S != 1)) return false;
   if (a.R * a.S > TC_MAX_TAPS) return false;
   if (!a.out_f32 && a.K % 8 != 0) return false;
   if (a.out_f32 && !(a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 &&
@@ -872,6 +387,7 @@ bool tc_conv_supported(const TcConvArgs &a) {
   if ((uintptr_t)a.x % 16 || (uintptr_t)a.w % 16) return false;
   if (a.y && (uintptr_t)a.y % 16) return false;
   if ((int64_t)a.N * a.P * a.Q >= (1ll << 31)) return false;
+  if (a.K > 4096) return false;   // the bias vector has to fit in shared memory
   return true;
 }
 
@@ -889,12 +405,23 @@ struct ArgsKeyHash {
 };
 struct Plan {
   TcParams p;
+  int mode;  // TC_MODE_* of the pixel-M kernel
   int bn;
   int dc;    // channels per output slab
   bool pn;   // pixel-N variant
   size_t smem;
   bool ok;
 };
+
+static TcFastDiv make_fastdiv(int d) {
+  TcFastDiv f{0u, 0u};
+  if (d <= 1) return f;
+  int s = 0;
+  while ((1ll << s) < d) ++s;                    // s = ceil(log2 d)
+  f.mul = (uint32_t)((((uint64_t)1 << (31 + s)) + d - 1) / d);
+  f.shift = (uint32_t)(s - 1);
+  return f;
+}
 
 static int floordiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
@@ -915,7 +442,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
   p.ldo = a.ldo;
   p.err = err_word;
   const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
-                    a.pad_w == 0;
+                    a.pad_w == 0 && a.w_step == 0;
   // output grid the tiles are cut from
   int Qg = a.Q, Pg = a.P, Ng = a.N;
   if (flat) {
@@ -940,11 +467,15 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
   p.tiles_n = (Ng + p.tn - 1) / p.tn;
   const int nsm = num_sms > 0 ? num_sms : 148;
   const int bn = pn ? 128
+                    : a.out_f32 ? (a.K > 32 ? 64 : 32)   // the fp32 head is compiled for these only
                     : pick_bn(a.K, (long)p.tiles_w * p.tiles_h * p.tiles_n,
                               (a.R * a.S * a.Cf + 63) / 64, nsm);
   pl.bn = bn;
   p.tiles_k = (a.K + bn - 1) / bn;
   p.total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_k;
+  p.div_k = make_fastdiv(p.tiles_k);
+  p.div_w = make_fastdiv(p.tiles_w);
+  p.div_h = make_fastdiv(p.tiles_h);
 
   const uint32_t boxA[4] = {(uint32_t)bk, (uint32_t)p.tw, (uint32_t)p.th, (uint32_t)p.tn};
   bool ok = true;
@@ -967,11 +498,15 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
         const int aw = floordiv(ew, sw), bw = ew - aw * sw;
         if (map_of[bh][bw] < 0) {
           const int Hm = (a.H - bh + sh - 1) / sh, Wm = (a.W - bw + sw - 1) / sw;
-          const bf16 *ptr = a.x + ((int64_t)bh * a.W + bw) * a.Cf;
+          // elements from one pixel to the next and from one row to the next (the folded
+          // form's pixels are overlapping windows of a padded row)
+          const int64_t px = a.w_step ? a.w_step : a.Cf;
+          const int64_t rowe = a.row_elems ? a.row_elems : (int64_t)a.W * a.Cf;
+          const bf16 *ptr = a.x + bh * rowe + bw * px;
           const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)(Wm > 0 ? Wm : 1),
                                     (uint64_t)(Hm > 0 ? Hm : 1), (uint64_t)a.N};
-          const uint64_t st[3] = {(uint64_t)sw * a.Cf * 2, (uint64_t)sh * a.W * a.Cf * 2,
-                                  (uint64_t)a.H * a.W * a.Cf * 2};
+          const uint64_t st[3] = {(uint64_t)(sw * px * 2), (uint64_t)(sh * rowe * 2),
+                                  (uint64_t)(a.H * rowe * 2)};
           ok &= make_map(&p.tmA[nmaps], ptr, 4, dims, st, boxA, bk * 2);
           map_of[bh][bw] = nmaps++;
         }
@@ -989,6 +524,8 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
   const int ksteps64 = (a.R * a.S * a.Cf + 63) / 64;
   const int dc = pn ? 64 : (bn < 64 ? bn : (bn == 256 && bk == 64 && ksteps64 >= 16 ? 32 : 64));
   pl.dc = dc;
+  pl.mode = a.out_f32 ? (TC_MODE_F32 | TC_MODE_CLAMP)
+                      : ((a.residual ? TC_MODE_RES : 0) | (a.act == ACT_RELU ? 0 : TC_MODE_CLAMP));
   if (!a.out_f32) {
     const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
     const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};
@@ -996,34 +533,37 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
     ok &= make_map(&p.tmD, a.y, 4, dims, st, box, dc * 2);
     if (a.residual) ok &= make_map(&p.tmR, a.residual, 4, dims, st, box, dc * 2);
   }
-  // shared memory: ring + output slabs (+ residual slabs) + bias + barriers + alignment
+  // shared memory: ring + output slabs + bias + barriers + alignment
   const size_t stage_bytes = pn ? (size_t)(128 + 256) * bk * 2 : 128 * bk * 2 + (size_t)bn * bk * 2;
-  const size_t fixed = pn ? 1024 + 2 * 256 * 128 + 8 * 80
-                          : 1024 + (size_t)TC_DBUF * 128 * dc * 2 + bn * 4 + 8 * 80;
-  int stages = (int)((TC_SMEM_LIMIT - fixed) / stage_bytes);
+  p.bias_floats = (a.K + bn - 1) / bn * bn;
+  const size_t slab_bytes = (size_t)128 * dc * 2;
+  const size_t fixed0 = pn ? 1024 + 2 * 256 * 128 + 8 * 80 : 1024 + (size_t)p.bias_floats * 4 + 8 * 80;
+  int dbuf = pn ? 0 : 3;
+  int stages;
+  if (!pn && a.residual) {
+    // The residual slab of an output slab is fetched into its buffer ahead of time; with
+    // short reductions a slab is consumed faster than the fetch takes, so those layers
+    // trade ring stages (down to what one tile needs, at least two) for slab buffers.
+    const int ks = a.R * a.S * (a.Cf / bk);
+    int min_stages = ks < 3 ? 2 : 3;
+    dbuf = (int)((TC_SMEM_LIMIT - fixed0 - min_stages * stage_bytes) / slab_bytes);
+    if (dbuf > 8) dbuf = 8;
+    if (dbuf < 3) dbuf = 3;
+  }
+  const size_t fixed = fixed0 + dbuf * slab_bytes;
+  stages = (int)((TC_SMEM_LIMIT - fixed) / stage_bytes);
   if (stages > 8) stages = 8;
   if (stages < 2) ok = false;
   p.stages = stages;
+  p.dbuf = dbuf;
   pl.smem = fixed + stages * stage_bytes;
   if (pl.smem < 120 * 1024) pl.smem = 120 * 1024;  // keep one CTA per SM (TMEM is per SM)
   if (getenv("OCCAMY_TC_PLAN_LOG"))
-    fprintf(stderr, "[tcplan] K %d Cf %d RS %d px %dx%dx%d box %dx%dx%d bn %d dc %d pn %d bk %d stages %d tiles %d smem %zu\n",
-            a.K, a.Cf, a.R * a.S, Qg, Pg, Ng, p.tw, p.th, p.tn, bn, dc, (int)pn, bk, stages,
+    fprintf(stderr, "[tcplan] K %d Cf %d RS %d px %dx%dx%d box %dx%dx%d bn %d dc %d pn %d bk %d stages %d dbuf %d tiles %d smem %zu\n",
+            a.K, a.Cf, a.R * a.S, Qg, Pg, Ng, p.tw, p.th, p.tn, bn, dc, (int)pn, bk, stages, dbuf,
             p.total_tiles, pl.smem);
   pl.ok = ok;
   return pl;
-}
-
-template <int BN, int DC>
-static void launch_plan_on(const Plan &pl, int num_sms, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    OCC_CUDA(cudaFuncSetAttribute(tc_conv_kernel<BN, DC>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT));
-    attr_set = true;
-  }
-  int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
-  tc_conv_kernel<BN, DC><<<grid, TC_THREADS, pl.smem, s>>>(pl.p);
 }
 
 static void launch_plan_pn(const Plan &pl, int num_sms, cudaStream_t s) {
@@ -1042,15 +582,18 @@ static void launch_any(const Plan &pl, int num_sms, cudaStream_t s) {
     launch_plan_pn(pl, num_sms, s);
     return;
   }
+  const int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
+  bool ok;
   switch (pl.bn) {
-    case 32: launch_plan_on<32, 32>(pl, num_sms, s); break;
-    case 64: launch_plan_on<64, 64>(pl, num_sms, s); break;
-    case 128: launch_plan_on<128, 64>(pl, num_sms, s); break;
+    case 32: ok = tc_launch_32_32(pl.p, pl.mode, grid, pl.smem, s); break;
+    case 64: ok = tc_launch_64_64(pl.p, pl.mode, grid, pl.smem, s); break;
+    case 128: ok = tc_launch_128_64(pl.p, pl.mode, grid, pl.smem, s); break;
     default:
-      if (pl.dc == 32) launch_plan_on<256, 32>(pl, num_sms, s);
-      else launch_plan_on<256, 64>(pl, num_sms, s);
+      ok = pl.dc == 32 ? tc_launch_256_32(pl.p, pl.mode, grid, pl.smem, s)
+                       : tc_launch_256_64(pl.p, pl.mode, grid, pl.smem, s);
       break;
   }
+  if (!ok) set_error(997, "tensor-core conv: no kernel for this tile shape and epilogue");
 }
 
 void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {

@@ -1,0 +1,721 @@
+// Device side of the tcgen05 implicit-GEMM convolution: parameter block, PTX wrappers and
+// the pixel-M kernel template.  Included by the translation units that instantiate the
+// kernel (one per tile shape, so that they compile in parallel) and by the host planner.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+
+namespace occ {
+
+constexpr int TC_THREADS = 320;      // pixel-N kernel: 1 producer warp + 1 MMA warp + 8 epilogue warps
+constexpr int TC_EW = 2;             // tc_conv_kernel: epilogue warps per TMEM lane quadrant
+constexpr int TC_EPI_THREADS = 256;
+constexpr int TC_DBUF = 3;           // output slab buffers in shared memory
+constexpr int TC_MAX_TAPS = 32;
+constexpr int TC_SMEM_LIMIT = 232448;  // 227 KB
+
+// Division of a tile index (< 2^31) by a positive constant: q = umulhi(x, mul) >> shift,
+// with mul == 0 standing for a divisor of one.
+struct TcFastDiv {
+  uint32_t mul, shift;
+};
+
+struct TcTap {
+  int map, dw, dh;
+};
+
+struct alignas(64) TcParams {
+  CUtensorMap tmA[4];
+  CUtensorMap tmB;
+  CUtensorMap tmD;
+  CUtensorMap tmR;
+  TcTap taps[TC_MAX_TAPS];
+  int num_taps, cblocks, bk, stages;
+  int tiles_w, tiles_h, tiles_n, tiles_k, total_tiles;
+  TcFastDiv div_k, div_w, div_h;   // divisions by tiles_k / tiles_w / tiles_h
+  int tw, th, tn, K;
+  const float *bias;
+  int has_res, act;
+  int gq, gp, gn;        // extents of the output grid the tiles are cut from
+  float lo, hi;
+  float *out_f32;
+  int ldo;
+  int m_total;
+  int bias_floats;       // K rounded up to whole channel tiles: bias entries kept in shared memory
+  int dbuf;              // output slab buffers in shared memory (3..8)
+  int n_mma;             // pixel-N variant: N of the MMA (pixels per tile rounded up to 16)
+  int *err;
+};
+
+// Epilogue flavours the pixel-M kernel is compiled for (template parameter MODE).
+constexpr int TC_MODE_RES = 1;     // adds a residual tensor
+constexpr int TC_MODE_CLAMP = 2;   // general clamp to [lo, hi]; otherwise ReLU
+constexpr int TC_MODE_F32 = 4;     // fp32 row-major output straight to global memory (GEMM head)
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t cnt) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(cnt));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t a, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t a) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t a, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(a), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~2 s of polling or as soon as another role has given up.
+// The polling loop is kept out of line: every role has several waits, and the kernel's code
+// has to stay small enough for the instruction cache.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t a, uint32_t parity, volatile int *abort_flag) {
+  const long long t0 = clock64();
+  int it = 0;
+  while (!mbar_try(a, parity)) {
+    if ((++it & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try(a, parity)) return true;
+  return mbar_wait_slow(a, parity, abort_flag);
+}
+// The same wait, polling loop inline: for the producer and MMA roles, whose loops are tiny
+// and where the return from a call would sit on the critical path of every k-step.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t a, uint32_t parity,
+                                              volatile int *abort_flag) {
+  if (mbar_try(a, parity)) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (!mbar_try(a, parity)) {
+    if ((++it & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *m, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, uint32_t src, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(m),
+      "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Two fp32 values in one 64-bit register (packed fp32 arithmetic of sm_100).
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float &a, float &b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// (a, b) -> bf16x2 with a in the low half; the second form clamps negatives to zero.
+__device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {
+  float a, b;
+  f2_unpack(v, a, b);
+  uint32_t r;
+#ifdef OCCAMY_TC_EXP_TRUNC
+  r = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);
+#else
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+#endif
+  return r;
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2_relu(uint64_t v) {
+  float a, b;
+  f2_unpack(v, a, b);
+  uint32_t r;
+#ifdef OCCAMY_TC_EXP_TRUNC
+  r = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);
+#else
+  asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+#endif
+  return r;
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
+template <int W>
+__device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t *r) {
+  if constexpr (W == 32) tc_ld32(taddr, r);
+  else if constexpr (W == 16) tc_ld16(taddr, r);
+  else tc_ld8(taddr, r);
+}
+__device__ __forceinline__ void tc_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+template <int THREADS>
+__device__ __forceinline__ void epi_bar_n() {
+  asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major bf16 tile whose rows are `bk` elements
+// (32 / 64 / 128 bytes, swizzled with the matching 32B / 64B / 128B pattern): 8-row groups
+// are 8*bk*2 bytes apart; descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk) {
+  const uint32_t sbo = (uint32_t)(8 * bk * 2);
+  const uint64_t layout = bk == 64 ? 2ull : (bk == 32 ? 4ull : 6ull);
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(sbo >> 4) << 32) |
+         (1ull << 46) | (layout << 61);
+}
+
+// The fused activations (identity, ReLU, clipped ReLU) are all a clamp to [lo, hi]; keeping
+// the epilogue to that one form keeps its unrolled body small.
+__device__ __forceinline__ float tc_act(float v, float lo, float hi) {
+  return fminf(fmaxf(v, lo), hi);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` inside a staged slab whose rows are
+// `row_bytes` (64 or 128) long, with the TMA swizzle of that width applied.
+__device__ __forceinline__ uint32_t slab_off(int row, int chunk, int row_bytes) {
+  const uint32_t off = (uint32_t)(row * row_bytes + chunk * 16);
+  const uint32_t mask = (uint32_t)(row_bytes / 16 - 1);
+  return off ^ (((off >> 7) & mask) << 4);
+}
+
+// ------------------------------------------------------------------ tile walk
+__device__ __forceinline__ uint32_t tc_fdiv(uint32_t x, TcFastDiv d) {
+  return d.mul ? (__umulhi(x, d.mul) >> d.shift) : x;
+}
+struct TcTile {
+  int k0, q0, p0, n0;   // first output channel / column / row / image of the tile
+};
+// Tiles are numbered channel-tile fastest, then column, row and image tiles.
+template <int BN>
+__device__ __forceinline__ TcTile tc_decode(const TcParams &p, int tile) {
+  const uint32_t sp = tc_fdiv((uint32_t)tile, p.div_k);
+  const uint32_t kt = (uint32_t)tile - sp * (uint32_t)p.tiles_k;
+  const uint32_t s2 = tc_fdiv(sp, p.div_w);
+  const uint32_t wq = sp - s2 * (uint32_t)p.tiles_w;
+  const uint32_t nn = tc_fdiv(s2, p.div_h);
+  const uint32_t hp = s2 - nn * (uint32_t)p.tiles_h;
+  TcTile t;
+  t.k0 = (int)kt * BN;
+  t.q0 = (int)wq * p.tw;
+  t.p0 = (int)hp * p.th;
+  t.n0 = (int)nn * p.tn;
+  return t;
+}
+
+// ------------------------------------------------------------------ the kernel
+// Pixels are the M side of the MMA (128 per tile), output channels the N side (BN per tile).
+//   DC   channels per staged output slab (64; 32 trades slab size for ring depth)
+//   EW   epilogue warps per TMEM lane quadrant; they split a slab's channels between them
+//   MODE epilogue flavour (TC_MODE_* bits); one flavour per instantiation keeps the code of
+//        a launch small, which matters: the roles run different code at the same time and
+//        instruction-cache misses stall all of them
+//
+// One persistent CTA per SM:
+//   warp 0            TMA producer (one lane): fills a ring of {A, B} stages
+//   warp 1            MMA issuer (one lane): tcgen05.mma 128 x BN x 16, fp32 accumulators in
+//                     TMEM, two accumulator buffers
+//   warps 2..2+4*EW   epilogue: tcgen05.ld the finished accumulator, add bias / residual,
+//                     activation, convert to bf16, write 128-pixel slabs of DC channels into
+//                     swizzled shared memory
+//   last warp         slab store (one lane): hands slab buffers to the epilogue (empty, or
+//                     pre-loaded with the residual slab) and TMA-stores written slabs
+// Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in the
+// error word, drains and returns.
+template <int BN, int DC, int EW, int MODE>
+__global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
+    tc_conv_kernel(const __grid_constant__ TcParams p) {
+  constexpr bool RES = (MODE & TC_MODE_RES) != 0;
+  constexpr bool CLAMP = (MODE & TC_MODE_CLAMP) != 0;
+  constexpr bool F32 = (MODE & TC_MODE_F32) != 0;
+  constexpr int EPI_THREADS = 128 * EW;
+  constexpr int STORE_WARP = 2 + 4 * EW;
+  constexpr int CW = DC / EW;                  // channels one epilogue thread handles per slab
+  constexpr int NSLAB = BN / DC;
+  constexpr int SLAB_BYTES = 128 * DC * 2;
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(128 >> 4) << 24);
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const int bk = p.bk, stages = p.stages, dbuf = p.dbuf;
+  const uint32_t a_bytes = 128u * bk * 2u, b_bytes = (uint32_t)BN * bk * 2u;
+  const uint32_t sA = base;
+  const uint32_t sB = sA + stages * a_bytes;
+  const uint32_t sD = sB + stages * b_bytes;                    // dbuf output slabs
+  const uint32_t sMisc = sD + dbuf * SLAB_BYTES;
+  uint8_t *misc_ptr = base_ptr + (sMisc - base);
+  float *bias_s = reinterpret_cast<float *>(misc_ptr);          // bias of every output channel
+  uint64_t *bars = reinterpret_cast<uint64_t *>(misc_ptr + p.bias_floats * 4);
+  const uint32_t bar0 = sMisc + p.bias_floats * 4;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
+  auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + s); };
+  auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * stages + 2 + s); };
+  auto rfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + 4 + s); };
+  auto dfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + 4 + dbuf + s); };
+  volatile uint32_t *tmem_holder =
+      reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 4 + 2 * dbuf);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 5 + 2 * dbuf);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    // descriptor fetches are off the critical path of the first loads / stores
+    tma_prefetch_map(&p.tmA[0]);
+    tma_prefetch_map(&p.tmB);
+    if (!F32) tma_prefetch_map(&p.tmD);
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      // one arrival per epilogue warp: arrivals on one barrier are serialised
+      mbar_init(tempty_bar(s), EPI_THREADS / 32);
+    }
+    for (int s = 0; s < dbuf; ++s) {
+      mbar_init(rfull_bar(s), 1);
+      mbar_init(dfull_bar(s), EPI_THREADS / 32);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32((const void *)tmem_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int rows_valid = p.tw * p.th * p.tn;
+  const int ksteps = p.num_taps * p.cblocks;
+  int err_code = 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + b_bytes;
+      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+        const TcTile tl = tc_decode<BN>(p, tile);
+        for (int t = 0; t < p.num_taps && !err_code; ++t) {
+          const TcTap tap = p.taps[t];
+          for (int cb = 0; cb < p.cblocks; ++cb) {
+            if (!mbar_wait_hot(empty_bar(stage), phase ^ 1u, abort_flag)) {
+              err_code = 1;
+              break;
+            }
+            mbar_expect_tx(full_bar(stage), tx_bytes);
+            tma_load_4d(sA + stage * a_bytes, &p.tmA[tap.map], full_bar(stage), cb * bk,
+                        tl.q0 + tap.dw, tl.p0 + tap.dh, tl.n0);
+            tma_load_3d(sB + stage * b_bytes, &p.tmB, full_bar(stage), cb * bk, tl.k0, t);
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+        if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          err_code = 2;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        uint32_t accumulate = 0;
+        for (int ks = 0; ks < ksteps; ++ks) {
+          if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
+            err_code = 3;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
+          const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
+          for (int kk = 0; kk < bk / 16; ++kk) {
+            tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
+                        accumulate);
+            accumulate = 1;
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (err_code) break;
+        tc_commit(tfull_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp == STORE_WARP) {
+    // ------------------------------------------------------------ slab store
+    // One thread owns the output slab buffers: it hands a buffer to the epilogue warps
+    // ("ready": free, or holding the residual slab the epilogue adds in place), and sends a
+    // written slab to global memory.  The epilogue warps never wait for one another.
+    if constexpr (!F32) {
+      if (lane == 0) {
+        uint32_t n_ready = 0, rb = 0;      // slabs handed out so far; buffer of the next one
+        int pf_tile = blockIdx.x, pf_sl = 0;
+        TcTile pf = tc_decode<BN>(p, pf_tile);
+        auto make_ready = [&](uint32_t upto) {
+          while (n_ready <= upto && pf_tile < p.total_tiles) {
+            if constexpr (RES) {
+              mbar_expect_tx(rfull_bar(rb), (uint32_t)rows_valid * DC * 2u);
+              tma_load_4d(sD + rb * SLAB_BYTES, &p.tmR, rfull_bar(rb), pf.k0 + pf_sl * DC, pf.q0,
+                          pf.p0, pf.n0);
+            } else {
+              mbar_arrive(rfull_bar(rb));
+            }
+            ++n_ready;
+            if (++rb == (uint32_t)dbuf) rb = 0;
+            if (++pf_sl == min(NSLAB, (p.K - pf.k0 + DC - 1) / DC)) {
+              pf_sl = 0;
+              pf_tile += gridDim.x;
+              pf = tc_decode<BN>(p, pf_tile);
+            }
+          }
+        };
+        make_ready(dbuf - 1);
+        uint32_t d_iter = 0, b = 0, ph = 0;
+        for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+          const TcTile tl = tc_decode<BN>(p, tile);
+          const int nslab = min(NSLAB, (p.K - tl.k0 + DC - 1) / DC);
+          for (int sl = 0; sl < nslab; ++sl) {
+            if (!mbar_wait(dfull_bar(b), ph, abort_flag)) {
+              err_code = 6;
+              break;
+            }
+            tma_store_4d(&p.tmD, sD + b * SLAB_BYTES, tl.k0 + sl * DC, tl.q0, tl.p0, tl.n0);
+            tma_store_commit();
+            // once at most dbuf - 2 stores are still reading, the buffer of slab
+            // d_iter - (dbuf - 2) is free and slab d_iter + 2 may use it
+            switch (dbuf) {
+              case 3: tma_store_wait_read<1>(); break;
+              case 4: tma_store_wait_read<2>(); break;
+              case 5: tma_store_wait_read<3>(); break;
+              case 6: tma_store_wait_read<4>(); break;
+              case 7: tma_store_wait_read<5>(); break;
+              default: tma_store_wait_read<6>(); break;
+            }
+            make_ready(d_iter + 2);
+            ++d_iter;
+            if (++b == (uint32_t)dbuf) {
+              b = 0;
+              ph ^= 1u;
+            }
+          }
+        }
+        tma_store_wait_read<0>();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 * EW warps)
+    const int quad = warp & 3;               // TMEM lane quadrant this warp may read
+    const int part = (warp - 2) >> 2;        // which part of a slab's channels
+    const int row = quad * 32 + lane;        // accumulator row == pixel index in the tile
+    const int et = threadIdx.x - 64;         // 0..EPI_THREADS-1
+    // swizzled offsets of this thread's 16-byte pieces inside a slab buffer
+    uint32_t soff[CW / 8];
+#pragma unroll
+    for (int c4 = 0; c4 < CW / 8; ++c4) soff[c4] = slab_off(row, part * (CW / 8) + c4, DC * 2);
+    // The whole bias vector goes to shared memory once: a global load per tile would put
+    // the memory latency on every tile's critical path.
+    for (int i = et; i < p.bias_floats; i += EPI_THREADS)
+      bias_s[i] = (p.bias && i < p.K) ? p.bias[i] : 0.0f;
+    epi_bar_n<EPI_THREADS>();
+    const float act_lo = p.lo, act_hi = p.hi;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint32_t buf = 0, buf_phase = 0;         // slab buffer the next slab goes through
+
+    for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+      const TcTile tl = tc_decode<BN>(p, tile);
+      const int nslab = min(NSLAB, (p.K - tl.k0 + DC - 1) / DC);
+      const float *bias_t = bias_s + tl.k0 + part * CW;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+        err_code = 4;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) +
+                             (uint32_t)(acc * BN + part * CW);
+      // every TMEM read of this tile has landed: the MMA warp may overwrite the buffer
+      auto release_acc = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+      };
+      // one slab: r holds this thread's CW accumulator columns of slab sl
+      auto slab = [&](const uint32_t *r, int sl) -> bool {
+        uint64_t v2[CW / 2];   // two channels per 64-bit register: packed fp32 adds
+        {
+          const float4 *b4 = reinterpret_cast<const float4 *>(bias_t + sl * DC);
+#pragma unroll
+          for (int j = 0; j < CW / 4; ++j) {
+            const float4 b = b4[j];
+            v2[2 * j] = f2_add(f2_pack(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1])),
+                               f2_pack(b.x, b.y));
+            v2[2 * j + 1] =
+                f2_add(f2_pack(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])),
+                       f2_pack(b.z, b.w));
+          }
+        }
+        if constexpr (F32) {
+          const int m = tl.q0 + row;
+          const int c0 = tl.k0 + sl * DC + part * CW;
+          if (row < rows_valid && m < p.m_total) {
+            float *o = p.out_f32 + (int64_t)m * p.ldo + c0;
+#pragma unroll
+            for (int j = 0; j < CW / 2; ++j) {
+              float a, b;
+              f2_unpack(v2[j], a, b);
+              if (c0 + 2 * j < p.K) o[2 * j] = tc_act(a, act_lo, act_hi);
+              if (c0 + 2 * j + 1 < p.K) o[2 * j + 1] = tc_act(b, act_lo, act_hi);
+            }
+          }
+          return true;
+        } else {
+          // the buffer is free, or (residual) holds the slab to add
+          if (!mbar_wait(rfull_bar(buf), buf_phase, abort_flag)) return false;
+          uint8_t *dptr = base_ptr + (sD - base) + buf * SLAB_BYTES;
+          if constexpr (RES) {
+#pragma unroll
+            for (int c4 = 0; c4 < CW / 8; ++c4) {
+              const uint4 rv = *reinterpret_cast<const uint4 *>(dptr + soff[c4]);
+              const uint32_t w4[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e)   // a bf16 is the top half of the fp32 of its value
+                v2[c4 * 4 + e] = f2_add(v2[c4 * 4 + e],
+                                        f2_pack(__uint_as_float(w4[e] << 16),
+                                                __uint_as_float(w4[e] & 0xffff0000u)));
+            }
+          }
+          uint32_t pk[CW / 2];
+#pragma unroll
+          for (int j = 0; j < CW / 2; ++j) {
+            if constexpr (CLAMP) {
+              float a, b;
+              f2_unpack(v2[j], a, b);
+              pk[j] = f2_to_bf16x2(f2_pack(tc_act(a, act_lo, act_hi), tc_act(b, act_lo, act_hi)));
+            } else {
+              pk[j] = f2_to_bf16x2_relu(v2[j]);   // ReLU rides on the conversion
+            }
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < CW / 8; ++c4)
+            *reinterpret_cast<uint4 *>(dptr + soff[c4]) =
+                make_uint4(pk[c4 * 4], pk[c4 * 4 + 1], pk[c4 * 4 + 2], pk[c4 * 4 + 3]);
+          // this warp's part of the slab is written: tell the store thread
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dfull_bar(buf));
+          if (++buf == (uint32_t)dbuf) {
+            buf = 0;
+            buf_phase ^= 1u;
+          }
+          return true;
+        }
+      };
+      // Slabs in pairs, so that the registers of one slab are loaded while the other is
+      // worked on and the loop body (two slabs) stays small.
+      uint32_t ra[CW], rb[CW];
+      tc_ld<CW>(t_row, ra);
+      bool ok = true;
+#pragma unroll 1
+      for (int sl = 0; sl < nslab && ok; sl += 2) {
+        tc_ld_wait();
+        if (sl + 1 < nslab) tc_ld<CW>(t_row + (uint32_t)((sl + 1) * DC), rb);
+        else release_acc();
+        ok = slab(ra, sl);
+        if (sl + 1 < nslab && ok) {
+          tc_ld_wait();
+          if (sl + 2 < nslab) tc_ld<CW>(t_row + (uint32_t)((sl + 2) * DC), ra);
+          else release_acc();
+          ok = slab(rb, sl + 1);
+        }
+      }
+      if (!ok) {
+        err_code = 5;
+        break;
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  if (err_code) {
+    atomicExch(p.err, 1000 + err_code);
+    *abort_flag = 1;
+    // let copies that are still in flight land before shared memory is given back
+    for (int i = 0; i < 50; ++i) __nanosleep(20000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// Launchers of the instantiations, one translation unit per tile shape.  `mode` is a
+// combination of TC_MODE_* the shape is compiled for; false when it is not.
+bool tc_launch_256_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+bool tc_launch_256_32(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+bool tc_launch_128_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+bool tc_launch_64_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+bool tc_launch_32_32(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+
+// Body shared by the launchers: picks the instantiation for `mode`, raises its dynamic
+// shared memory limit once, launches.
+template <int BN, int DC, int MODE>
+inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t s) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(tc_conv_kernel<BN, DC, TC_EW, MODE>,
+                         cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
+    attr_set = true;
+  }
+  tc_conv_kernel<BN, DC, TC_EW, MODE><<<grid, 64 + 128 * TC_EW + 32, smem, s>>>(p);
+}
+template <int BN, int DC, bool WITH_F32>
+inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
+  switch (mode) {
+    case 0: tc_launch_one<BN, DC, 0>(p, grid, smem, s); return true;
+    case TC_MODE_RES: tc_launch_one<BN, DC, TC_MODE_RES>(p, grid, smem, s); return true;
+    case TC_MODE_CLAMP: tc_launch_one<BN, DC, TC_MODE_CLAMP>(p, grid, smem, s); return true;
+    case TC_MODE_RES | TC_MODE_CLAMP:
+      tc_launch_one<BN, DC, TC_MODE_RES | TC_MODE_CLAMP>(p, grid, smem, s);
+      return true;
+    case TC_MODE_F32 | TC_MODE_CLAMP:
+      if constexpr (WITH_F32) {
+        tc_launch_one<BN, DC, TC_MODE_F32 | TC_MODE_CLAMP>(p, grid, smem, s);
+        return true;
+      }
+      return false;
+    default: return false;
+  }
+}
+
+}  // namespace occ

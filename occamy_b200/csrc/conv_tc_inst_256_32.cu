@@ -1,0 +1,11 @@
+// Instantiations of the tcgen05 convolution kernel for 256-channel tiles staged in 32-channel
+// slabs (a translation unit of its own so that the tile shapes compile in parallel).
+#include "conv_tc_dev.cuh"
+
+namespace occ {
+
+bool tc_launch_256_32(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
+  return tc_launch_mode<256, 32, false>(p, mode, grid, smem, s);
+}
+
+}  // namespace occ

@@ -67,14 +67,17 @@ void launch_pack_dw_f32(const float *w, float *out, int C, int R, int S, cudaStr
 // ... and fp32 KCRS with tiny C -> bf16 [R][K][Sp*Cp] (width taps folded into channels).
 void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Sp, int Cp,
                            cudaStream_t s);
-// Input side of the folded form: x fp32 NCHW -> bf16 [N][H][Q][Sp*Cp], where entry
-// (n,h,q,s,c) = x[n,c,h,q*stride_w - pad_w + s] (zero outside the image or for s>=S, c>=C).
-void launch_fold_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Q, int S,
-                            int Sp, int Cp, int pad_w, int stride_w, cudaStream_t s);
+// Input side of the folded form: x fp32 NCHW (C <= Cp) -> bf16 [N][H][Wp][Cp] with pad_w zero
+// pixels on the left of every row and zeros up to Wp on the right.  The A vector of output
+// column q, Cf = Sp*Cp elements starting at pixel q*stride_w, is then a window of the row;
+// windows of neighbouring columns overlap and a tensor map with a pixel stride shorter than
+// its innermost extent reads them in place.
+void launch_pad_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Wp, int Cp,
+                           int pad_w, cudaStream_t s);
 
 // ---- tcgen05 implicit-GEMM convolution / GEMM --------------------------------
 struct TcConvArgs {
-  const bf16 *x;         // A operand: NHWC bf16 [N][H][W][C] (or folded [N][H][Q][Cf])
+  const bf16 *x;         // A operand: NHWC bf16 [N][H][W][C] (or folded rows, see w_step)
   const bf16 *w;         // B operand: packed [T][K][Cf]
   const float *bias;     // [K] or null
   const bf16 *residual;  // NHWC bf16 like the output, or null
@@ -87,6 +90,9 @@ struct TcConvArgs {
   int pad_h, pad_w, stride_h, stride_w;  // stride_w = 1, pad_w = 0 for the folded form
   int act;
   float lo, hi;
+  // Folded form only (else 0): elements between the A vectors of neighbouring output
+  // columns, and elements per input row; the vectors overlap when w_step < Cf.
+  int w_step, row_elems;
 };
 // Returns false when the shape is outside what the kernel supports (caller falls back).
 bool tc_conv_supported(const TcConvArgs &a);

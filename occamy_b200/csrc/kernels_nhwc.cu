@@ -359,54 +359,41 @@ void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S
   count(CNT_LAUNCHES);
 }
 
-// x fp32 NCHW -> bf16 [N][H][Q][Sp*Cp].  One CTA per (n, h) image row: the C input rows
-// are staged in shared memory with coalesced loads, then every thread assembles the
-// Sp*Cp-channel vectors of its output columns and writes them as 16-byte pieces, so a warp
-// writes one contiguous run.
-__global__ void fold_input_kernel(const float *__restrict__ x, bf16 *__restrict__ out, int C,
-                                  int H, int W, int Q, int S, int Sp, int Cp, int pad_w,
-                                  int stride_w) {
-  extern __shared__ float srow[];  // [C][W]
-  const int h = blockIdx.x % H;
-  const int64_t n = blockIdx.x / H;
-  for (int i = threadIdx.x; i < C * W; i += blockDim.x) {
-    const int c = i / W, w = i % W;
-    srow[i] = x[((n * C + c) * H + h) * (int64_t)W + w];
-  }
-  __syncthreads();
-  const int Cf = Sp * Cp;           // multiple of 8
-  const int pieces = Cf / 8;        // 16-byte pieces per output pixel
-  bf16 *orow = out + ((n * H + h) * (int64_t)Q) * Cf;
-  for (int i = threadIdx.x; i < Q * pieces; i += blockDim.x) {
-    const int q = i / pieces, pc = i % pieces;
+// x fp32 NCHW -> bf16 [N][H][Wp][Cp], image shifted right by pad_w pixels, zeros elsewhere.
+// One thread per 16-byte piece of the output; reads of one channel are contiguous along w.
+__global__ void pad_input_kernel(const float *__restrict__ x, bf16 *__restrict__ out, int C, int H,
+                                 int W, int Wp, int Cp, int pad_w, int64_t pieces_total) {
+  const int pieces_row = Wp * Cp / 8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < pieces_total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int pc = (int)(i % pieces_row);
+    const int64_t nh = i / pieces_row;
+    const int h = (int)(nh % H);
+    const int64_t n = nh / H;
+    float f[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = pc * 8 + u;
+      const int c = e % Cp, w = e / Cp - pad_w;
+      f[u] = (c < C && w >= 0 && w < W) ? x[((n * C + c) * H + h) * (int64_t)W + w] : 0.0f;
+    }
     __nv_bfloat162 v[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float f[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int cf = pc * 8 + e * 2 + u;
-        const int s2 = cf / Cp, c = cf % Cp;
-        const int ww = q * stride_w - pad_w + s2;
-        f[u] = (s2 < S && c < C && ww >= 0 && ww < W) ? srow[c * W + ww] : 0.0f;
-      }
-      v[e] = __floats2bfloat162_rn(f[0], f[1]);
-    }
+    for (int e = 0; e < 4; ++e) v[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
     uint4 pk;
     pk.x = *reinterpret_cast<uint32_t *>(&v[0]);
     pk.y = *reinterpret_cast<uint32_t *>(&v[1]);
     pk.z = *reinterpret_cast<uint32_t *>(&v[2]);
     pk.w = *reinterpret_cast<uint32_t *>(&v[3]);
-    *reinterpret_cast<uint4 *>(orow + (int64_t)i * 8) = pk;
+    *reinterpret_cast<uint4 *>(out + i * 8) = pk;
   }
 }
 
-void launch_fold_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Q, int S,
-                            int Sp, int Cp, int pad_w, int stride_w, cudaStream_t s) {
-  if ((int64_t)N * H * Q == 0) return;
-  const size_t smem = (size_t)C * W * sizeof(float);
-  fold_input_kernel<<<(unsigned)(N * H), 256, smem, s>>>(x, out, C, H, W, Q, S, Sp, Cp, pad_w,
-                                                        stride_w);
+void launch_pad_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Wp, int Cp,
+                           int pad_w, cudaStream_t s) {
+  const int64_t pieces = (int64_t)N * H * (Wp * Cp / 8);
+  if (pieces == 0) return;
+  pad_input_kernel<<<grid_for(pieces, 256), 256, 0, s>>>(x, out, C, H, W, Wp, Cp, pad_w, pieces);
   count(CNT_LAUNCHES);
 }
 
