@@ -21,7 +21,7 @@ INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 RUNTIME_SRCS = ["runtime.cu", "kernels_f32.cu", "kernels_nhwc.cu", "conv_tc.cu", "conv_tc_inst_256_64.cu",
                 "conv_tc_inst_256_32.cu", "conv_tc_inst_128_64.cu", "conv_tc_inst_64_64.cu",
-                "conv_tc_inst_32_32.cu", "trace.cu", "abi.cu", "misc_ops.cu", "no_alloc.cu"]
+                "conv_tc_inst_32_32.cu", "stem_pool.cu", "trace.cu", "abi.cu", "misc_ops.cu", "no_alloc.cu"]
 REPLAY_SRCS = [os.path.join("host", "replay.cpp")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

@@ -64,7 +64,7 @@ void die(const char *what, cudaError_t e, size_t size) {
   exit(-1);
 }
 
-enum PackLayout { PACK_KRSC = 1, PACK_DW = 2, PACK_FOLD = 3, PACK_RAW = 4 };
+enum PackLayout { PACK_KRSC = 1, PACK_DW = 2, PACK_FOLD = 3, PACK_RAW = 4, PACK_STEM = 5 };
 
 // Device pointer of the packed form of the filter at `w`; resident across calls when the
 // filter was uploaded from host memory (a compiled model's constant), otherwise packed
@@ -99,13 +99,14 @@ void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int
     dst = pw.dev;
     r.resident[rec->host_src] = std::make_pair(rec->host_bytes, rec->host_hash);
   } else {
-    dst = scratch_get(1, packed_bytes);
+    dst = scratch_get(layout == PACK_STEM ? 5 : 1, packed_bytes);
   }
   if (!dst) return nullptr;
   if (layout == PACK_KRSC) launch_pack_krsc_bf16(w, (bf16 *)dst, K, C, R, S, r.stream);
   else if (layout == PACK_DW) launch_pack_dw_f32(w, (float *)dst, C, R, S, r.stream);
   else if (layout == PACK_RAW)
     OCC_CUDA(cudaMemcpyAsync(dst, w, packed_bytes, cudaMemcpyDeviceToDevice, r.stream));
+  else if (layout == PACK_STEM) launch_pack_stem_bf16(w, (bf16 *)dst, C, R, S, Cp, Sp * Cp, r.stream);
   else launch_pack_fold_bf16(w, (bf16 *)dst, K, C, R, S, Sp, Cp, r.stream);
   return dst;
 }
@@ -138,6 +139,8 @@ struct ConvJob {
   bool bias_set = false, res_set = false, act_set = false;
   int absorbed = 0;           // later calls folded into this one so far
   uintptr_t dep_lo[2] = {0, 0}, dep_hi[2] = {0, 0};  // device ranges still to be read
+  // folded (few-channel) form: what the fused convolution + pool kernel needs besides `a`
+  const bf16 *w_stem = nullptr;   // filter in that kernel's layout, packed while the filter is live
 };
 
 ConvJob g_pending;  // convolution held back while later calls are folded into it
@@ -208,6 +211,7 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
   job.bias_set = bias != nullptr;
   job.act_set = g.act != ACT_IDENTITY;
   job.res_set = false;
+  job.w_stem = nullptr;
   return true;
 }
 
@@ -371,6 +375,9 @@ float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t
   e.fusable = shape_ok && r.mode == MATH_BF16 && g.P > 0 && g.Q > 0 && g.N > 0 &&
               (depthwise ? g.C % 8 == 0
                          : (g.groups == 1 && g.K % 8 == 0 && (g.C < 16 || g.C % 16 == 0)));
+  // the fused convolution + max-pool kernel takes 64-channel stems whose column step is 16 bytes
+  e.poolable = e.fusable && !depthwise && g.C <= 4 && g.K == 64 && g.stride_w == 2 && g.Q <= 128 &&
+               g.S <= 16 && g.R <= 11;
   const Role role = step(e, false);
 
   if (!shape_ok) {
@@ -389,6 +396,12 @@ float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t
     if (ok) {
       job.out = y;
       if (role == R_DEFER) {   // later calls of the recorded sequence fold into this one
+        if (e.poolable && !depthwise && job.a.w_step) {
+          // the pool that may join later runs after the filter tensor has been given back
+          const int cp = job.a.w_step / g.stride_w;
+          job.w_stem = (const bf16 *)packed_weights(w, PACK_STEM, stem_pool_weight_bytes(g.R, job.a.Cf),
+                                                    g.K, g.C, g.R, g.S, job.a.Cf / cp, cp);
+        }
         g_pending = job;
         g_pending.active = true;
         return y;
@@ -882,7 +895,43 @@ static float *pool_common(int sym, float *x, int64_t *dI, float *y, int64_t *dO,
   te_ptr(e, x); te_ptr(e, y); te_dims(e, dI, 4); te_dims(e, dO, 4); te_dims(e, kernel, 2);
   te_dims(e, padding, 4); te_dims(e, stride, 2);
   e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = numel4(dO) * 4;
-  step(e, false);
+  if (!avg && kernel[0] == 3 && kernel[1] == 3 && stride[0] == 2 && stride[1] == 2 && ph == 1 &&
+      pw == 1 && padding[1] == 1 && padding[3] == 1)
+    e.kind = CK_POOL_3S2;
+  const Role role = step(e, false);
+  if (role == R_ABSORB && g_pending.active) {
+    // the held-back stem convolution and this pool run as one kernel
+    ConvJob &j = g_pending;
+    const ConvGeom &g = j.g;
+    bool done = false;
+    if (!j.depthwise && j.w_stem && !j.res_set && x == j.out && N == g.N && C == g.K && H == g.P &&
+        W == g.Q && e.kind == CK_POOL_3S2) {
+      StemPoolArgs sa;
+      memset(&sa, 0, sizeof(sa));
+      sa.x = j.a.x;
+      sa.bias = j.a.bias;
+      sa.y = (bf16 *)y;
+      sa.N = g.N; sa.H = g.H; sa.row_bytes = j.a.row_elems * 2; sa.w_step_bytes = j.a.w_step * 2;
+      sa.P = g.P; sa.Q = g.Q; sa.K = g.K; sa.R = g.R; sa.Cf = j.a.Cf;
+      sa.pad_h = g.pad_h; sa.stride_h = g.stride_h;
+      sa.PP = P; sa.QP = Q;
+      sa.lo = j.a.act == ACT_RELU ? 0.0f : (j.a.act == ACT_CLIP ? j.a.lo : -INFINITY);
+      sa.hi = j.a.act == ACT_CLIP ? j.a.hi : INFINITY;
+      sa.w = j.w_stem;
+      if (stem_pool_supported(sa)) {
+        if (launch_stem_pool(sa, r.dev_err, r.num_sms, r.stream)) {
+          j.active = false;
+          j.absorbed++;
+          elide(j.out);
+          trace_count_chain();
+          mark_bf16(y, N, C, P, Q);
+          done = true;
+        }
+      }
+    }
+    if (done) return y;
+    flush_pending();
+  }
   if (r.mode == MATH_BF16 && C % 8 == 0 && is_bf16(x, N, C, H, W)) {
     launch_pool_bf16((const bf16 *)x, (bf16 *)y, N, C, H, W, P, Q, (int)kernel[0], (int)kernel[1],
                      ph, pw, (int)stride[0], (int)stride[1], avg, r.stream);

@@ -546,6 +546,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
     // trade ring stages (down to what one tile needs, at least two) for slab buffers.
     const int ks = a.R * a.S * (a.Cf / bk);
     int min_stages = ks < 3 ? 2 : 3;
+    if (const char *f = getenv("OCCAMY_TC_RES_STAGES")) min_stages = atoi(f) > 1 ? atoi(f) : min_stages;  // tuning aid
     dbuf = (int)((TC_SMEM_LIMIT - fixed0 - min_stages * stage_bytes) / slab_bytes);
     if (dbuf > 8) dbuf = 8;
     if (dbuf < 3) dbuf = 3;

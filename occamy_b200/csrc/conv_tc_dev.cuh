@@ -102,6 +102,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t a, uint32_t parity, volatile 
   if (mbar_try(a, parity)) return true;
   return mbar_wait_slow(a, parity, abort_flag);
 }
+// The same wait for roles with slack: sleeps between polls, so that many waiting warps do
+// not take issue slots away from a single thread that is issuing short MMAs.
+static __device__ __noinline__ bool mbar_wait_sleepy(uint32_t a, uint32_t parity,
+                                                     volatile int *abort_flag) {
+  if (mbar_try(a, parity)) return true;
+  const long long t0 = clock64();
+  int it = 0;
+  while (!mbar_try(a, parity)) {
+    __nanosleep(128);
+    if ((++it & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
 // The same wait, polling loop inline: for the producer and MMA roles, whose loops are tiny
 // and where the return from a call would sit on the critical path of every k-step.
 __device__ __forceinline__ bool mbar_wait_hot(uint32_t a, uint32_t parity,

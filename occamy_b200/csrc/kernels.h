@@ -94,6 +94,26 @@ struct TcConvArgs {
   // columns, and elements per input row; the vectors overlap when w_step < Cf.
   int w_step, row_elems;
 };
+// ---- few-channel convolution fused with the 3x3 / stride 2 / pad 1 max pool after it -----
+struct StemPoolArgs {
+  const bf16 *x;      // padded channels-last rows [N][H][row_bytes / 2] (launch_pad_input_bf16)
+  const bf16 *w;      // launch_pack_stem_bf16 layout
+  const float *bias;  // [K] or null
+  bf16 *y;            // pooled output, NHWC bf16 [N][PP][QP][K]
+  int N, H, row_bytes, w_step_bytes;
+  int P, Q, K;        // convolution output rows / columns / channels
+  int R, Cf;          // filter rows, Sp*Cp folded channels
+  int pad_h, stride_h;
+  int PP, QP;         // pooled rows / columns
+  float lo, hi;       // clamp applied before the pool
+};
+bool stem_pool_supported(const StemPoolArgs &a);
+size_t stem_pool_weight_bytes(int R, int Cf);
+// fp32 KCRS (C <= Cp) -> the weight layout of the fused kernel
+void launch_pack_stem_bf16(const float *w, bf16 *out, int C, int R, int S, int Cp, int Cf,
+                           cudaStream_t s);
+bool launch_stem_pool(const StemPoolArgs &a, int *err_word, int num_sms, cudaStream_t s);
+
 // Returns false when the shape is outside what the kernel supports (caller falls back).
 bool tc_conv_supported(const TcConvArgs &a);
 void launch_tc_conv(const TcConvArgs &a, cudaStream_t s);

@@ -109,6 +109,24 @@ void analyse(const std::vector<Entry> &rec, std::vector<uint8_t> &roles) {
       members.push_back(j);
       cur = f.out;
     }
+    // a stem convolution takes the max pool behind it along, when the pool is the only
+    // reader of the full-resolution tensor
+    if (c.poolable && !res_set) {
+      const size_t from = members.empty() ? i + 1 : members.back() + 1;
+      for (size_t j = from; j < rec.size(); ++j) {
+        const Entry &f = rec[j];
+        if (is_passive(f.sym)) {
+          if ((f.sym == S_MEMOFFSET || f.sym == S_MALLOC) && overlaps(f.out, f.out_bytes, cur, cur_bytes))
+            break;
+          if (f.sym == S_DEALLOC && f.out == cur) break;
+          continue;
+        }
+        if (f.sym == S_MAXPOOL && f.kind == CK_POOL_3S2 && f.in[0] == cur && f.out != cur &&
+            dies_unread(rec, cur, cur_bytes, j + 1))
+          members.push_back(j);
+        break;
+      }
+    }
     if (members.empty()) continue;
     roles[i] = R_DEFER;
     for (size_t m : members) roles[m] = R_ABSORB;

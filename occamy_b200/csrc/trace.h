@@ -5,6 +5,7 @@
 // calls between cudnnCreate and cudnnDestroy (the compiled function's prologue and
 // epilogue).  When an inference ends it looks for chains
 //     convolution -> [+ bias [1,K,1,1]] -> [+ same-shape tensor] -> [ReLU | Clip]
+// (and, for a few-channel stem convolution, a 3x3 / stride 2 max pool behind it)
 // whose intermediate results nobody else reads before their memory is handed out again,
 // and marks them.  The next time the same call sequence comes by, the convolution of such
 // a chain is held back, the following calls are folded into its epilogue, and one kernel
@@ -26,7 +27,10 @@ enum Sym {
 enum Role { R_EAGER = 0, R_DEFER = 1, R_ABSORB = 2 };
 
 // kind of a tensor-op / activation entry, as far as chains care
-enum ChainKind { CK_NONE = 0, CK_BIAS_ADD = 1, CK_SAME_ADD = 2, CK_RELU = 3, CK_CLIP = 4 };
+enum ChainKind {
+  CK_NONE = 0, CK_BIAS_ADD = 1, CK_SAME_ADD = 2, CK_RELU = 3, CK_CLIP = 4,
+  CK_POOL_3S2 = 5   // max pool 3x3, stride 2, pad 1
+};
 
 struct Entry {
   uint64_t sig = 1469598103934665603ull;
@@ -38,6 +42,7 @@ struct Entry {
   int kind = CK_NONE;      // ChainKind, or the activation mode of a fused convolution
   bool fusable = false;    // convolution that the bf16 path takes (may head a chain)
   bool depthwise = false;
+  bool poolable = false;   // convolution whose kernel can take a following CK_POOL_3S2 along
 };
 
 // Signature building.  Device pointers are taken relative to the active pool when they

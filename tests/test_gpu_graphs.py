@@ -133,14 +133,15 @@ def test_deterministic_replay():
     assert max_rel_err(outs[0], outs[1]) <= 1e-2
 
 
-@pytest.mark.parametrize("case", [("resnet50", replay.FUSE_REFERENCE, 16),
+@pytest.mark.parametrize("case", [("resnet50", replay.FUSE_REFERENCE, 17),
                                   ("resnet50", replay.FUSE_NONE, 53),
                                   ("mobilenet_v2", replay.FUSE_NONE, 50),
                                   ("mobilenet_v2", replay.FUSE_REFERENCE, 42)])
 def test_cross_call_fusion(case):
     """Element-wise calls that follow a convolution are folded into its epilogue once the
     call sequence has been seen: conv3 + residual add + ReLU of every ResNet block with the
-    reference's fusion on; conv + bias add + ReLU/Clip (+ residual) without it."""
+    reference's fusion on (plus the stem convolution with its max pool); conv + bias add +
+    ReLU/Clip (+ residual) without it."""
     name, fuse, chains = case
     rt.set_math_mode(rt.MATH_BF16)
     g = getattr(graphs, name)(batch=2, seed=4, image=64)
@@ -200,3 +201,45 @@ def test_new_call_sequence_after_a_recorded_one():
     (wb,) = run_graph_oracle(gb, xb)
     for y, w in ((a1, wa), (a3, wa), (b1, wb), (b2, wb)):
         assert max_rel_err(y, w) <= 2e-2
+
+
+def _stem_graph(N, H, W, R, pad, act, seed):
+    g = graphs.Graph((N, 3, H, W), seed)
+    g.name = "stem"
+    w, b = g.he_conv(64, 3, R, R)
+    y = g.conv(0, w, b, pads=(pad, pad), strides=(2, 2))
+    if act == "relu":
+        y = g.relu(y)
+    elif act == "clip":
+        y = g.clip(y, -0.25, 0.75)
+    y = g.maxpool(y, (3, 3), (1, 1), (2, 2))
+    g.mark_output(y)
+    return g
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 64, 7, 3, "relu"), (3, 224, 224, 7, 3, "relu"),
+                                   (1, 70, 54, 7, 3, "clip"), (2, 33, 47, 5, 2, "none"),
+                                   (5, 96, 200, 3, 1, "relu"), (1, 17, 250, 7, 3, "relu")])
+@pytest.mark.parametrize("fuse", [replay.FUSE_REFERENCE, replay.FUSE_NONE])
+def test_stem_conv_with_max_pool(shape, fuse):
+    """A 64-channel RGB stem and the 3x3 / stride 2 max pool behind it run as one kernel from
+    the second inference on; the result must match the call-by-call run bit for bit (same
+    bf16 rounding of the convolution output before the pool) and the oracle within the bf16
+    tolerance.  Odd sizes exercise the image edges of both the convolution and the pool."""
+    N, H, W, R, pad, act = shape
+    rt.set_math_mode(rt.MATH_BF16)
+    g = _stem_graph(N, H, W, R, pad, act, seed=7)
+    x = graphs.make_input(g, 5)
+    p = g.to_program()
+    p.lower(fuse=fuse)
+    b = replay.Binding()
+    (want,) = run_graph_oracle(g, x)
+    (y0,) = p.run(b, x)
+    n0 = rt.lib().occamy_fused_chains()
+    (y1,) = p.run(b, x)
+    assert rt.lib().occamy_fused_chains() - n0 == 1
+    assert rt.last_error() == 0
+    assert max_rel_err(y0, want) <= 2e-2 and max_rel_err(y1, want) <= 2e-2
+    # conv + ReLU fused by the reference lowering round the same way in both runs
+    if fuse == replay.FUSE_REFERENCE and act != "clip":
+        assert np.array_equal(y0, y1)
