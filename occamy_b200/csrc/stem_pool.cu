@@ -506,9 +506,22 @@ bool launch_stem_pool(const StemPoolArgs &a, int *err_word, int num_sms, cudaStr
     attr_set = true;
   }
   const int grid = p.units < num_sms ? p.units : num_sms;
+  Runtime &r = rt();
+  int prof_slot = -1;
+  if (r.profiling) {   // timed like the other tensor-core launches
+    prof_slot = r.prof_count++;
+    while ((int)r.prof_events.size() < 2 * (prof_slot + 1)) {
+      cudaEvent_t e;
+      OCC_CUDA(cudaEventCreate(&e));
+      r.prof_events.push_back(e);
+    }
+    OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot], s));
+  }
   // at least half of the shared memory, so that one CTA (one TMEM allocation) runs per SM
   stem_pool_kernel<<<grid, ST_THREADS, smem < 120 * 1024 ? 120 * 1024 : smem, s>>>(p);
+  if (prof_slot >= 0) OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot + 1], s));
   count(CNT_LAUNCHES);
+  count(CNT_TC_LAUNCHES);
   return cudaGetLastError() == cudaSuccess;
 }
 
