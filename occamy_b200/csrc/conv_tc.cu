@@ -425,7 +425,7 @@ static TcFastDiv make_fastdiv(int d) {
 
 static int floordiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
-static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
+static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool allow_halo = true) {
   Plan pl;
   memset(&pl, 0, sizeof(pl));
   TcParams &p = pl.p;
@@ -457,16 +457,33 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
   static const bool pn_allowed = !(getenv("OCCAMY_TC_PIXEL_N") && !strcmp(getenv("OCCAMY_TC_PIXEL_N"), "0"));
   // worth it only where the tensor pipe is the limit: the transposing epilogue is slower
   // than the plain one, which hurts the HBM-bound 1x1 layers
-  const bool pn = pn_allowed && !a.out_f32 && a.K <= 128 && a.R * a.S > 1 &&
+  // 3x3 / stride 1 / pad 1 with 64 -> 64 channels and rows of at most 126 pixels: the input
+  // block of a tile is loaded once and the taps are windows of it (TC_MODE_HALO)
+  static const bool halo_allowed = !(getenv("OCCAMY_TC_HALO") && !strcmp(getenv("OCCAMY_TC_HALO"), "0"));
+  const bool halo = allow_halo && halo_allowed && !a.out_f32 && a.R == 3 && a.S == 3 &&
+                    a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 1 && a.pad_w == 1 &&
+                    a.Cf == 64 && a.K == 64 && a.W + 2 <= 128 && a.w_step == 0 && a.Q == a.W &&
+                    a.P == a.H;
+  const bool pn = !halo && pn_allowed && !a.out_f32 && a.K <= 128 && a.R * a.S > 1 &&
                   a.R * a.S * a.Cf >= 9 * 64;
   pl.pn = pn;
-  choose_box(Qg, Pg, Ng, pn ? 256 : 128, &p.tw, &p.th, &p.tn);
+  if (halo) {
+    p.tw = a.W + 2;                      // two junk columns that the store clips
+    p.th = 128 / p.tw < a.P ? 128 / p.tw : a.P;
+    p.tn = 1;
+    p.halo = 1;
+    p.halo_wp = p.tw;
+    p.halo_a_bytes = ((p.th + 2) * p.tw * 128 + 1023) / 1024 * 1024;
+  } else {
+    choose_box(Qg, Pg, Ng, pn ? 256 : 128, &p.tw, &p.th, &p.tn);
+  }
   p.n_mma = (p.tw * p.th * p.tn + 15) / 16 * 16;
-  p.tiles_w = (Qg + p.tw - 1) / p.tw;
+  p.tiles_w = halo ? 1 : (Qg + p.tw - 1) / p.tw;
   p.tiles_h = (Pg + p.th - 1) / p.th;
   p.tiles_n = (Ng + p.tn - 1) / p.tn;
   const int nsm = num_sms > 0 ? num_sms : 148;
   const int bn = pn ? 128
+                    : halo ? 64
                     : a.out_f32 ? (a.K > 32 ? 64 : 32)   // the fp32 head is compiled for these only
                     : pick_bn(a.K, (long)p.tiles_w * p.tiles_h * p.tiles_n,
                               (a.R * a.S * a.Cf + 63) / 64, nsm);
@@ -479,7 +496,13 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
 
   const uint32_t boxA[4] = {(uint32_t)bk, (uint32_t)p.tw, (uint32_t)p.th, (uint32_t)p.tn};
   bool ok = true;
-  if (flat) {
+  if (halo) {
+    const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N};
+    const uint64_t st[3] = {(uint64_t)a.Cf * 2, (uint64_t)a.W * a.Cf * 2, (uint64_t)a.H * a.W * a.Cf * 2};
+    const uint32_t box[4] = {64u, (uint32_t)p.tw, (uint32_t)(p.th + 2), 1u};
+    ok &= make_map(&p.tmA[0], a.x, 4, dims, st, box, 128);
+    p.num_taps = 9;
+  } else if (flat) {
     const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)Qg, 1, 1};
     const uint64_t st[3] = {(uint64_t)a.Cf * 2, (uint64_t)Qg * a.Cf * 2, (uint64_t)Qg * a.Cf * 2};
     ok &= make_map(&p.tmA[0], a.x, 4, dims, st, boxA, bk * 2);
@@ -525,7 +548,8 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
   const int dc = pn ? 64 : (bn < 64 ? bn : (bn == 256 && bk == 64 && ksteps64 >= 16 ? 32 : 64));
   pl.dc = dc;
   pl.mode = a.out_f32 ? (TC_MODE_F32 | TC_MODE_CLAMP)
-                      : ((a.residual ? TC_MODE_RES : 0) | (a.act == ACT_RELU ? 0 : TC_MODE_CLAMP));
+                      : ((a.residual ? TC_MODE_RES : 0) | (a.act == ACT_RELU ? 0 : TC_MODE_CLAMP) |
+                         (halo ? TC_MODE_HALO : 0));
   if (!a.out_f32) {
     const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
     const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};
@@ -534,10 +558,14 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
     if (a.residual) ok &= make_map(&p.tmR, a.residual, 4, dims, st, box, dc * 2);
   }
   // shared memory: ring + output slabs + bias + barriers + alignment
-  const size_t stage_bytes = pn ? (size_t)(128 + 256) * bk * 2 : 128 * bk * 2 + (size_t)bn * bk * 2;
+  const size_t stage_bytes = pn     ? (size_t)(128 + 256) * bk * 2
+                             : halo ? (size_t)p.halo_a_bytes
+                                    : 128 * bk * 2 + (size_t)bn * bk * 2;
   p.bias_floats = (a.K + bn - 1) / bn * bn;
   const size_t slab_bytes = (size_t)128 * dc * 2;
-  const size_t fixed0 = pn ? 1024 + 2 * 256 * 128 + 8 * 80 : 1024 + (size_t)p.bias_floats * 4 + 8 * 80;
+  const size_t fixed0 = pn ? 1024 + 2 * 256 * 128 + 8 * 80
+                           : 1024 + (size_t)p.bias_floats * 4 + 8 * 80 +
+                                 (halo ? (size_t)9 * bn * bk * 2 : 0);   // halo: resident weights
   int dbuf = pn ? 0 : 3;
   int stages;
   if (!pn && a.residual) {
@@ -563,6 +591,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms) {
     fprintf(stderr, "[tcplan] K %d Cf %d RS %d px %dx%dx%d box %dx%dx%d bn %d dc %d pn %d bk %d stages %d dbuf %d tiles %d smem %zu\n",
             a.K, a.Cf, a.R * a.S, Qg, Pg, Ng, p.tw, p.th, p.tn, bn, dc, (int)pn, bk, stages, dbuf,
             p.total_tiles, pl.smem);
+  if (halo && !ok) return build_plan(a, err_word, num_sms, false);   // e.g. the block map was refused
   pl.ok = ok;
   return pl;
 }

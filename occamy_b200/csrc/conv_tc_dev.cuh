@@ -45,6 +45,10 @@ struct alignas(64) TcParams {
   float *out_f32;
   int ldo;
   int m_total;
+  int halo;              // 3x3 halo form: the A block of a tile is loaded once, the taps are
+                         // windows of it (see TC_MODE_HALO); then:
+  int halo_wp;           //   pixels per block row (output width + 2)
+  int halo_a_bytes;      //   bytes of one staged block, a multiple of 1024
   int bias_floats;       // K rounded up to whole channel tiles: bias entries kept in shared memory
   int dbuf;              // output slab buffers in shared memory (3..8)
   int n_mma;             // pixel-N variant: N of the MMA (pixels per tile rounded up to 16)
@@ -55,6 +59,13 @@ struct alignas(64) TcParams {
 constexpr int TC_MODE_RES = 1;     // adds a residual tensor
 constexpr int TC_MODE_CLAMP = 2;   // general clamp to [lo, hi]; otherwise ReLU
 constexpr int TC_MODE_F32 = 4;     // fp32 row-major output straight to global memory (GEMM head)
+// 3x3 / stride 1 / pad 1 with 64 input channels and resident weights: the producer loads a
+// tile's input block (its rows plus one row above and below, whole image width plus one zero
+// column on either side) ONCE and the nine taps are windows of that block, shifted by whole
+// pixels - a swizzled operand may start at any multiple of 128 bytes inside a 1024-aligned
+// buffer.  The tile is th full rows of width W + 2; its two extra columns are junk that the
+// TMA store clips.
+constexpr int TC_MODE_HALO = 8;
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -232,6 +243,20 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uin
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// tcgen05.mma with each operand descriptor given as its two 32-bit halves: only the low
+// half (start address) changes from one MMA to the next, and 32-bit arithmetic keeps the
+// single issuing thread's instruction count down.
+__device__ __forceinline__ void mma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                         uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t *r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -351,6 +376,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
   constexpr bool RES = (MODE & TC_MODE_RES) != 0;
   constexpr bool CLAMP = (MODE & TC_MODE_CLAMP) != 0;
   constexpr bool F32 = (MODE & TC_MODE_F32) != 0;
+  constexpr bool HALO = (MODE & TC_MODE_HALO) != 0;
   constexpr int EPI_THREADS = 128 * EW;
   constexpr int STORE_WARP = 2 + 4 * EW;
   constexpr int CW = DC / EW;                  // channels one epilogue thread handles per slab
@@ -364,10 +390,12 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const int bk = p.bk, stages = p.stages, dbuf = p.dbuf;
-  const uint32_t a_bytes = 128u * bk * 2u, b_bytes = (uint32_t)BN * bk * 2u;
+  // halo form: the ring carries input blocks only, the weights of all taps sit behind it
+  const uint32_t a_bytes = HALO ? (uint32_t)p.halo_a_bytes : 128u * bk * 2u;
+  const uint32_t b_bytes = (uint32_t)BN * bk * 2u;
   const uint32_t sA = base;
   const uint32_t sB = sA + stages * a_bytes;
-  const uint32_t sD = sB + stages * b_bytes;                    // dbuf output slabs
+  const uint32_t sD = sB + (HALO ? (uint32_t)p.num_taps : (uint32_t)stages) * b_bytes;   // dbuf output slabs
   const uint32_t sMisc = sD + dbuf * SLAB_BYTES;
   uint8_t *misc_ptr = base_ptr + (sMisc - base);
   float *bias_s = reinterpret_cast<float *>(misc_ptr);          // bias of every output channel
@@ -379,9 +407,10 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
   auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * stages + 2 + s); };
   auto rfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + 4 + s); };
   auto dfull_bar = [&](int s) { return bar0 + 8u * (2 * stages + 4 + dbuf + s); };
+  const uint32_t wfull_bar = bar0 + 8u * (2 * stages + 4 + 2 * dbuf);   // halo form: weights landed
   volatile uint32_t *tmem_holder =
-      reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 4 + 2 * dbuf);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 5 + 2 * dbuf);
+      reinterpret_cast<volatile uint32_t *>(bars + 2 * stages + 5 + 2 * dbuf);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 6 + 2 * dbuf);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -403,6 +432,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
       mbar_init(rfull_bar(s), 1);
       mbar_init(dfull_bar(s), EPI_THREADS / 32);
     }
+    mbar_init(wfull_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -427,6 +457,27 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      if constexpr (HALO) {
+        // weights of all taps once, then one input block per tile
+        mbar_expect_tx(wfull_bar, (uint32_t)p.num_taps * b_bytes);
+        for (int t = 0; t < p.num_taps; ++t)
+          tma_load_3d(sB + t * b_bytes, &p.tmB, wfull_bar, 0, 0, t);
+        const uint32_t blk_bytes = (uint32_t)((p.th + 2) * p.halo_wp) * 128u;
+        for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+          const TcTile tl = tc_decode<BN>(p, tile);
+          if (!mbar_wait_hot(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            err_code = 1;
+            break;
+          }
+          mbar_expect_tx(full_bar(stage), blk_bytes);
+          // column -1 and row p0 - 1 onwards; what lies outside the image arrives as zeros
+          tma_load_4d(sA + stage * a_bytes, &p.tmA[0], full_bar(stage), 0, -1, tl.p0 - 1, tl.n0);
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      } else {
       const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + b_bytes;
       for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
         const TcTile tl = tc_decode<BN>(p, tile);
@@ -448,12 +499,54 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
           }
         }
       }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
+      if constexpr (HALO) {
+        // 3x3 taps as shifted windows of the staged block: (dh * wp + dw) pixels of 128 bytes
+        // further on.  Straight-line issue code: the MMAs are short when BN is small, and a
+        // taken branch costs the issuing thread more than one of them.
+        const uint64_t d0 = make_smem_desc(sA, 64);
+        const uint32_t a_hi = (uint32_t)(d0 >> 32), b_hi = a_hi;
+        const uint32_t a_lo0 = (uint32_t)d0;
+        const uint32_t b_lo0 = (uint32_t)make_smem_desc(sB, 64);
+        const uint32_t stage_desc = a_bytes >> 4, tap_desc = b_bytes >> 4;
+        const uint32_t wp8 = (uint32_t)p.halo_wp * 8u;   // one block row in descriptor units
+        if (!mbar_wait_hot(wfull_bar, 0, abort_flag)) err_code = 3;
+        for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+          if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+            err_code = 2;
+            break;
+          }
+          if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
+            err_code = 3;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+          const uint32_t a_lo = a_lo0 + (uint32_t)stage * stage_desc;
+#pragma unroll
+          for (int t = 0; t < 9; ++t) {
+            const uint32_t at = a_lo + (uint32_t)(t / 3) * wp8 + (uint32_t)(t % 3) * 8u;
+            const uint32_t bt = b_lo0 + (uint32_t)t * tap_desc;
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              mma_lohi(d_tmem, at + 2 * kk, a_hi, bt + 2 * kk, b_hi, IDESC, (t | kk) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          tc_commit(tfull_bar(acc));
+          if (++stage == stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
+        }
+      } else {
       for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
         if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           err_code = 2;
@@ -485,6 +578,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
         tc_commit(tfull_bar(acc));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+      }
       }
     }
   } else if (warp == STORE_WARP) {
@@ -718,7 +812,7 @@ inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t
   }
   tc_conv_kernel<BN, DC, TC_EW, MODE><<<grid, 64 + 128 * TC_EW + 32, smem, s>>>(p);
 }
-template <int BN, int DC, bool WITH_F32>
+template <int BN, int DC, bool WITH_F32, bool WITH_HALO = false>
 inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
   switch (mode) {
     case 0: tc_launch_one<BN, DC, 0>(p, grid, smem, s); return true;
@@ -733,8 +827,24 @@ inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, c
         return true;
       }
       return false;
-    default: return false;
+    default: break;
   }
+  if constexpr (WITH_HALO) {
+    switch (mode) {
+      case TC_MODE_HALO: tc_launch_one<BN, DC, TC_MODE_HALO>(p, grid, smem, s); return true;
+      case TC_MODE_HALO | TC_MODE_RES:
+        tc_launch_one<BN, DC, TC_MODE_HALO | TC_MODE_RES>(p, grid, smem, s);
+        return true;
+      case TC_MODE_HALO | TC_MODE_CLAMP:
+        tc_launch_one<BN, DC, TC_MODE_HALO | TC_MODE_CLAMP>(p, grid, smem, s);
+        return true;
+      case TC_MODE_HALO | TC_MODE_RES | TC_MODE_CLAMP:
+        tc_launch_one<BN, DC, TC_MODE_HALO | TC_MODE_RES | TC_MODE_CLAMP>(p, grid, smem, s);
+        return true;
+      default: break;
+    }
+  }
+  return false;
 }
 
 }  // namespace occ

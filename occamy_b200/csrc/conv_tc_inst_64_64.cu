@@ -5,7 +5,7 @@
 namespace occ {
 
 bool tc_launch_64_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
-  return tc_launch_mode<64, 64, true>(p, mode, grid, smem, s);
+  return tc_launch_mode<64, 64, true, true>(p, mode, grid, smem, s);
 }
 
 }  // namespace occ

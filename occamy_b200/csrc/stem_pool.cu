@@ -68,21 +68,6 @@ __device__ __forceinline__ uint64_t desc_plain(uint32_t saddr, uint32_t lbo, uin
          ((uint64_t)(sbo >> 4) << 32) | (1ull << 46);
 }
 
-// tcgen05.mma with each operand descriptor given as its two 32-bit halves: only the low
-// half (start address) changes from one MMA to the next, and 32-bit arithmetic keeps the
-// single issuing thread's instruction count down.
-__device__ __forceinline__ void mma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
-                                         uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-      "setp.ne.b32 p, %6, 0;\n"
-      "mov.b64 da, {%1, %2};\n"
-      "mov.b64 db, {%3, %4};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n}" ::"r"(d_tmem),
-      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // The same, issued only when `valid` is non-zero (a predicated instruction, not a branch:
 // a taken branch costs the single issuing thread more than the MMA it would skip).
 __device__ __forceinline__ void mma_lohi_if(uint32_t valid, uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
