@@ -360,40 +360,59 @@ void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S
 }
 
 // x fp32 NCHW -> bf16 [N][H][Wp][Cp], image shifted right by pad_w pixels, zeros elsewhere.
-// One thread per 16-byte piece of the output; reads of one channel are contiguous along w.
-__global__ void pad_input_kernel(const float *__restrict__ x, bf16 *__restrict__ out, int C, int H,
-                                 int W, int Wp, int Cp, int pad_w, int64_t pieces_total) {
-  const int pieces_row = Wp * Cp / 8;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < pieces_total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int pc = (int)(i % pieces_row);
-    const int64_t nh = i / pieces_row;
-    const int h = (int)(nh % H);
-    const int64_t n = nh / H;
-    float f[8];
+// One thread per 16-byte piece of an output row, eight image rows per CTA; CP is a template
+// parameter so that the index arithmetic is shifts, and reads of one channel are contiguous
+// along w.
+template <int CP>
+__global__ void __launch_bounds__(256) pad_input_kernel(const float *__restrict__ x, bf16 *__restrict__ out, int C,
+                                 int H, int W, int Wp, int pad_w, int64_t rows_total) {
+  constexpr int ROWS = 8;                        // image rows per CTA
+  const int pieces_row = Wp * CP / 8;
+  const int64_t plane = (int64_t)H * W;
+  for (int pc = threadIdx.x; pc < pieces_row; pc += blockDim.x) {
+    // source column and channel of the piece's eight values (the same for every row)
+    int col[8];
+    bool on[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int e = pc * 8 + u;
-      const int c = e % Cp, w = e / Cp - pad_w;
-      f[u] = (c < C && w >= 0 && w < W) ? x[((n * C + c) * H + h) * (int64_t)W + w] : 0.0f;
+      const int c = e % CP, w = e / CP - pad_w;
+      on[u] = c < C && w >= 0 && w < W;
+      col[u] = on[u] ? (int)(c * plane + w) : 0;
     }
-    __nv_bfloat162 v[4];
+#pragma unroll 4
+    for (int rr = 0; rr < ROWS; ++rr) {
+      const int64_t nh = (int64_t)blockIdx.x * ROWS + rr;     // n * H + h
+      if (nh >= rows_total) break;
+      const int64_t n = nh / H;
+      const int h = (int)(nh - n * H);
+      const float *xin = x + (n * C * H + h) * (int64_t)W;
+      float f[8];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) v[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
-    uint4 pk;
-    pk.x = *reinterpret_cast<uint32_t *>(&v[0]);
-    pk.y = *reinterpret_cast<uint32_t *>(&v[1]);
-    pk.z = *reinterpret_cast<uint32_t *>(&v[2]);
-    pk.w = *reinterpret_cast<uint32_t *>(&v[3]);
-    *reinterpret_cast<uint4 *>(out + i * 8) = pk;
+      for (int u = 0; u < 8; ++u) f[u] = on[u] ? xin[col[u]] : 0.0f;
+      __nv_bfloat162 v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+      uint4 pk;
+      pk.x = *reinterpret_cast<uint32_t *>(&v[0]);
+      pk.y = *reinterpret_cast<uint32_t *>(&v[1]);
+      pk.z = *reinterpret_cast<uint32_t *>(&v[2]);
+      pk.w = *reinterpret_cast<uint32_t *>(&v[3]);
+      *reinterpret_cast<uint4 *>(out + (nh * Wp * CP) + (int64_t)pc * 8) = pk;
+    }
   }
 }
 
 void launch_pad_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Wp, int Cp,
                            int pad_w, cudaStream_t s) {
-  const int64_t pieces = (int64_t)N * H * (Wp * Cp / 8);
-  if (pieces == 0) return;
-  pad_input_kernel<<<grid_for(pieces, 256), 256, 0, s>>>(x, out, C, H, W, Wp, Cp, pad_w, pieces);
+  const int pieces_row = Wp * Cp / 8;
+  if ((int64_t)N * H * pieces_row == 0) return;
+  const int threads = pieces_row >= 256 ? 256 : (pieces_row + 31) / 32 * 32;
+  const int64_t rows = (int64_t)N * H;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (Cp == 4) pad_input_kernel<4><<<grid, threads, 0, s>>>(x, out, C, H, W, Wp, pad_w, rows);
+  else if (Cp == 8) pad_input_kernel<8><<<grid, threads, 0, s>>>(x, out, C, H, W, Wp, pad_w, rows);
+  else pad_input_kernel<16><<<grid, threads, 0, s>>>(x, out, C, H, W, Wp, pad_w, rows);
   count(CNT_LAUNCHES);
 }
 
