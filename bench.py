@@ -341,9 +341,10 @@ def main():
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak if peak else None,
                      "traffic": profiled_traffic(per_rank, args.graph) if world == 1 else None,
-                     "traffic_note": "DRAM read+write bytes of the 54 launches of one step "
-                                     "(ncu, profiles/tc_conv_traffic_resnet50_b256.txt)",
-                     "kernel": "tc_conv_kernel", "launches_per_step": per_step,
+                     "traffic_note": "DRAM read+write bytes of the tensor-core launches of one "
+                                     "step (ncu, profiles/tc_conv_traffic_resnet50_b256.txt)",
+                     "kernel": "tc_conv_kernel (+ tc_conv_pn_kernel, stem_pool_kernel)",
+                     "launches_per_step": per_step,
                      "kernel_ms_per_step": tc_total_ms, "peak_source": peaks["source"] +
                      " (sustained cuBLAS bf16)"},
     }
@@ -391,8 +392,28 @@ def write_per_layer(path, g, tc_ms, peaks, ms_step):
             hh = min(H, P * R if R < st[0] else (P - 1) * st[0] + R)
             ww = min(W, Q * S if S < st[1] else (Q - 1) * st[1] + S)
             xin = N * Cg * hh * ww
-            byts = 2 * xin + 2 * K * Cg * R * S + 4 * K + 2 * N * K * P * Q
+            out_elems = N * K * P * Q
             name = f"conv {Cg}->{K} {R}x{S} s{n.attrs['strides'][0]} out {P}x{Q}"
+            extra = 0
+            # what the fused call sequence folds into this launch: a residual operand read,
+            # or (stem) the max pool, which shrinks the tensor that is written
+            cur = n.out
+            for m in g.nodes:
+                if cur not in m.ins:
+                    continue
+                if m.op == "relu":
+                    cur = m.out
+                elif m.op == "add":
+                    extra += 2 * out_elems
+                    cur = m.out
+                elif m.op == "maxpool" and Cg < 16:
+                    out_elems = int(np.prod(g.shapes[m.out]))
+                    xin = N * 4 * H * (W + 8)          # padded channels-last rows, 4 channels
+                    name += " +pool"
+                    break
+                else:
+                    break
+            byts = 2 * xin + 2 * K * Cg * R * S + 4 * K + 2 * out_elems + extra
         else:
             M, Nn = g.shapes[n.out]
             Kd = g.shapes[n.ins[0]][1]
@@ -411,7 +432,8 @@ def write_per_layer(path, g, tc_ms, peaks, ms_step):
                      bound / ms if ms else 0))
     with open(path, "w") as f:
         f.write(f"# {g.name}: per tensor-core launch, ms_per_step {ms_step:.3f}\n")
-        f.write("# layer | GFLOP | MB (bf16 act) | ms | TFLOP/s | GB/s | bound | frac of roofline\n")
+        f.write("# layer | GFLOP | MB (bf16 activations, incl. residual operand) | ms | TFLOP/s | GB/s | "
+                "bound | frac of roofline\n")
         for r in rows:
             f.write(f"{r[0]:40s} {r[1]:9.2f} {r[2]:9.2f} {r[3]:8.4f} {r[4]:8.1f} {r[5]:8.1f} "
                     f"{r[6]:7s} {r[7]:6.3f}\n")
