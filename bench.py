@@ -350,7 +350,7 @@ def main():
     }
     if not args.no_cpu_baseline and world == 1:
         cores = os.cpu_count() or 1
-        sample = 4
+        sample = 16
         v, dt = cpu_baseline_sample(sample, 3)
         line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": cores, "kind": "port",
                                 "sample": f"{sample} images (of the batch-256 workload), fp32 C "
