@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), TC_EPI_THREADS);
+      mbar_init(tempty_bar(s), TC_EPI_THREADS / 32);   // one arrival per epilogue warp
     }
     mbar_init(rfull_bar, 1);
     *abort_flag = 0;
@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  pdl_launch_dependents();   // the next kernel's prologue may overlap this one
+  pdl_wait();                // nothing above touched global memory
 
   const int rows_valid = p.tw * p.th * p.tn;   // pixels per tile (<= 256)
   const int ksteps = p.num_taps * p.cblocks;
@@ -233,7 +235,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
         }
       }
       tc_fence_before();
-      mbar_arrive(tempty_bar(acc));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
       fence_async_smem();
       epi_bar();
       if (leader) {
@@ -604,7 +607,7 @@ static void launch_plan_pn(const Plan &pl, int num_sms, cudaStream_t s) {
     attr_set = true;
   }
   int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
-  tc_conv_pn_kernel<<<grid, TC_THREADS, pl.smem, s>>>(pl.p);
+  tc_launch_pdl(tc_conv_pn_kernel, grid, TC_THREADS, pl.smem, s, pl.p);
 }
 
 static void launch_any(const Plan &pl, int num_sms, cudaStream_t s) {

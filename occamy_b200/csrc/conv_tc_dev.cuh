@@ -186,6 +186,16 @@ __device__ __forceinline__ void tma_store_wait_read() {
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may
+// start while the kernel before it in the stream is still running.  `pdl_wait` returns once
+// that kernel has completed and its writes are visible: nothing before it may touch memory
+// other kernels write or read.  `pdl_launch_dependents` lets the kernel after this one be
+// scheduled as soon as SMs free up, so that its prologue overlaps this kernel's tail.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Two fp32 values in one 64-bit register (packed fp32 arithmetic of sm_100).
 __device__ __forceinline__ uint64_t f2_pack(float a, float b) {
   uint64_t r;
@@ -447,6 +457,10 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Everything above touched only this CTA's shared memory and TMEM, so it may overlap the
+  // previous kernel; from here on global memory is read and written.
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int rows_valid = p.tw * p.th * p.tn;
   const int ksteps = p.num_taps * p.cblocks;
@@ -800,6 +814,23 @@ bool tc_launch_128_64(const TcParams &p, int mode, int grid, size_t smem, cudaSt
 bool tc_launch_64_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
 bool tc_launch_32_32(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
 
+// Launch with programmatic stream serialisation (see pdl_wait).
+template <typename Kernel, typename Params>
+inline void tc_launch_pdl(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t s,
+                          const Params &p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 // Body shared by the launchers: picks the instantiation for `mode`, raises its dynamic
 // shared memory limit once, launches.
 template <int BN, int DC, int MODE>
@@ -810,7 +841,7 @@ inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
     attr_set = true;
   }
-  tc_conv_kernel<BN, DC, TC_EW, MODE><<<grid, 64 + 128 * TC_EW + 32, smem, s>>>(p);
+  tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32, smem, s, p);
 }
 template <int BN, int DC, bool WITH_F32, bool WITH_HALO = false>
 inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {

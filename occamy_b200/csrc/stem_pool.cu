@@ -171,6 +171,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem_pool_kernel(const StemPara
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   int err_code = 0;
+  pdl_launch_dependents();   // the next kernel's prologue may overlap this one
+  pdl_wait();
 
   // pooled rows [i0, i1) and convolution rows [h_lo, h_hi] of a unit
   auto unit_rows = [&](int unit, int &n, int &i0, int &i1, int &h_lo, int &h_hi) {
@@ -503,7 +505,7 @@ bool launch_stem_pool(const StemPoolArgs &a, int *err_word, int num_sms, cudaStr
     OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot], s));
   }
   // at least half of the shared memory, so that one CTA (one TMEM allocation) runs per SM
-  stem_pool_kernel<<<grid, ST_THREADS, smem < 120 * 1024 ? 120 * 1024 : smem, s>>>(p);
+  tc_launch_pdl(stem_pool_kernel, grid, ST_THREADS, smem < 120 * 1024 ? 120 * 1024 : smem, s, p);
   if (prof_slot >= 0) OCC_CUDA(cudaEventRecord(r.prof_events[2 * prof_slot + 1], s));
   count(CNT_LAUNCHES);
   count(CNT_TC_LAUNCHES);
