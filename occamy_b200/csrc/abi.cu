@@ -69,9 +69,14 @@ enum PackLayout { PACK_KRSC = 1, PACK_DW = 2, PACK_FOLD = 3, PACK_RAW = 4, PACK_
 // Device pointer of the packed form of the filter at `w`; resident across calls when the
 // filter was uploaded from host memory (a compiled model's constant), otherwise packed
 // into scratch.  `packed_bytes` is the size of the packed form.
+// Set by packed_weights: the returned copy was already on the device before this call (no
+// kernel or copy was enqueued to produce it).
+bool g_pack_was_resident = false;
+
 void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int C, int R, int S,
                      int Sp, int Cp) {
   Runtime &r = rt();
+  g_pack_was_resident = false;
   uintptr_t base;
   TensorRec *rec = reg_find(w, &base);
   const bool cacheable = r.cache_weights && rec && base == (uintptr_t)w && rec->host_src;
@@ -80,8 +85,10 @@ void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int
     key.src = rec->host_src;
     key.bytes = rec->host_bytes;
     auto it = r.wcache.find(key);
-    if (it != r.wcache.end() && it->second.hash == rec->host_hash && it->second.bytes == packed_bytes)
+    if (it != r.wcache.end() && it->second.hash == rec->host_hash && it->second.bytes == packed_bytes) {
+      g_pack_was_resident = true;
       return it->second.dev;
+    }
   }
   ensure_f32(w);
   void *dst = nullptr;
@@ -119,6 +126,7 @@ const float *resident_f32(const float *p, size_t bytes) {
     const float *d = (const float *)packed_weights(p, PACK_RAW, bytes, 0, 0, 0, 0, 0, 0);
     if (d) return d;
   }
+  g_pack_was_resident = false;
   ensure_f32(p);
   return p;
 }
@@ -205,7 +213,12 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
                                        g.R, g.S, 0, 0);
   }
   if (!a.w) return false;
+  bool ready = g_pack_was_resident;
   a.bias = bias ? resident_f32(bias, (size_t)g.K * 4) : nullptr;
+  if (bias) ready = ready && g_pack_was_resident;
+  // filter and bias were on the device before this call: the kernel may fetch them while the
+  // kernel before it is still running
+  a.consts_ready = ready ? 1 : 0;
   job.depthwise = false;
   job.g = g;
   job.bias_set = bias != nullptr;
@@ -837,6 +850,7 @@ float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, 
       const float *bd = resident_f32(B, (size_t)g.K * 4);
       if (g_pending.depthwise) g_pending.bias = bd;
       else g_pending.a.bias = bd;
+      if (!g_pack_was_resident) g_pending.a.consts_ready = 0;
       g_pending.bias_set = true;
       pending_retarget(out);
       return out;

@@ -444,6 +444,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
   p.out_f32 = a.out_f32;
   p.ldo = a.ldo;
   p.err = err_word;
+  p.consts_ready = a.consts_ready;
   const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
                     a.pad_w == 0 && a.w_step == 0;
   // output grid the tiles are cut from

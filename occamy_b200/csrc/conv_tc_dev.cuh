@@ -45,6 +45,8 @@ struct alignas(64) TcParams {
   float *out_f32;
   int ldo;
   int m_total;
+  int consts_ready;      // filter and bias were resident before the launch: they may be
+                         // fetched before the previous kernel in the stream has finished
   int halo;              // 3x3 halo form: the A block of a tile is loaded once, the taps are
                          // windows of it (see TC_MODE_HALO); then:
   int halo_wp;           //   pixels per block row (output width + 2)
@@ -457,14 +459,34 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  // Everything above touched only this CTA's shared memory and TMEM, so it may overlap the
-  // previous kernel; from here on global memory is read and written.
-  pdl_launch_dependents();
-  pdl_wait();
-
   const int rows_valid = p.tw * p.th * p.tn;
   const int ksteps = p.num_taps * p.cblocks;
   int err_code = 0;
+  // Everything above touched only this CTA's shared memory and TMEM, so it may overlap the
+  // previous kernel in the stream.  Resident weights may be fetched early as well: the
+  // producer requests the weight tiles of its first k-steps (halo form: all of them) now.
+  int pre_b = 0;   // leading k-steps of the first tile whose weight tile is already on its way
+  if (warp == 0 && lane == 0 && p.consts_ready && (int)blockIdx.x < p.total_tiles) {
+    if constexpr (HALO) {
+      mbar_expect_tx(wfull_bar, (uint32_t)p.num_taps * b_bytes);
+      for (int t = 0; t < p.num_taps; ++t)
+        tma_load_3d(sB + t * b_bytes, &p.tmB, wfull_bar, 0, 0, t);
+    } else {
+      const TcTile tl = tc_decode<BN>(p, blockIdx.x);
+      pre_b = min(stages, ksteps);
+      int t = 0, cb = 0;
+      for (int s = 0; s < pre_b; ++s) {
+        mbar_expect_tx(full_bar(s), (uint32_t)rows_valid * bk * 2u + b_bytes);
+        tma_load_3d(sB + s * b_bytes, &p.tmB, full_bar(s), cb * bk, tl.k0, t);
+        if (++cb == p.cblocks) {
+          cb = 0;
+          ++t;
+        }
+      }
+    }
+  }
+  pdl_launch_dependents();
+  pdl_wait();   // from here on memory that other kernels write is read and written
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -472,10 +494,13 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
       int stage = 0;
       uint32_t phase = 0;
       if constexpr (HALO) {
-        // weights of all taps once, then one input block per tile
-        mbar_expect_tx(wfull_bar, (uint32_t)p.num_taps * b_bytes);
-        for (int t = 0; t < p.num_taps; ++t)
-          tma_load_3d(sB + t * b_bytes, &p.tmB, wfull_bar, 0, 0, t);
+        // weights of all taps once (unless they were requested early), then one input block
+        // per tile
+        if (!p.consts_ready) {
+          mbar_expect_tx(wfull_bar, (uint32_t)p.num_taps * b_bytes);
+          for (int t = 0; t < p.num_taps; ++t)
+            tma_load_3d(sB + t * b_bytes, &p.tmB, wfull_bar, 0, 0, t);
+        }
         const uint32_t blk_bytes = (uint32_t)((p.th + 2) * p.halo_wp) * 128u;
         for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
           const TcTile tl = tc_decode<BN>(p, tile);
@@ -502,10 +527,14 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
               err_code = 1;
               break;
             }
-            mbar_expect_tx(full_bar(stage), tx_bytes);
+            if (pre_b > 0) {
+              --pre_b;   // this stage's barrier is armed and its weight tile on its way
+            } else {
+              mbar_expect_tx(full_bar(stage), tx_bytes);
+              tma_load_3d(sB + stage * b_bytes, &p.tmB, full_bar(stage), cb * bk, tl.k0, t);
+            }
             tma_load_4d(sA + stage * a_bytes, &p.tmA[tap.map], full_bar(stage), cb * bk,
                         tl.q0 + tap.dw, tl.p0 + tap.dh, tl.n0);
-            tma_load_3d(sB + stage * b_bytes, &p.tmB, full_bar(stage), cb * bk, tl.k0, t);
             if (++stage == stages) {
               stage = 0;
               phase ^= 1u;

@@ -93,6 +93,9 @@ struct TcConvArgs {
   // Folded form only (else 0): elements between the A vectors of neighbouring output
   // columns, and elements per input row; the vectors overlap when w_step < Cf.
   int w_step, row_elems;
+  // Filter (and bias) were resident on the device before this call was made, i.e. no work
+  // enqueued earlier in the stream produces them.
+  int consts_ready;
 };
 // ---- few-channel convolution fused with the 3x3 / stride 2 / pad 1 max pool after it -----
 struct StemPoolArgs {
