@@ -13,8 +13,9 @@
 //
 // One persistent CTA per SM works through units of (image, band of pooled rows):
 //   warp 0      producer (one lane): bulk-copies the weights once, then input rows into a ring
-//   warp 1      MMA issuer (one lane): per convolution row R taps x Cf/16 tcgen05.mma
-//               (128 x 64 x 16) into one of four TMEM accumulators; releases input rows
+//   2 warps     MMA issuers (one lane each, alternate convolution rows): per row R taps x
+//               Cf/16 tcgen05.mma (128 x 64 x 16) into one of four TMEM accumulators;
+//               release input rows
 //   8 warps     epilogue: accumulator -> + bias -> clamp -> bf16 -> convolution-row ring in
 //               shared memory (swizzled so that a warp's 128-byte rows spread over banks)
 //   8 warps     pool: max over the 3x3 windows of three ring rows -> global memory
@@ -29,7 +30,8 @@ namespace {
 
 constexpr int ST_EPI_WARPS = 8;    // two per TMEM lane quadrant, 32 channels each
 constexpr int ST_POOL_WARPS = 8;
-constexpr int ST_THREADS = 64 + 32 * (ST_EPI_WARPS + ST_POOL_WARPS);
+constexpr int ST_ISSUER_B = 2 + ST_EPI_WARPS + ST_POOL_WARPS;   // warp of the second MMA issuer
+constexpr int ST_THREADS = 32 * (ST_ISSUER_B + 1);
 constexpr int ST_NIN = 8;     // input ring slots (a slot holds stride_h rows)
 constexpr int ST_NCR = 6;     // convolution-row ring slots
 constexpr int ST_NACC = 4;    // TMEM accumulators (64 columns each)
@@ -141,7 +143,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem_pool_kernel(const StemPara
     mbar_init(w_full, 1);
     for (int s = 0; s < ST_NIN; ++s) {
       mbar_init(in_full(s), 1);
-      mbar_init(in_empty(s), 1);
+      mbar_init(in_empty(s), 2);   // both MMA issuers hand a group back
     }
     for (int s = 0; s < ST_NACC; ++s) {
       mbar_init(tfull(s), 1);
@@ -215,14 +217,19 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem_pool_kernel(const StemPara
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == ST_ISSUER_B) {
+    // ------------------------------------------------------------ MMA issuers
+    // Two threads (in two warps) take alternate convolution rows: the MMAs are short (64
+    // columns) and one thread cannot issue them as fast as the tensor core retires them.
+    // Both read every input group, so a group goes back to the producer when both have
+    // committed it (each does so once it will not read the group again).
     if (lane == 0) {
+      const int me = warp == 1 ? 0 : 1;
       constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) |
                                  ((uint32_t)(ST_K >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       if (!mbar_wait_hot(w_full, 0, abort_flag)) err_code = 2;
       uint32_t gbase = 0;   // ring index of the unit's first group
-      uint32_t c = 0;       // convolution rows issued so far
+      uint32_t cbase = 0;   // convolution rows before this unit
       const int kk_n = p.Cf / 16;
       const uint64_t adesc0 = desc_plain(sIn, 16, 128);
       const uint64_t bdesc0 = desc_plain(sW, ST_K * 16, 128);
@@ -235,31 +242,31 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem_pool_kernel(const StemPara
       for (int unit = blockIdx.x; unit < p.units && !err_code; unit += gridDim.x) {
         int n, i0, i1, h_lo, h_hi;
         unit_rows(unit, n, i0, i1, h_lo, h_hi);
-        // the first convolution row of a unit needs all its groups; later ones one new group
-        for (int k = 0; k < p.G - 1; ++k) {
-          const uint32_t gq = gbase + (uint32_t)k;
-          if (!mbar_wait_hot(in_full(gq % ST_NIN), (gq / ST_NIN) & 1u, abort_flag)) err_code = 4;
-        }
-        for (int h = h_lo; h <= h_hi && !err_code; ++h, ++c) {
+        const int rows = h_hi - h_lo + 1;
+        const int groups = rows + p.G - 1;        // groups the producer loads for this unit
+        int waited = 0, released = 0;             // groups (unit-relative) waited for / committed
+        // rows of the unit whose running number (over all units) has my parity
+        for (int k = (int)((cbase + (uint32_t)me) & 1u); k < rows && !err_code; k += 2) {
+          const uint32_t c = cbase + (uint32_t)k;
           const uint32_t a = c % ST_NACC, aph = (c / ST_NACC) & 1u;
-          const uint32_t g0 = gbase + (uint32_t)(h - h_lo);          // ring index of group h
-          const uint32_t gn = g0 + (uint32_t)(p.G - 1);              // the group that is new
           if (!mbar_wait_hot(tempty(a), aph ^ 1u, abort_flag)) {
             err_code = 3;
             break;
           }
-          if (!mbar_wait_hot(in_full(gn % ST_NIN), (gn / ST_NIN) & 1u, abort_flag)) {
-            err_code = 4;
-            break;
+          for (; waited < k + p.G; ++waited) {     // row k reads groups k ... k + G - 1
+            const uint32_t gq = gbase + (uint32_t)waited;
+            if (!mbar_wait_hot(in_full(gq % ST_NIN), (gq / ST_NIN) & 1u, abort_flag)) err_code = 4;
           }
+          if (err_code) break;
           tc_fence_after();
           // taps whose input row lies inside the image (a row of padding contributes nothing)
+          const int h = h_lo + k;
           const int jb = h * p.stride_h - p.pad_h;
           const int r_lo = max(0, -jb), r_hi = min(p.R - 1, p.H - 1 - jb);
           const uint32_t d_tmem = tmem_base + a * ST_K;
-          const uint32_t s0 = g0 % ST_NIN;
-          // The issue code is straight-line: the MMAs are short (64 columns), one thread
-          // issues them, and every taken branch costs it more than an MMA.
+          const uint32_t s0 = (gbase + (uint32_t)k) % ST_NIN;
+          // The issue code is straight-line: every taken branch costs the issuing thread more
+          // than an MMA.
           if (p.R == 7 && kk_n == 2 && p.stride_h == 2) {
             issue_row<7, 2, 2>(d_tmem, r_lo, r_hi, s0, a_lo0, a_hi, slot_desc, row_desc, b_lo0, b_hi,
                                tap_desc, kstep_desc, IDESC);
@@ -277,12 +284,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem_pool_kernel(const StemPara
             }
           }
           tc_commit(tfull(a));
-          tc_commit(in_empty(s0));     // group h goes back to the producer
+          // my next row is k + 2: groups below it are of no more use to me
+          for (; released < k + 2 && released < groups; ++released)
+            tc_commit(in_empty((gbase + (uint32_t)released) % ST_NIN));
         }
-        // the groups only the unit's last rows read
-        const uint32_t gend = gbase + (uint32_t)(h_hi - h_lo + 1);
-        for (int k = 0; k < p.G - 1; ++k) tc_commit(in_empty((gend + (uint32_t)k) % ST_NIN));
-        gbase = gend + (uint32_t)(p.G - 1);
+        // whatever of the unit I have not committed yet (also when none of its rows was mine)
+        for (; released < groups; ++released)
+          tc_commit(in_empty((gbase + (uint32_t)released) % ST_NIN));
+        gbase += (uint32_t)groups;
+        cbase += (uint32_t)rows;
       }
     }
   } else if (warp < 2 + ST_EPI_WARPS) {
@@ -349,7 +359,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) stem_pool_kernel(const StemPara
         if (lane == 0) mbar_arrive(cr_full(cs));
       }
     }
-  } else {
+  } else if (warp < ST_ISSUER_B) {
     // ------------------------------------------------------------ pool
     const int pt = threadIdx.x - 32 * (2 + ST_EPI_WARPS);
     constexpr int PT = 32 * ST_POOL_WARPS;
