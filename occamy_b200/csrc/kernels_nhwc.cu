@@ -210,32 +210,45 @@ void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P,
   count(CNT_LAUNCHES);
 }
 
-// Global average pool: [N][HW][C] bf16 -> [N][C] fp32; thread per (n, 8 channels).
-__global__ void gap_bf16_kernel(const bf16x8 *__restrict__ x, float *__restrict__ y, int HW,
-                                int C8, int64_t total) {
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int c8 = (int)(i % C8);
-    const int64_t n = i / C8;
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+// Global average pool: [N][HW][C] bf16 -> [N][C] fp32.  One CTA per (image, 64-channel group
+// of 8 threads): the GAP_ROWS thread rows split the pixels, each thread sums 8 channels of its
+// pixels with 16-byte loads (a warp covers 4 pixels x 128 bytes), partial sums meet in shared
+// memory.
+constexpr int GAP_ROWS = 16;
+__global__ void __launch_bounds__(8 * GAP_ROWS) gap_bf16_kernel(const bf16x8 *__restrict__ x,
+                                                               float *__restrict__ y, int HW, int C8) {
+  __shared__ float part[GAP_ROWS][8][8];
+  const int lane8 = threadIdx.x & 7, prow = threadIdx.x >> 3;
+  const int c8 = blockIdx.x * 8 + lane8;
+  const int64_t n = blockIdx.y;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (c8 < C8) {
     const bf16x8 *xp = x + n * HW * C8 + c8;
-    for (int p = 0; p < HW; ++p) {
+    for (int p = prow; p < HW; p += GAP_ROWS) {
       float f[8];
       unpack8(xp[(int64_t)p * C8], f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] += f[k];
     }
-    const float inv = 1.0f / (float)HW;
-    float4 *yp = (float4 *)(y + i * 8);
-    yp[0] = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
-    yp[1] = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k) part[prow][lane8][k] = acc[k];
+  __syncthreads();
+  if (threadIdx.x < 64) {            // thread = (channel group lane, channel within it)
+    const int l = threadIdx.x >> 3, k = threadIdx.x & 7;
+    float s = 0.0f;
+#pragma unroll
+    for (int r = 0; r < GAP_ROWS; ++r) s += part[r][l][k];
+    const int c = (blockIdx.x * 8 + l) * 8 + k;
+    if (blockIdx.x * 8 + l < C8) y[n * C8 * 8 + c] = s * (1.0f / (float)HW);
   }
 }
 
 void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t s) {
-  const int64_t total = (int64_t)N * (C / 8);
-  if (total == 0) return;
-  gap_bf16_kernel<<<grid_for(total, 128), 128, 0, s>>>((const bf16x8 *)x, y, HW, C / 8, total);
+  if ((int64_t)N * C == 0) return;
+  const int C8 = C / 8;
+  const dim3 grid((unsigned)((C8 + 7) / 8), (unsigned)N);
+  gap_bf16_kernel<<<grid, 8 * GAP_ROWS, 0, s>>>((const bf16x8 *)x, y, HW, C8);
   count(CNT_LAUNCHES);
 }
 
