@@ -570,7 +570,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
   const size_t fixed0 = pn ? 1024 + 2 * 256 * 128 + 8 * 80
                            : 1024 + (size_t)p.bias_floats * 4 + 8 * 80 +
                                  (halo ? (size_t)9 * bn * bk * 2 : 0);   // halo: resident weights
-  int dbuf = pn ? 0 : 3;
+  int dbuf = pn ? 0 : (3 + TC_NSTORE - 1) / TC_NSTORE * TC_NSTORE;
   int stages;
   if (!pn && a.residual) {
     // The residual slab of an output slab is fetched into its buffer ahead of time; with
@@ -582,6 +582,8 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
     dbuf = (int)((TC_SMEM_LIMIT - fixed0 - min_stages * stage_bytes) / slab_bytes);
     if (dbuf > 8) dbuf = 8;
     if (dbuf < 3) dbuf = 3;
+    dbuf = dbuf / TC_NSTORE * TC_NSTORE;
+    if (dbuf < TC_NSTORE * 2) dbuf = TC_NSTORE * 2;
   }
   const size_t fixed = fixed0 + dbuf * slab_bytes;
   stages = (int)((TC_SMEM_LIMIT - fixed) / stage_bytes);

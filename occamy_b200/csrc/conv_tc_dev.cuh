@@ -13,6 +13,7 @@ namespace occ {
 
 constexpr int TC_THREADS = 320;      // pixel-N kernel: 1 producer warp + 1 MMA warp + 8 epilogue warps
 constexpr int TC_EW = 2;             // tc_conv_kernel: epilogue warps per TMEM lane quadrant
+constexpr int TC_NSTORE = 2;         // tc_conv_kernel: slab-store threads (slab buffers: a multiple)
 constexpr int TC_EPI_THREADS = 256;
 constexpr int TC_DBUF = 3;           // output slab buffers in shared memory
 constexpr int TC_MAX_TAPS = 32;
@@ -383,7 +384,7 @@ __device__ __forceinline__ TcTile tc_decode(const TcParams &p, int tile) {
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in the
 // error word, drains and returns.
 template <int BN, int DC, int EW, int MODE>
-__global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
+__global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE, 1)
     tc_conv_kernel(const __grid_constant__ TcParams p) {
   constexpr bool RES = (MODE & TC_MODE_RES) != 0;
   constexpr bool CLAMP = (MODE & TC_MODE_CLAMP) != 0;
@@ -624,62 +625,72 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32, 1)
       }
       }
     }
-  } else if (warp == STORE_WARP) {
+  } else if (warp >= STORE_WARP) {
     // ------------------------------------------------------------ slab store
-    // One thread owns the output slab buffers: it hands a buffer to the epilogue warps
-    // ("ready": free, or holding the residual slab the epilogue adds in place), and sends a
-    // written slab to global memory.  The epilogue warps never wait for one another.
+    // TC_NSTORE threads (one per warp) own the output slab buffers, slab d belonging to
+    // thread d % TC_NSTORE: the owner hands the buffer to the epilogue warps ("ready": free,
+    // or holding the residual slab the epilogue adds in place) and sends the written slab to
+    // global memory.  The epilogue warps never wait for one another.  More than one thread,
+    // because a single thread's issue rate (TMA store + residual load + bookkeeping per slab)
+    // limits the layers whose tiles are short.
     if constexpr (!F32) {
       if (lane == 0) {
-        uint32_t n_ready = 0, rb = 0;      // slabs handed out so far; buffer of the next one
-        int pf_tile = blockIdx.x, pf_sl = 0;
-        TcTile pf = tc_decode<BN>(p, pf_tile);
-        auto make_ready = [&](uint32_t upto) {
-          while (n_ready <= upto && pf_tile < p.total_tiles) {
-            if constexpr (RES) {
-              mbar_expect_tx(rfull_bar(rb), (uint32_t)rows_valid * DC * 2u);
-              tma_load_4d(sD + rb * SLAB_BYTES, &p.tmR, rfull_bar(rb), pf.k0 + pf_sl * DC, pf.q0,
-                          pf.p0, pf.n0);
-            } else {
-              mbar_arrive(rfull_bar(rb));
-            }
-            ++n_ready;
-            if (++rb == (uint32_t)dbuf) rb = 0;
-            if (++pf_sl == min(NSLAB, (p.K - pf.k0 + DC - 1) / DC)) {
-              pf_sl = 0;
-              pf_tile += gridDim.x;
-              pf = tc_decode<BN>(p, pf_tile);
+        const uint32_t me = (uint32_t)(warp - STORE_WARP);
+        auto nslab_of = [&](const TcTile &t) { return min(NSLAB, (p.K - t.k0 + DC - 1) / DC); };
+        // cursor over the slabs this thread makes ready: (tile, slab) of slab number r_next
+        uint32_t r_next = me;
+        int r_tile = blockIdx.x, r_sl = 0;
+        TcTile rt_ = tc_decode<BN>(p, r_tile);
+        int r_ns = nslab_of(rt_);
+        auto r_advance = [&]() {          // one slab further
+          if (++r_sl == r_ns) {
+            r_sl = 0;
+            r_tile += gridDim.x;
+            if (r_tile < p.total_tiles) {
+              rt_ = tc_decode<BN>(p, r_tile);
+              r_ns = nslab_of(rt_);
             }
           }
         };
-        make_ready(dbuf - 1);
-        uint32_t d_iter = 0, b = 0, ph = 0;
+        for (uint32_t i = 0; i < me && r_tile < p.total_tiles; ++i) r_advance();
+        auto ready_one = [&]() {          // hand out slab r_next, move to my next one
+          if (r_tile >= p.total_tiles) return;
+          const uint32_t rb = r_next % (uint32_t)dbuf;
+          if constexpr (RES) {
+            mbar_expect_tx(rfull_bar(rb), (uint32_t)rows_valid * DC * 2u);
+            tma_load_4d(sD + rb * SLAB_BYTES, &p.tmR, rfull_bar(rb), rt_.k0 + r_sl * DC, rt_.q0,
+                        rt_.p0, rt_.n0);
+          } else {
+            mbar_arrive(rfull_bar(rb));
+          }
+          r_next += TC_NSTORE;
+          for (int i = 0; i < TC_NSTORE && r_tile < p.total_tiles; ++i) r_advance();
+        };
+        for (int i = 0; i < dbuf / TC_NSTORE; ++i) ready_one();     // every buffer starts out free
+        uint32_t d = 0;   // running slab number
+        bool first = true;   // my first store frees no buffer yet
         for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
           const TcTile tl = tc_decode<BN>(p, tile);
-          const int nslab = min(NSLAB, (p.K - tl.k0 + DC - 1) / DC);
-          for (int sl = 0; sl < nslab; ++sl) {
+          const int nslab = nslab_of(tl);
+          for (int sl = 0; sl < nslab; ++sl, ++d) {
+            if (d % TC_NSTORE != me) continue;
+            const uint32_t b = d % (uint32_t)dbuf, ph = (d / (uint32_t)dbuf) & 1u;
             if (!mbar_wait(dfull_bar(b), ph, abort_flag)) {
               err_code = 6;
               break;
             }
             tma_store_4d(&p.tmD, sD + b * SLAB_BYTES, tl.k0 + sl * DC, tl.q0, tl.p0, tl.n0);
             tma_store_commit();
-            // once at most dbuf - 2 stores are still reading, the buffer of slab
-            // d_iter - (dbuf - 2) is free and slab d_iter + 2 may use it
-            switch (dbuf) {
-              case 3: tma_store_wait_read<1>(); break;
-              case 4: tma_store_wait_read<2>(); break;
-              case 5: tma_store_wait_read<3>(); break;
-              case 6: tma_store_wait_read<4>(); break;
-              case 7: tma_store_wait_read<5>(); break;
-              default: tma_store_wait_read<6>(); break;
+            // Once at most dbuf / TC_NSTORE - 1 of my stores are still reading, the buffer of
+            // my slab before this one is free: the slab dbuf further on may have it.
+            switch (dbuf / TC_NSTORE) {
+              case 1: tma_store_wait_read<0>(); break;
+              case 2: tma_store_wait_read<1>(); break;
+              case 3: tma_store_wait_read<2>(); break;
+              default: tma_store_wait_read<3>(); break;
             }
-            make_ready(d_iter + 2);
-            ++d_iter;
-            if (++b == (uint32_t)dbuf) {
-              b = 0;
-              ph ^= 1u;
-            }
+            if (!first) ready_one();
+            first = false;
           }
         }
         tma_store_wait_read<0>();
@@ -870,7 +881,7 @@ inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
     attr_set = true;
   }
-  tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32, smem, s, p);
+  tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32 * TC_NSTORE, smem, s, p);
 }
 template <int BN, int DC, bool WITH_F32, bool WITH_HALO = false>
 inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
