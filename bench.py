@@ -404,6 +404,11 @@ def write_per_layer(path, g, tc_ms, peaks, ms_step):
                 if m.op == "relu":
                     cur = m.out
                 elif m.op == "add":
+                    # the add folds into the convolution right before it; the other branch's
+                    # convolution only produces the operand
+                    between = g.nodes[g.nodes.index(n) + 1:g.nodes.index(m)]
+                    if any(b.op == "conv" for b in between):
+                        break
                     extra += 2 * out_elems
                     cur = m.out
                 elif m.op == "maxpool" and Cg < 16:

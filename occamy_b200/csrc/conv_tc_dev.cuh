@@ -379,12 +379,13 @@ __device__ __forceinline__ TcTile tc_decode(const TcParams &p, int tile) {
 //   warps 2..2+4*EW   epilogue: tcgen05.ld the finished accumulator, add bias / residual,
 //                     activation, convert to bf16, write 128-pixel slabs of DC channels into
 //                     swizzled shared memory
-//   last warp         slab store (one lane): hands slab buffers to the epilogue (empty, or
-//                     pre-loaded with the residual slab) and TMA-stores written slabs
+//   TC_NSTORE warps   slab store (one lane each): hand slab buffers to the epilogue (empty,
+//                     or pre-loaded with the residual slab) and TMA-store written slabs
+//   last warp         second MMA issuer of the halo form (idle otherwise)
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in the
 // error word, drains and returns.
 template <int BN, int DC, int EW, int MODE>
-__global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE, 1)
+__global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
     tc_conv_kernel(const __grid_constant__ TcParams p) {
   constexpr bool RES = (MODE & TC_MODE_RES) != 0;
   constexpr bool CLAMP = (MODE & TC_MODE_CLAMP) != 0;
@@ -545,7 +546,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE, 1)
       }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (HALO && warp == STORE_WARP + TC_NSTORE)) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       int stage = 0, acc = 0;
@@ -561,18 +562,31 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE, 1)
         const uint32_t stage_desc = a_bytes >> 4, tap_desc = b_bytes >> 4;
         const uint32_t wp8 = (uint32_t)p.halo_wp * 8u;   // one block row in descriptor units
         if (!mbar_wait_hot(wfull_bar, 0, abort_flag)) err_code = 3;
-        for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-          if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+        // Two issuing threads take alternate tiles (and with them alternate accumulators):
+        // 36 MMAs of 48 cycles per tile are more than one thread issues in that time.
+        const int me = warp == 1 ? 0 : 1;
+        int it = 0;   // tiles of this CTA so far
+        for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x, ++it) {
+          if (++stage == stages) {   // ring stage and accumulator advance with every tile
+            stage = 0;
+            phase ^= 1u;
+          }
+          const int my_stage = stage == 0 ? stages - 1 : stage - 1;
+          const uint32_t my_phase = stage == 0 ? phase ^ 1u : phase;
+          const int my_acc = it & 1;
+          const uint32_t my_acc_phase = (uint32_t)(it >> 1) & 1u;
+          if ((it & 1) != me) continue;
+          if (!mbar_wait_hot(tempty_bar(my_acc), my_acc_phase ^ 1u, abort_flag)) {
             err_code = 2;
             break;
           }
-          if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
+          if (!mbar_wait_hot(full_bar(my_stage), my_phase, abort_flag)) {
             err_code = 3;
             break;
           }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-          const uint32_t a_lo = a_lo0 + (uint32_t)stage * stage_desc;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(my_acc * BN);
+          const uint32_t a_lo = a_lo0 + (uint32_t)my_stage * stage_desc;
 #pragma unroll
           for (int t = 0; t < 9; ++t) {
             const uint32_t at = a_lo + (uint32_t)(t / 3) * wp8 + (uint32_t)(t % 3) * 8u;
@@ -581,14 +595,8 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE, 1)
             for (int kk = 0; kk < 4; ++kk)
               mma_lohi(d_tmem, at + 2 * kk, a_hi, bt + 2 * kk, b_hi, IDESC, (t | kk) ? 1u : 0u);
           }
-          tc_commit(empty_bar(stage));
-          tc_commit(tfull_bar(acc));
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-          acc ^= 1;
-          if (acc == 0) acc_phase ^= 1u;
+          tc_commit(empty_bar(my_stage));
+          tc_commit(tfull_bar(my_acc));
         }
       } else {
       for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
@@ -625,7 +633,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE, 1)
       }
       }
     }
-  } else if (warp >= STORE_WARP) {
+  } else if (warp >= STORE_WARP && warp < STORE_WARP + TC_NSTORE) {
     // ------------------------------------------------------------ slab store
     // TC_NSTORE threads (one per warp) own the output slab buffers, slab d belonging to
     // thread d % TC_NSTORE: the owner hands the buffer to the epilogue warps ("ready": free,
@@ -696,7 +704,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE, 1)
         tma_store_wait_read<0>();
       }
     }
-  } else {
+  } else if (warp < STORE_WARP) {
     // ------------------------------------------------------------ epilogue (4 * EW warps)
     const int quad = warp & 3;               // TMEM lane quadrant this warp may read
     const int part = (warp - 2) >> 2;        // which part of a slab's channels
@@ -881,7 +889,8 @@ inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
     attr_set = true;
   }
-  tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32 * TC_NSTORE, smem, s, p);
+  tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32 * TC_NSTORE + 32, smem,
+                s, p);
 }
 template <int BN, int DC, bool WITH_F32, bool WITH_HALO = false>
 inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
