@@ -573,11 +573,10 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
   int dbuf = pn ? 0 : (3 + TC_NSTORE - 1) / TC_NSTORE * TC_NSTORE;
   int stages;
   if (!pn && a.residual) {
-    // The residual slab of an output slab is fetched into its buffer ahead of time; with
-    // short reductions a slab is consumed faster than the fetch takes, so those layers
-    // trade ring stages (down to what one tile needs, at least two) for slab buffers.
-    const int ks = a.R * a.S * (a.Cf / bk);
-    int min_stages = ks < 3 ? 2 : 3;
+    // The residual slab of an output slab is fetched into its buffer ahead of time, and a
+    // slab is consumed faster than the fetch takes: whatever shared memory three ring stages
+    // leave goes to slab buffers.
+    int min_stages = 3;
     if (const char *f = getenv("OCCAMY_TC_RES_STAGES")) min_stages = atoi(f) > 1 ? atoi(f) : min_stages;  // tuning aid
     dbuf = (int)((TC_SMEM_LIMIT - fixed0 - min_stages * stage_bytes) / slab_bytes);
     if (dbuf > 8) dbuf = 8;

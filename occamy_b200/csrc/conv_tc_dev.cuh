@@ -676,7 +676,6 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
         };
         for (int i = 0; i < dbuf / TC_NSTORE; ++i) ready_one();     // every buffer starts out free
         uint32_t d = 0;   // running slab number
-        bool first = true;   // my first store frees no buffer yet
         for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
           const TcTile tl = tc_decode<BN>(p, tile);
           const int nslab = nslab_of(tl);
@@ -689,16 +688,13 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
             }
             tma_store_4d(&p.tmD, sD + b * SLAB_BYTES, tl.k0 + sl * DC, tl.q0, tl.p0, tl.n0);
             tma_store_commit();
-            // Once at most dbuf / TC_NSTORE - 1 of my stores are still reading, the buffer of
-            // my slab before this one is free: the slab dbuf further on may have it.
-            switch (dbuf / TC_NSTORE) {
-              case 1: tma_store_wait_read<0>(); break;
-              case 2: tma_store_wait_read<1>(); break;
-              case 3: tma_store_wait_read<2>(); break;
-              default: tma_store_wait_read<3>(); break;
-            }
-            if (!first) ready_one();
-            first = false;
+            // The store has read its buffer out long before my next slab is written (the
+            // other store thread's slab comes in between), so wait for that here and give
+            // the buffer straight to the slab dbuf further on: every buffer that is not in
+            // this one store is then filling (residual fetch, epilogue), which is what hides
+            // the residual's memory latency.
+            tma_store_wait_read<0>();
+            ready_one();
           }
         }
         tma_store_wait_read<0>();
