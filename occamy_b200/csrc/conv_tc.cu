@@ -549,7 +549,9 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
   // For 256-wide tiles with a long reduction, 32-channel slabs free enough shared memory
   // for a fourth ring stage, which those layers need more than a cheap epilogue.
   const int ksteps64 = (a.R * a.S * a.Cf + 63) / 64;
-  const int dc = pn ? 64 : (bn < 64 ? bn : (bn == 256 && bk == 64 && ksteps64 >= 16 ? 32 : 64));
+  int dc = pn ? 64 : (bn < 64 ? bn : (bn == 256 && bk == 64 && ksteps64 >= 16 ? 32 : 64));
+  if (const char *f = getenv("OCCAMY_TC_DC"))   // tuning aid: slab width of the 256-wide tiles
+    if (!pn && bn == 256 && (atoi(f) == 32 || atoi(f) == 64)) dc = atoi(f);
   pl.dc = dc;
   pl.mode = a.out_f32 ? (TC_MODE_F32 | TC_MODE_CLAMP)
                       : ((a.residual ? TC_MODE_RES : 0) | (a.act == ACT_RELU ? 0 : TC_MODE_CLAMP) |
