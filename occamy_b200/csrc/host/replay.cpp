@@ -21,6 +21,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -135,6 +136,8 @@ struct Program {
   std::vector<Buffer> bufs;
   std::vector<Instr> prog;
   bool pool = true;
+  int pool_mode = 1;       // 1: the reference's first fit; 2: offline greedy-by-size
+  int64_t live_peak = 0;   // lower bound of any plan: most bytes live at one time
   int64_t pool_bytes = 0;
   int64_t sum_bytes = 0;   // sum of all buffer sizes (what per-tensor cudaMalloc would total)
   int64_t counts[16] = {0};
@@ -472,6 +475,63 @@ void place_deallocs(Program &p, bool dealloc_opt) {
   p.prog.swap(out);
 }
 
+// Most bytes live at any point of the program: no plan can use less.
+static int64_t live_bytes_peak(const Program &p) {
+  int64_t live = 0, peak = 0;
+  for (const Instr &in : p.prog) {
+    if (in.kind == I_MALLOC) live += round32(p.bufs[in.out].bytes);
+    else if (in.kind == I_DEALLOC) live -= round32(p.bufs[in.out].bytes);
+    if (live > peak) peak = live;
+  }
+  return peak;
+}
+
+// Offline plan (not the reference's): a compiled model is straight-line code, so every
+// buffer's lifetime [malloc, dealloc] is known before anything is placed.  Buffers go in
+// order of decreasing size, each at the lowest offset where it overlaps no already placed
+// buffer that is live at the same time.  The online first fit below has to place buffers in
+// program order and fragments around long-lived ones.
+static void plan_pool_by_size(Program &p) {
+  struct Item { int buf; int64_t size; int from, to; int64_t offset; };
+  std::vector<Item> items;
+  std::vector<int> item_of(p.bufs.size(), -1);
+  for (size_t i = 0; i < p.prog.size(); ++i) {
+    const Instr &in = p.prog[i];
+    if (in.kind == I_MALLOC) {
+      item_of[in.out] = (int)items.size();
+      items.push_back(Item{in.out, round32(p.bufs[in.out].bytes), (int)i, (int)p.prog.size(), 0});
+    } else if (in.kind == I_DEALLOC && item_of[in.out] >= 0) {
+      items[item_of[in.out]].to = (int)i;
+    }
+  }
+  std::vector<int> order(items.size());
+  for (size_t i = 0; i < order.size(); ++i) order[i] = (int)i;
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int a, int b) { return items[a].size > items[b].size; });
+  std::vector<int> placed;
+  int64_t high = 0;
+  for (int idx : order) {
+    Item &it = items[idx];
+    // offsets of the placed buffers that are live together with this one, in address order
+    std::vector<std::pair<int64_t, int64_t>> busy;
+    for (int q : placed) {
+      const Item &o = items[q];
+      if (o.from <= it.to && it.from <= o.to && o.size > 0) busy.push_back({o.offset, o.offset + o.size});
+    }
+    std::sort(busy.begin(), busy.end());
+    int64_t at = 0;
+    for (const auto &b : busy) {
+      if (b.first - at >= it.size) break;
+      if (b.second > at) at = b.second;
+    }
+    it.offset = at;
+    p.bufs[it.buf].offset = at;
+    if (at + it.size > high) high = at + it.size;
+    placed.push_back(idx);
+  }
+  p.pool_bytes = high;
+}
+
 void plan_pool(Program &p) {
   Planner pl;
   p.sum_bytes = 0;
@@ -485,6 +545,8 @@ void plan_pool(Program &p) {
     }
   }
   p.pool_bytes = pl.high_water;
+  p.live_peak = live_bytes_peak(p);
+  if (p.pool_mode == 2) plan_pool_by_size(p);
 }
 
 }  // namespace
@@ -610,6 +672,8 @@ int occ_op_softmax(void *h, int x, int axis) {
 
 // fuse: 0 = none (what the reference's test scripts compile), 1 = the reference's
 // conv+bias(+relu) fusion, 2 = additionally conv+bias+clip(0,6) -> activMode 3.
+// pool_opt: 0 = one wrapDNNMalloc per tensor, 1 = the reference's first-fit pool plan,
+// 2 = pool with the offline greedy-by-size plan.
 int occ_lower(void *h, int fuse, int dealloc_opt, int pool_opt, int64_t workspace_bytes) {
   Program &p = *static_cast<Program *>(h);
   p.bufs.clear();
@@ -621,6 +685,7 @@ int occ_lower(void *h, int fuse, int dealloc_opt, int pool_opt, int64_t workspac
   if (!p.error.empty()) return -1;
   place_deallocs(p, dealloc_opt != 0);
   p.pool = pool_opt != 0;
+  p.pool_mode = pool_opt == 2 ? 2 : 1;
   plan_pool(p);
   memset(p.counts, 0, sizeof(p.counts));
   for (const Instr &in : p.prog) p.counts[in.kind]++;
@@ -629,6 +694,7 @@ int occ_lower(void *h, int fuse, int dealloc_opt, int pool_opt, int64_t workspac
 
 int64_t occ_pool_bytes(void *h) { return static_cast<Program *>(h)->pool_bytes; }
 int64_t occ_sum_bytes(void *h) { return static_cast<Program *>(h)->sum_bytes; }
+int64_t occ_live_peak_bytes(void *h) { return static_cast<Program *>(h)->live_peak; }
 void occ_instr_counts(void *h, int64_t *out16) {
   memcpy(out16, static_cast<Program *>(h)->counts, sizeof(int64_t) * 16);
 }
@@ -644,6 +710,28 @@ int occ_plan(void *h, int64_t *offsets, int64_t *bytes, int cap) {
       }
       ++n;
     }
+  return n;
+}
+
+// Lifetime [malloc index, dealloc index] (program positions) of every buffer, in allocation
+// order like occ_plan; a buffer that is never freed lives to the end of the program.
+int occ_lifetimes(void *h, int64_t *from, int64_t *to, int cap) {
+  Program &p = *static_cast<Program *>(h);
+  std::vector<int> slot(p.bufs.size(), -1);
+  int n = 0;
+  for (size_t i = 0; i < p.prog.size(); ++i) {
+    const Instr &in = p.prog[i];
+    if (in.kind == I_MALLOC) {
+      slot[in.out] = n;
+      if (n < cap) {
+        from[n] = (int64_t)i;
+        to[n] = (int64_t)p.prog.size();
+      }
+      ++n;
+    } else if (in.kind == I_DEALLOC && slot[in.out] >= 0 && slot[in.out] < cap) {
+      to[slot[in.out]] = (int64_t)i;
+    }
+  }
   return n;
 }
 

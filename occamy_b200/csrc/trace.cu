@@ -196,7 +196,11 @@ Role trace_step(Entry &e, bool *deviated) {
     }
     ts.cands.resize(keep);
     if (keep) {
+      // recorded programs that share this prefix must agree on the call's role (two models
+      // with the same first layers may continue differently); otherwise it runs as it stands
       role = (Role)ts.programs[ts.cands[0]].roles[index];
+      for (size_t k = 1; k < keep; ++k)
+        if ((Role)ts.programs[ts.cands[k]].roles[index] != role) role = R_EAGER;
       ts.matched_so_far = true;
     } else {
       *deviated = ts.matched_so_far;

@@ -21,6 +21,7 @@ _lib = None
 INSTR_NAMES = ("malloc", "dealloc", "h2d_const", "h2d_input", "d2h_output", "conv",
                "conv_bias_act", "tensor_op", "active", "clip", "maxpool", "avgpool", "reduce",
                "flatten", "matmul", "softmax")
+POOL_NONE, POOL_FIRST_FIT, POOL_BY_SIZE = 0, 1, 2   # Program.lower(pool_opt=...)
 FUSE_NONE, FUSE_REFERENCE, FUSE_WITH_CLIP = 0, 1, 2
 
 
@@ -52,6 +53,10 @@ def lib():
         L.occ_lower.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64]
         L.occ_pool_bytes.restype = C.c_int64
         L.occ_pool_bytes.argtypes = [C.c_void_p]
+        L.occ_lifetimes.restype = C.c_int
+        L.occ_lifetimes.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int]
+        L.occ_live_peak_bytes.restype = C.c_int64
+        L.occ_live_peak_bytes.argtypes = [C.c_void_p]
         L.occ_sum_bytes.restype = C.c_int64
         L.occ_sum_bytes.argtypes = [C.c_void_p]
         L.occ_instr_counts.argtypes = [C.c_void_p, _i64p]
@@ -153,6 +158,11 @@ class Program:
         return int(lib().occ_pool_bytes(self.h))
 
     @property
+    def live_peak_bytes(self):
+        """Most bytes live at one point of the program: the lower bound of any pool plan."""
+        return int(lib().occ_live_peak_bytes(self.h))
+
+    @property
     def sum_bytes(self):
         return int(lib().occ_sum_bytes(self.h))
 
@@ -166,6 +176,13 @@ class Program:
         off, by = (C.c_int64 * n)(), (C.c_int64 * n)()
         lib().occ_plan(self.h, off, by, n)
         return [(int(off[i]), int(by[i])) for i in range(n)]
+
+    def lifetimes(self):
+        """(malloc position, dealloc position) of every buffer, in the order of plan()."""
+        n = lib().occ_lifetimes(self.h, None, None, 0)
+        a, b = (C.c_int64 * n)(), (C.c_int64 * n)()
+        lib().occ_lifetimes(self.h, a, b, n)
+        return [(int(a[i]), int(b[i])) for i in range(n)]
 
     # ---- execution ----
     def run(self, binding: Binding, x: np.ndarray):

@@ -243,3 +243,23 @@ def test_stem_conv_with_max_pool(shape, fuse):
     # conv + ReLU fused by the reference lowering round the same way in both runs
     if fuse == replay.FUSE_REFERENCE and act != "clip":
         assert np.array_equal(y0, y1)
+
+
+@pytest.mark.parametrize("name", ["resnet50", "mobilenet_v2"])
+def test_offline_pool_plan_runs_the_same(name):
+    """The runtime takes whatever offsets the caller planned: with the greedy-by-size plan
+    (smaller pool, different aliasing between tensors) the result is the same bits as with
+    the reference's first-fit plan, call by call and with cross-call fusion."""
+    rt.set_math_mode(rt.MATH_BF16)
+    g = getattr(graphs, name)(batch=2, seed=5, image=64)
+    x = graphs.make_input(g, 6)
+    b = replay.Binding()
+    outs = {}
+    for mode in (replay.POOL_FIRST_FIT, replay.POOL_BY_SIZE):
+        p = g.to_program()
+        p.lower(fuse=replay.FUSE_REFERENCE, pool_opt=mode)
+        outs[mode] = [p.run(b, x)[0] for _ in range(3)]
+        assert rt.last_error() == 0
+        assert np.array_equal(outs[mode][1], outs[mode][2])
+    assert np.array_equal(outs[replay.POOL_FIRST_FIT][0], outs[replay.POOL_BY_SIZE][0])
+    assert np.array_equal(outs[replay.POOL_FIRST_FIT][2], outs[replay.POOL_BY_SIZE][2])

@@ -136,3 +136,29 @@ def test_mobilenet_fusion_variants(native_libs):
     p.lower(fuse=replay.FUSE_WITH_CLIP)
     c = p.instr_counts()
     assert c["clip"] == 17               # only the depthwise ones keep a separate clip
+
+
+@pytest.mark.parametrize("name,batch", [("resnet50", 4), ("vgg16", 2), ("mobilenet_v2", 4)])
+def test_offline_plan_is_valid_and_not_larger(name, batch, native_libs):
+    """The greedy-by-size plan must keep simultaneously live buffers apart, stay at or above
+    the live-bytes lower bound, and not need more memory than the reference's first fit on the
+    benchmark graphs."""
+    g = getattr(graphs, name)(batch=batch, seed=0, image=64)
+    p1 = g.to_program()
+    p1.lower(fuse=replay.FUSE_REFERENCE, pool_opt=replay.POOL_FIRST_FIT)
+    p2 = g.to_program()
+    p2.lower(fuse=replay.FUSE_REFERENCE, pool_opt=replay.POOL_BY_SIZE)
+    assert p2.live_peak_bytes == p1.live_peak_bytes
+    assert p2.live_peak_bytes <= p2.pool_bytes <= p1.pool_bytes
+    # validity: replay the lifetimes against the planned offsets
+    life = p2.lifetimes()
+    plan = p2.plan()
+    assert len(life) == len(plan)
+    spans = [(off, off + by, a, b) for (off, by), (a, b) in zip(plan, life) if by > 0]
+    for i in range(len(spans)):
+        for j in range(i + 1, len(spans)):
+            o1, e1, a1, b1 = spans[i]
+            o2, e2, a2, b2 = spans[j]
+            if a1 <= b2 and a2 <= b1:          # live together
+                assert e1 <= o2 or e2 <= o1, (spans[i], spans[j])
+        assert spans[i][1] <= p2.pool_bytes
