@@ -300,10 +300,215 @@ __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float 
   }
 }
 
+// 3x3 depthwise convolution, stride ST (1 or 2), for images at least a CTA's column count wide.
+// A CTA owns G 8-channel groups (G * 16 bytes of every pixel) of a strip of `cols` output
+// columns of one image and walks down it in tiles of TH output rows.  The input tile with its
+// halo is staged in shared memory by 16-byte cp.async copies, two tiles deep, so that the
+// global-memory latency is covered by the copy engine and not by registers or occupancy; what
+// lies outside the image is stored as zeros.  A thread owns one channel group of one output
+// column: the nine filter taps (72 fp32 values as packed pairs) and the three input rows of the
+// current window stay in registers, an output row costs ST * 3 shared-memory loads and 36 packed
+// fp32 FMAs, and the 16-byte stores of a warp are contiguous.
+__device__ __forceinline__ uint64_t dw_pair(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t dw_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+struct DwRow {
+  uint64_t v[3][4];   // three columns x 8 channels as fp32 pairs
+};
+
+template <int ST>
+__global__ void __launch_bounds__(256, 1) depthwise3x3_tile_kernel(
+    const bf16x8 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+    bf16x8 *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c) {
+  extern __shared__ uint4 dw_smem[];
+  const int C8 = g.C / 8;
+  int b = blockIdx.x;
+  const int cb = b % tiles_c;
+  b /= tiles_c;
+  const int qt = b % tiles_q;
+  const int64_t n = b / tiles_q;
+  const int q0 = qt * cols;
+  const int IW = (cols - 1) * ST + 3, IH = (TH - 1) * ST + 3;
+  const int stage_vecs = IH * IW * G;
+  const int tid = threadIdx.x;
+  const int gl = tid % G, col = tid / G;
+  const bool active = col < cols;
+  const int c8 = cb * G + gl;
+  const bf16x8 *xin = x + n * g.H * g.W * C8 + cb * G;
+  const int w_in0 = q0 * ST - g.pad_w;
+
+  // stage the input rows of row tile t into buffer t & 1
+  auto stage = [&](int t) {
+    uint4 *dst = dw_smem + (t & 1) * stage_vecs;
+    const int h_in0 = t * TH * ST - g.pad_h;
+    for (int i = tid; i < stage_vecs; i += 256) {
+      const int gg = i % G;
+      const int iw = (i / G) % IW;
+      const int ih = i / (G * IW);
+      const int h = h_in0 + ih, ww = w_in0 + iw;
+      if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) {
+        const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + i);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa),
+                     "l"(xin + ((int64_t)h * g.W + ww) * C8 + gg)
+                     : "memory");
+      } else {
+        dst[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  uint64_t wv[9][4];
+  uint64_t bv[4] = {0, 0, 0, 0};
+  if (active) {
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      const float4 *wp = (const float4 *)(w + (int64_t)t * g.C + c8 * 8);
+      const float4 a = wp[0], bb = wp[1];
+      wv[t][0] = dw_pair(a.x, a.y);
+      wv[t][1] = dw_pair(a.z, a.w);
+      wv[t][2] = dw_pair(bb.x, bb.y);
+      wv[t][3] = dw_pair(bb.z, bb.w);
+    }
+    if (bias) {
+      const float4 *bp = (const float4 *)(bias + c8 * 8);
+      const float4 a = bp[0], bb = bp[1];
+      bv[0] = dw_pair(a.x, a.y);
+      bv[1] = dw_pair(a.z, a.w);
+      bv[2] = dw_pair(bb.x, bb.y);
+      bv[3] = dw_pair(bb.z, bb.w);
+    }
+  }
+  const int q = q0 + col;
+  const int ntiles = (g.P + TH - 1) / TH;
+  stage(0);
+  for (int t = 0; t < ntiles; ++t) {
+    if (t + 1 < ntiles) {
+      stage(t + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (active && q < g.Q) {
+      const uint4 *src = dw_smem + (t & 1) * stage_vecs + (col * ST) * G + gl;
+      auto load_row = [&](int ih, DwRow &r) {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+          const uint4 v = src[(ih * IW + k) * G];
+          const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)   // a bf16 is the top half of the fp32 of the same value
+            r.v[k][j] = dw_pair(__uint_as_float(u[j] << 16), __uint_as_float(u[j] & 0xffff0000u));
+        }
+      };
+      auto emit = [&](int p, const DwRow &a, const DwRow &bq, const DwRow &cq) {
+        if (p >= g.P) return;
+        uint64_t acc[4] = {bv[0], bv[1], bv[2], bv[3]};
+#pragma unroll
+        for (int k = 0; k < 3; ++k)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[j] = dw_fma2(a.v[k][j], wv[k][j], acc[j]);
+            acc[j] = dw_fma2(bq.v[k][j], wv[3 + k][j], acc[j]);
+            acc[j] = dw_fma2(cq.v[k][j], wv[6 + k][j], acc[j]);
+          }
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          asm("mov.b64 {%0, %1}, %2;" : "=f"(f[2 * j]), "=f"(f[2 * j + 1]) : "l"(acc[j]));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = act_apply_b(f[k], g.act, g.lo, g.hi);
+        y[((n * g.P + p) * g.Q + q) * C8 + c8] = pack8(f);
+      };
+      DwRow r0, r1, r2;
+      const int pbase = t * TH;
+      if (ST == 1) {
+        load_row(0, r0);
+        load_row(1, r1);
+        for (int pl = 0; pl < TH; pl += 3) {
+          load_row(pl + 2, r2);
+          emit(pbase + pl, r0, r1, r2);
+          if (pl + 1 < TH) {
+            load_row(pl + 3, r0);
+            emit(pbase + pl + 1, r1, r2, r0);
+          }
+          if (pl + 2 < TH) {
+            load_row(pl + 4, r1);
+            emit(pbase + pl + 2, r2, r0, r1);
+          }
+        }
+      } else {
+        load_row(0, r0);
+        for (int pl = 0; pl < TH; pl += 3) {
+          load_row(2 * pl + 1, r1);
+          load_row(2 * pl + 2, r2);
+          emit(pbase + pl, r0, r1, r2);
+          if (pl + 1 < TH) {
+            load_row(2 * pl + 3, r0);
+            load_row(2 * pl + 4, r1);
+            emit(pbase + pl + 1, r2, r0, r1);
+          }
+          if (pl + 2 < TH) {
+            load_row(2 * pl + 5, r2);
+            load_row(2 * pl + 6, r0);
+            emit(pbase + pl + 2, r1, r2, r0);
+          }
+        }
+      }
+    }
+    __syncthreads();   // the buffer is staged again two tiles on
+  }
+}
+
 void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias, bf16 *y,
                            const ConvGeom &g, cudaStream_t s) {
   const int64_t total = (int64_t)g.N * g.P * g.Q * (g.C / 8);
   if (total == 0) return;
+  const int C8 = g.C / 8;
+  int G = 8;
+  while (G > 1 && C8 % G) --G;                 // channel groups per CTA: a divisor of C / 8
+  const int cols_max = 256 / G;
+  if (g.R == 3 && g.S == 3 && g.stride_h == g.stride_w && (g.stride_h == 1 || g.stride_h == 2) &&
+      g.Q * 8 >= cols_max * 7 && G >= 2) {
+    // image rows at least (nearly) as wide as a CTA's column strip: the tiled kernel
+    const int ST = g.stride_h;
+    const int tiles_q = (g.Q + cols_max - 1) / cols_max;
+    const int cols = (g.Q + tiles_q - 1) / tiles_q;       // even split of the row
+    int TH = 12;
+    auto stage_bytes = [&](int th) { return (size_t)((th - 1) * ST + 3) * ((cols - 1) * ST + 3) * G * 16; };
+    while (TH > 3 && 2 * stage_bytes(TH) > 200 * 1024) TH -= 3;
+    const size_t smem = 2 * stage_bytes(TH);
+    const int tiles_c = C8 / G;
+    const unsigned grid = (unsigned)((int64_t)g.N * tiles_q * tiles_c);
+    static bool attr_set[2] = {false, false};
+    if (ST == 1) {
+      if (!attr_set[0]) {
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024);
+        attr_set[0] = true;
+      }
+      depthwise3x3_tile_kernel<1><<<grid, 256, smem, s>>>((const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g,
+                                                         G, cols, TH, tiles_q, tiles_c);
+    } else {
+      if (!attr_set[1]) {
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             200 * 1024);
+        attr_set[1] = true;
+      }
+      depthwise3x3_tile_kernel<2><<<grid, 256, smem, s>>>((const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g,
+                                                         G, cols, TH, tiles_q, tiles_c);
+    }
+    count(CNT_LAUNCHES);
+    return;
+  }
   depthwise_bf16_kernel<<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, w_rsc, bias,
                                                               (bf16x8 *)y, g, total);
   count(CNT_LAUNCHES);

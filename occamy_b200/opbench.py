@@ -1,0 +1,169 @@
+"""Timing of the memory-bound operator kernels through the C ABI.
+
+    python -m occamy_b200.opbench [--batch 256] [--reps 20] [--out table.txt]
+
+Every row calls one ABI symbol (pooling, element-wise add / ReLU / Clip, depthwise convolution,
+global average pool, softmax) on device-resident tensors of the sizes ResNet-50 and MobileNetV2
+produce at the given batch, in bf16 mode with the input already in the runtime's bf16 NHWC
+format (it is the output of a convolution call, as in a model).  Times are CUDA-event medians on
+the runtime's stream; between repetitions the tensors (hundreds of MB) do not fit the L2.
+"achieved" is algorithmic bytes / time, "frac" its share of the measured copy bandwidth in
+MEASURED_PEAKS.json (fallback 6650 GB/s).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+
+import numpy as np
+
+from . import runtime as rt
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _hbm_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class _T:
+    def __init__(self, shape, data=None):
+        self.shape = tuple(int(s) for s in shape)
+        n = int(np.prod(self.shape))
+        if data is not None:
+            self.buf = rt.DeviceBuffer.from_numpy(np.ascontiguousarray(data, np.float32))
+        else:
+            self.buf = rt.DeviceBuffer(max(n, 1) * 4)
+        self.ptr = self.buf.ptr
+
+
+def _bf16_tensor(h, rng, N, Cc, H, W):
+    """A [N,Cc,H,W] tensor in the runtime's bf16 NHWC format: the output of a 1x1 convolution."""
+    cin = 16
+    x = _T((N, cin, H, W), rng.standard_normal((N, cin, H, W), dtype=np.float32))
+    w = _T((Cc, cin, 1, 1), rng.standard_normal((Cc, cin, 1, 1), dtype=np.float32) * 0.25)
+    y = _T((N, Cc, H, W))
+    rt.lib().DNNConvFunc(h, x.ptr, rt.dims(x.shape), w.ptr, rt.dims(w.shape), None, 0, 1, 1,
+                         rt.dims((0, 0)), rt.dims((1, 1)), y.ptr)
+    rt.lib().occamy_synchronize()
+    x.buf.free()
+    return y
+
+
+def main():
+    import torch
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    torch.cuda.init()
+    rt.set_math_mode(rt.MATH_BF16)
+    L = rt.lib()
+    h = C.c_void_p()
+    L.cudnnCreate(C.byref(h))
+    stream = torch.cuda.ExternalStream(L.occamy_stream())
+    rng = np.random.Generator(np.random.PCG64(0))
+    peak, peak_src = _hbm_peak()
+    B = args.batch
+    rows = []
+
+    def timed(name, nbytes, fn):
+        for _ in range(3):
+            fn()
+        ms = []
+        for _ in range(args.reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            fn()
+            e1.record(stream)
+            e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        t = statistics.median(ms)
+        gbs = nbytes / t / 1e6
+        rows.append((name, nbytes / 1e6, t, gbs, gbs / peak))
+        err = rt.last_error()
+        if err:
+            raise SystemExit(f"{name}: runtime error {err}")
+
+    def pool(x, k, pad, st, avg):
+        N, Cc, H, W = x.shape
+        P = (H + 2 * pad - k) // st + 1
+        y = _T((N, Cc, P, P))
+        fn = L.DNNAveragePoolFunc if avg else L.DNNMaxPoolFunc
+        call = lambda: fn(h, x.ptr, rt.dims(x.shape), y.ptr, rt.dims(y.shape), rt.dims((k, k)),
+                          rt.dims((pad, pad, pad, pad)), rt.dims((st, st)))
+        return call, 2 * (int(np.prod(x.shape)) + int(np.prod(y.shape))), y
+
+    def depthwise(x, st):
+        N, Cc, H, W = x.shape
+        P = (H + 2 - 3) // st + 1
+        w = _T((Cc, 1, 3, 3), rng.standard_normal((Cc, 1, 3, 3), dtype=np.float32) * 0.3)
+        y = _T((N, Cc, P, P))
+        call = lambda: L.DNNConvFunc(h, x.ptr, rt.dims(x.shape), w.ptr, rt.dims(w.shape), None, 0, 1, Cc,
+                                     rt.dims((1, 1)), rt.dims((st, st)), y.ptr)
+        return call, 2 * (int(np.prod(x.shape)) + int(np.prod(y.shape))) + 36 * Cc, (w, y)
+
+    # ---- ResNet-50 sized tensors ----
+    x = _bf16_tensor(h, rng, B, 64, 112, 112)
+    call, nb, keep = pool(x, 3, 1, 2, False)
+    timed(f"max pool 3x3/2 [{B},64,112,112]", nb, call)
+    del keep
+    x.buf.free()
+
+    a = _bf16_tensor(h, rng, B, 256, 56, 56)
+    b = _bf16_tensor(h, rng, B, 256, 56, 56)
+    out = _T(a.shape)
+    n = int(np.prod(a.shape))
+    timed(f"add [{B},256,56,56]", 6 * n,
+          lambda: L.DNNTensorOpFunc(h, 0, a.ptr, rt.dims(a.shape), 4, b.ptr, rt.dims(b.shape), 4, out.ptr,
+                                    rt.dims(a.shape), 4, 1.0))
+    timed(f"ReLU [{B},256,56,56]", 4 * n,
+          lambda: L.DNNActiveFunc(h, a.ptr, rt.dims(a.shape), 1, out.ptr))
+    timed(f"Clip(0,6) [{B},256,56,56]", 4 * n,
+          lambda: L.CUDAClipFunc(a.ptr, out.ptr, rt.dims(a.shape), 0.0, 6.0, 4))
+    call, nb, keep = pool(a, 2, 0, 2, True)
+    timed(f"average pool 2x2/2 [{B},256,56,56]", nb, call)
+    del keep
+    for t in (a, b, out):
+        t.buf.free()
+
+    g = _bf16_tensor(h, rng, B, 2048, 7, 7)
+    gy = _T((B, 2048, 1, 1))
+    timed(f"global average pool [{B},2048,7,7]", 2 * int(np.prod(g.shape)) + 4 * B * 2048,
+          lambda: L.DNNReduceFunc(h, 4, g.ptr, rt.dims(g.shape), gy.ptr, rt.dims(gy.shape), 5))
+    g.buf.free()
+
+    # ---- MobileNetV2 sized depthwise convolutions ----
+    for (Cc, H, st) in ((32, 112, 1), (96, 112, 2), (144, 56, 1), (192, 28, 2), (384, 14, 1), (960, 7, 1)):
+        x = _bf16_tensor(h, rng, B, Cc, H, H)
+        call, nb, keep = depthwise(x, st)
+        timed(f"depthwise 3x3/{st} [{B},{Cc},{H},{H}]", nb, call)
+        del keep
+        x.buf.free()
+
+    s = _T((B, 1000), rng.standard_normal((B, 1000), dtype=np.float32))
+    sy = _T((B, 1000))
+    timed(f"softmax [{B},1000] fp32", 8 * B * 1000,
+          lambda: L.CUDASoftmaxFunc(s.ptr, rt.dims(s.shape), sy.ptr, rt.dims(s.shape), 1, 2))
+
+    lines = [f"# memory-bound operator kernels through the C ABI, batch {B}, bf16 mode; "
+             f"peak = {peak:.0f} GB/s ({peak_src} copy bandwidth)",
+             "# op | MB (algorithmic) | ms | GB/s | frac of peak"]
+    for r in rows:
+        lines.append(f"{r[0]:44s} {r[1]:9.1f} {r[2]:8.4f} {r[3]:8.1f} {r[4]:6.3f}")
+    text = "\n".join(lines)
+    print(text)
+    if args.out:
+        open(args.out, "w").write(text + "\n")
+
+
+if __name__ == "__main__":
+    main()
