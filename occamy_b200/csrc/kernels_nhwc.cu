@@ -256,9 +256,12 @@ void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t
 // Depthwise convolution on NHWC: thread per (n, p, q, 8 channels); the R*S taps of a
 // channel group are 2 float4 loads each from the [R*S][C] fp32 filter (L1-resident).
 // ---------------------------------------------------------------------------
+// CLAMP: the activation is identity / ReLU / Clip, applied as a clamp to [lo, hi] (the general
+// switch drags the transcendental activations' code into the loop).
+template <bool CLAMP>
 __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float *__restrict__ w,
                                       const float *__restrict__ bias, bf16x8 *__restrict__ y,
-                                      ConvGeom g, int64_t total) {
+                                      ConvGeom g, int64_t total, float lo, float hi) {
   const int C8 = g.C / 8;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -295,7 +298,8 @@ __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float 
       }
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) acc[k] = act_apply_b(acc[k], g.act, g.lo, g.hi);
+    for (int k = 0; k < 8; ++k)
+      acc[k] = CLAMP ? fminf(fmaxf(acc[k], lo), hi) : act_apply_b(acc[k], g.act, g.lo, g.hi);
     y[i] = pack8(acc);
   }
 }
@@ -320,13 +324,15 @@ __device__ __forceinline__ uint64_t dw_fma2(uint64_t a, uint64_t b, uint64_t c) 
   return r;
 }
 struct DwRow {
-  uint64_t v[3][4];   // three columns x 8 channels as fp32 pairs
+  uint32_t v[3][4];   // three columns x 8 channels, bf16 pairs as loaded (unpacked at use:
+                      // fp32 rows would not leave registers for two CTAs per SM)
 };
 
 template <int ST>
-__global__ void __launch_bounds__(256, 1) depthwise3x3_tile_kernel(
+__global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
     const bf16x8 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
-    bf16x8 *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c) {
+    bf16x8 *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c,
+    float act_lo, float act_hi) {
   extern __shared__ uint4 dw_smem[];
   const int C8 = g.C / 8;
   int b = blockIdx.x;
@@ -344,46 +350,57 @@ __global__ void __launch_bounds__(256, 1) depthwise3x3_tile_kernel(
   const bf16x8 *xin = x + n * g.H * g.W * C8 + cb * G;
   const int w_in0 = q0 * ST - g.pad_w;
 
+  // Staging: a thread always copies the same 16-byte pieces of a tile row (piece j = tid + 256 k
+  // of the IW * G pieces), so their column / channel-group arithmetic is done once.
+  constexpr int KMAX = 4;                       // IW * G <= 1024 pieces per tile row
+  const int row_vecs = IW * G;
+  int64_t src_off[KMAX];                        // offset of the piece inside an input row, or -1
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) {
+    const int j = tid + 256 * k;
+    const int gg = j % G, ww = w_in0 + j / G;
+    src_off[k] = (j < row_vecs && ww >= 0 && ww < g.W) ? (int64_t)ww * C8 + gg : -1;
+  }
   // stage the input rows of row tile t into buffer t & 1
   auto stage = [&](int t) {
     uint4 *dst = dw_smem + (t & 1) * stage_vecs;
     const int h_in0 = t * TH * ST - g.pad_h;
-    for (int i = tid; i < stage_vecs; i += 256) {
-      const int gg = i % G;
-      const int iw = (i / G) % IW;
-      const int ih = i / (G * IW);
-      const int h = h_in0 + ih, ww = w_in0 + iw;
-      if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) {
-        const uint32_t sa = (uint32_t)__cvta_generic_to_shared(dst + i);
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa),
-                     "l"(xin + ((int64_t)h * g.W + ww) * C8 + gg)
-                     : "memory");
-      } else {
-        dst[i] = make_uint4(0, 0, 0, 0);
+    for (int ih = 0; ih < IH; ++ih) {
+      const int h = h_in0 + ih;
+      const bool hv = h >= 0 && h < g.H;
+      const bf16x8 *rowp = xin + (int64_t)h * g.W * C8;
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k) {
+        const int j = tid + 256 * k;
+        if (j >= row_vecs) break;
+        uint4 *d = dst + ih * row_vecs + j;
+        if (hv && src_off[k] >= 0) {
+          const uint32_t sa = (uint32_t)__cvta_generic_to_shared(d);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(rowp + src_off[k])
+                       : "memory");
+        } else {
+          *d = make_uint4(0, 0, 0, 0);
+        }
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  uint64_t wv[9][4];
-  uint64_t bv[4] = {0, 0, 0, 0};
+  float wv[9][8];
+  float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (active) {
 #pragma unroll
     for (int t = 0; t < 9; ++t) {
       const float4 *wp = (const float4 *)(w + (int64_t)t * g.C + c8 * 8);
       const float4 a = wp[0], bb = wp[1];
-      wv[t][0] = dw_pair(a.x, a.y);
-      wv[t][1] = dw_pair(a.z, a.w);
-      wv[t][2] = dw_pair(bb.x, bb.y);
-      wv[t][3] = dw_pair(bb.z, bb.w);
+      wv[t][0] = a.x; wv[t][1] = a.y; wv[t][2] = a.z; wv[t][3] = a.w;
+      wv[t][4] = bb.x; wv[t][5] = bb.y; wv[t][6] = bb.z; wv[t][7] = bb.w;
     }
     if (bias) {
       const float4 *bp = (const float4 *)(bias + c8 * 8);
       const float4 a = bp[0], bb = bp[1];
-      bv[0] = dw_pair(a.x, a.y);
-      bv[1] = dw_pair(a.z, a.w);
-      bv[2] = dw_pair(bb.x, bb.y);
-      bv[3] = dw_pair(bb.z, bb.w);
+      bv[0] = a.x; bv[1] = a.y; bv[2] = a.z; bv[3] = a.w;
+      bv[4] = bb.x; bv[5] = bb.y; bv[6] = bb.z; bv[7] = bb.w;
     }
   }
   const int q = q0 + col;
@@ -405,27 +422,29 @@ __global__ void __launch_bounds__(256, 1) depthwise3x3_tile_kernel(
           const uint4 v = src[(ih * IW + k) * G];
           const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j)   // a bf16 is the top half of the fp32 of the same value
-            r.v[k][j] = dw_pair(__uint_as_float(u[j] << 16), __uint_as_float(u[j] & 0xffff0000u));
+          for (int j = 0; j < 4; ++j) r.v[k][j] = u[j];
         }
       };
       auto emit = [&](int p, const DwRow &a, const DwRow &bq, const DwRow &cq) {
         if (p >= g.P) return;
-        uint64_t acc[4] = {bv[0], bv[1], bv[2], bv[3]};
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = bv[j];
 #pragma unroll
         for (int k = 0; k < 3; ++k)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[j] = dw_fma2(a.v[k][j], wv[k][j], acc[j]);
-            acc[j] = dw_fma2(bq.v[k][j], wv[3 + k][j], acc[j]);
-            acc[j] = dw_fma2(cq.v[k][j], wv[6 + k][j], acc[j]);
+          for (int j = 0; j < 4; ++j) {   // a bf16 is the top half of the fp32 of the same value
+            f[2 * j] = fmaf(__uint_as_float(a.v[k][j] << 16), wv[k][2 * j], f[2 * j]);
+            f[2 * j + 1] = fmaf(__uint_as_float(a.v[k][j] & 0xffff0000u), wv[k][2 * j + 1], f[2 * j + 1]);
+            f[2 * j] = fmaf(__uint_as_float(bq.v[k][j] << 16), wv[3 + k][2 * j], f[2 * j]);
+            f[2 * j + 1] = fmaf(__uint_as_float(bq.v[k][j] & 0xffff0000u), wv[3 + k][2 * j + 1], f[2 * j + 1]);
+            f[2 * j] = fmaf(__uint_as_float(cq.v[k][j] << 16), wv[6 + k][2 * j], f[2 * j]);
+            f[2 * j + 1] = fmaf(__uint_as_float(cq.v[k][j] & 0xffff0000u), wv[6 + k][2 * j + 1], f[2 * j + 1]);
           }
-        float f[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          asm("mov.b64 {%0, %1}, %2;" : "=f"(f[2 * j]), "=f"(f[2 * j + 1]) : "l"(acc[j]));
-#pragma unroll
-        for (int k = 0; k < 8; ++k) f[k] = act_apply_b(f[k], g.act, g.lo, g.hi);
+        // the activations this kernel takes are all a clamp (a switch over every activation,
+        // inlined into each unrolled copy of this body, would not fit the instruction cache)
+        for (int k = 0; k < 8; ++k) f[k] = fminf(fmaxf(f[k], act_lo), act_hi);
         y[((n * g.P + p) * g.Q + q) * C8 + c8] = pack8(f);
       };
       DwRow r0, r1, r2;
@@ -477,14 +496,18 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
   while (G > 1 && C8 % G) --G;                 // channel groups per CTA: a divisor of C / 8
   const int cols_max = 256 / G;
   if (g.R == 3 && g.S == 3 && g.stride_h == g.stride_w && (g.stride_h == 1 || g.stride_h == 2) &&
-      g.Q * 8 >= cols_max * 7 && G >= 2) {
+      (g.act == ACT_IDENTITY || g.act == ACT_RELU || g.act == ACT_CLIP) &&
+      g.Q * 8 >= cols_max * 7 && G >= 2 &&
+      ((cols_max - 1) * g.stride_h + 3) * G <= 1024) {
     // image rows at least (nearly) as wide as a CTA's column strip: the tiled kernel
     const int ST = g.stride_h;
+    const float act_lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
+    const float act_hi = g.act == ACT_CLIP ? g.hi : INFINITY;
     const int tiles_q = (g.Q + cols_max - 1) / cols_max;
     const int cols = (g.Q + tiles_q - 1) / tiles_q;       // even split of the row
     int TH = 12;
     auto stage_bytes = [&](int th) { return (size_t)((th - 1) * ST + 3) * ((cols - 1) * ST + 3) * G * 16; };
-    while (TH > 3 && 2 * stage_bytes(TH) > 200 * 1024) TH -= 3;
+    while (TH > 3 && 2 * stage_bytes(TH) > 100 * 1024) TH -= 3;   // two CTAs per SM
     const size_t smem = 2 * stage_bytes(TH);
     const int tiles_c = C8 / G;
     const unsigned grid = (unsigned)((int64_t)g.N * tiles_q * tiles_c);
@@ -496,7 +519,7 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
         attr_set[0] = true;
       }
       depthwise3x3_tile_kernel<1><<<grid, 256, smem, s>>>((const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g,
-                                                         G, cols, TH, tiles_q, tiles_c);
+                                                         G, cols, TH, tiles_q, tiles_c, act_lo, act_hi);
     } else {
       if (!attr_set[1]) {
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -504,13 +527,20 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
         attr_set[1] = true;
       }
       depthwise3x3_tile_kernel<2><<<grid, 256, smem, s>>>((const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g,
-                                                         G, cols, TH, tiles_q, tiles_c);
+                                                         G, cols, TH, tiles_q, tiles_c, act_lo, act_hi);
     }
     count(CNT_LAUNCHES);
     return;
   }
-  depthwise_bf16_kernel<<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, w_rsc, bias,
-                                                              (bf16x8 *)y, g, total);
+  if (g.act == ACT_IDENTITY || g.act == ACT_RELU || g.act == ACT_CLIP) {
+    const float lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
+    const float hi = g.act == ACT_CLIP ? g.hi : INFINITY;
+    depthwise_bf16_kernel<true><<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, w_rsc, bias,
+                                                                      (bf16x8 *)y, g, total, lo, hi);
+  } else {
+    depthwise_bf16_kernel<false><<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, w_rsc, bias,
+                                                                       (bf16x8 *)y, g, total, 0.f, 0.f);
+  }
   count(CNT_LAUNCHES);
 }
 
