@@ -24,8 +24,20 @@ static inline int grid_for(int64_t n, int threads) {
   return (int)b;
 }
 
+// Eight bf16 values moved as one 16-byte word: the copy operations go through the uint4 member,
+// so a load or store of a bf16x8 is a single 128-bit access (a member-wise copy of the four pairs
+// compiles to four 32-bit accesses, which costs four times the L1 wavefronts).
 struct alignas(16) bf16x8 {
-  __nv_bfloat162 v[4];
+  union {
+    uint4 u;
+    __nv_bfloat162 v[4];
+  };
+  __device__ __forceinline__ bf16x8() {}
+  __device__ __forceinline__ bf16x8(const bf16x8 &o) : u(o.u) {}
+  __device__ __forceinline__ bf16x8 &operator=(const bf16x8 &o) {
+    u = o.u;
+    return *this;
+  }
 };
 
 __device__ __forceinline__ void unpack8(const bf16x8 &p, float *f) {
@@ -196,10 +208,91 @@ __global__ void __launch_bounds__(256) pool_bf16_kernel(const bf16x8 *__restrict
   }
 }
 
+// Pooling with a compile-time square window K and stride S: one thread per (n, p, q, 8 channels).
+// All K*K 16-byte loads of a thread are issued before the first is used: their addresses are
+// clamped into the image instead of being skipped (a clamped element lies inside the window, so the
+// maximum is unchanged; the average masks it to zero), which leaves no branch between the loads.
+// Neighbouring windows overlap in the L1.  The grid is (chunks of one image's outputs) x images, so
+// a thread needs two short divisions only.
+template <int K, int S, bool AVG>
+__global__ void __launch_bounds__(256) pool_win_bf16_kernel(const bf16x8 *__restrict__ x,
+                                                            bf16x8 *__restrict__ y, int C8, int H,
+                                                            int W, int Q, int pad_h, int pad_w,
+                                                            unsigned per_image, unsigned chunks) {
+  const unsigned n = blockIdx.x / chunks;
+  const unsigned j = (blockIdx.x - n * chunks) * 256u + threadIdx.x;
+  if (j >= per_image) return;
+  const unsigned pq = j / (unsigned)C8;
+  const int c8 = (int)(j - pq * (unsigned)C8);
+  const int p = (int)(pq / (unsigned)Q), q = (int)(pq - (unsigned)p * (unsigned)Q);
+  const bf16x8 *xin = x + (int64_t)n * H * W * C8 + c8;
+  const int h0 = p * S - pad_h, w0 = q * S - pad_w;
+  bf16x8 v[K][K];
+#pragma unroll
+  for (int r = 0; r < K; ++r) {
+    const int h = min(max(h0 + r, 0), H - 1);
+#pragma unroll
+    for (int c = 0; c < K; ++c) {
+      const int w = min(max(w0 + c, 0), W - 1);
+      v[r][c] = xin[((int64_t)h * W + w) * C8];
+    }
+  }
+  bf16x8 out;
+  if (AVG) {
+    float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < K; ++r)
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        const bool in = (unsigned)(h0 + r) < (unsigned)H && (unsigned)(w0 + c) < (unsigned)W;
+        float f[8];
+        unpack8(v[r][c], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sum[k] += in ? f[k] : 0.0f;
+      }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum[k] *= 1.0f / (float)(K * K);
+    out = pack8(sum);
+  } else {
+    out = v[0][0];
+#pragma unroll
+    for (int r = 0; r < K; ++r)
+#pragma unroll
+      for (int c = 0; c < K; ++c)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out.v[k] = __hmax2_nan(out.v[k], v[r][c].v[k]);
+  }
+  y[(int64_t)n * per_image + j] = out;
+}
+
+template <int K, int S>
+static void launch_pool_win(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P, int Q,
+                            int pad_h, int pad_w, bool avg, cudaStream_t s) {
+  const unsigned per_image = (unsigned)((int64_t)P * Q * (C / 8));
+  const unsigned chunks = (per_image + 255u) / 256u;
+  const unsigned grid = chunks * (unsigned)N;
+  if (avg)
+    pool_win_bf16_kernel<K, S, true><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, Q,
+                                                         pad_h, pad_w, per_image, chunks);
+  else
+    pool_win_bf16_kernel<K, S, false><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, Q,
+                                                          pad_h, pad_w, per_image, chunks);
+  count(CNT_LAUNCHES);
+}
+
 void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P, int Q, int kh,
                       int kw, int pad_h, int pad_w, int sh, int sw, bool avg, cudaStream_t s) {
   const int64_t total = (int64_t)N * P * Q * (C / 8);
   if (total == 0) return;
+  // every window lies at least partly inside the image and the per-image index fits 32 bits
+  if (kh == kw && sh == sw && pad_h < kh && pad_w < kw && (P - 1) * sh - pad_h < H &&
+      (Q - 1) * sw - pad_w < W && (int64_t)P * Q * (C / 8) < (1ll << 31) - 256 &&
+      ((int64_t)P * Q * (C / 8) + 255) / 256 * N < (1ll << 31)) {
+    if (kh == 3 && sh == 2) return launch_pool_win<3, 2>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
+    if (kh == 2 && sh == 2) return launch_pool_win<2, 2>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
+    if (kh == 3 && sh == 1) return launch_pool_win<3, 1>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
+    if (kh == 2 && sh == 1) return launch_pool_win<2, 1>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
+  }
   const int grid = grid_for(total, 256);
   if (avg)
     pool_bf16_kernel<true><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, P, Q,

@@ -1,6 +1,6 @@
 """Timing of the memory-bound operator kernels through the C ABI.
 
-    python -m occamy_b200.opbench [--batch 256] [--reps 20] [--out table.txt]
+    python -m occamy_b200.opbench [--batch 256] [--reps 20] [--only pool] [--out table.txt]
 
 Every row calls one ABI symbol (pooling, element-wise add / ReLU / Clip, depthwise convolution,
 global average pool, softmax) on device-resident tensors of the sizes ResNet-50 and MobileNetV2
@@ -63,6 +63,7 @@ def main():
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--out", default="")
+    ap.add_argument("--only", default="", help="run only the rows whose name contains this text")
     args = ap.parse_args()
     torch.cuda.init()
     rt.set_math_mode(rt.MATH_BF16)
@@ -76,6 +77,8 @@ def main():
     rows = []
 
     def timed(name, nbytes, fn):
+        if args.only and args.only not in name:
+            return
         for _ in range(3):
             fn()
         ms = []
