@@ -397,18 +397,19 @@ __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float 
   }
 }
 
-// 3x3 depthwise convolution, stride ST (1 or 2), for images at least a CTA's column count wide.
-// A CTA owns G 8-channel groups (G * 16 bytes of every pixel) of a strip of `cols` output
-// columns of one image and walks down it in tiles of TH output rows.  The input tile with its
-// halo is staged in shared memory by 16-byte cp.async copies, two tiles deep, so that the
-// global-memory latency is covered by the copy engine and not by registers or occupancy; what
-// lies outside the image is stored as zeros.  A thread owns one channel group of one output
-// column: the nine filter taps (72 fp32 values as packed pairs) and the three input rows of the
-// current window stay in registers, an output row costs ST * 3 shared-memory loads and 36 packed
-// fp32 FMAs, and the 16-byte stores of a warp are contiguous.
-__device__ __forceinline__ uint64_t dw_pair(float a, float b) {
+// 3x3 depthwise convolution, stride ST (1 or 2), tiled.
+// A CTA owns G 8-channel groups (G * 16 bytes of every pixel) of a strip of `cols` output columns
+// and works through a run of row tiles (TH output rows each) that continues from one image into
+// the next, so the grid is cut into equal runs whatever the image size.  The input tile with its
+// halo is staged in shared memory by 16-byte cp.async copies, two tiles deep; what lies outside
+// the image is stored as zeros.  A thread owns FOUR channels of one output column: its nine taps
+// (18 packed fp32 pairs) and the three input rows of the current window, already converted to
+// fp32 pairs, stay in registers, so an input value is converted once and an output row costs
+// ST * 3 eight-byte shared-memory loads and 18 packed FMAs (fma.rn.f32x2).  The kernel is bound by
+// instruction issue as much as by memory, which is why the work per output is kept this small.
+__device__ __forceinline__ uint64_t dw_pair(uint32_t lo_bits, uint32_t hi_bits) {
   uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo_bits), "r"(hi_bits));
   return r;
 }
 __device__ __forceinline__ uint64_t dw_fma2(uint64_t a, uint64_t b, uint64_t c) {
@@ -416,52 +417,64 @@ __device__ __forceinline__ uint64_t dw_fma2(uint64_t a, uint64_t b, uint64_t c) 
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+// two bf16 values in one word -> the fp32 pair (a bf16 is the top half of the fp32 of that value)
+__device__ __forceinline__ uint64_t dw_unpack(uint32_t v) { return dw_pair(v << 16, v & 0xffff0000u); }
+// fp32 pair -> clamp -> two bf16 in one word
+__device__ __forceinline__ uint32_t dw_finish(uint64_t acc, float lo, float hi) {
+  float a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(acc));
+  a = fminf(fmaxf(a, lo), hi);
+  b = fminf(fmaxf(b, lo), hi);
+  const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&r);
+}
 struct DwRow {
-  uint32_t v[3][4];   // three columns x 8 channels, bf16 pairs as loaded (unpacked at use:
-                      // fp32 rows would not leave registers for two CTAs per SM)
+  uint64_t v[3][2];   // three columns x four channels as fp32 pairs
 };
 
 template <int ST>
 __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
-    const bf16x8 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
-    bf16x8 *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c,
-    float act_lo, float act_hi) {
+    const uint4 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
+    uint2 *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c, int ntiles,
+    int run_len, int run_total, float act_lo, float act_hi) {
   extern __shared__ uint4 dw_smem[];
   const int C8 = g.C / 8;
   int b = blockIdx.x;
   const int cb = b % tiles_c;
   b /= tiles_c;
   const int qt = b % tiles_q;
-  const int64_t n = b / tiles_q;
+  const int run = b / tiles_q;
+  const int s0 = run * run_len, s1 = min(s0 + run_len, run_total);   // (image, row tile) pairs
+  if (s0 >= s1) return;
   const int q0 = qt * cols;
   const int IW = (cols - 1) * ST + 3, IH = (TH - 1) * ST + 3;
-  const int stage_vecs = IH * IW * G;
+  const int row_vecs = IW * G, stage_vecs = IH * row_vecs;
   const int tid = threadIdx.x;
-  const int gl = tid % G, col = tid / G;
-  const bool active = col < cols;
+  const int half = tid & 1, gl = (tid >> 1) % G, col = tid / (2 * G);
+  const int q = q0 + col;
+  const bool active = col < cols && q < g.Q;
   const int c8 = cb * G + gl;
-  const bf16x8 *xin = x + n * g.H * g.W * C8 + cb * G;
   const int w_in0 = q0 * ST - g.pad_w;
 
   // Staging: a thread always copies the same 16-byte pieces of a tile row (piece j = tid + 256 k
-  // of the IW * G pieces), so their column / channel-group arithmetic is done once.
-  constexpr int KMAX = 4;                       // IW * G <= 1024 pieces per tile row
-  const int row_vecs = IW * G;
-  int64_t src_off[KMAX];                        // offset of the piece inside an input row, or -1
+  // of the IW * G pieces, at most 2 * 128 + G of them), so their arithmetic is done once.
+  constexpr int KMAX = 2;
+  int src_off[KMAX];                            // offset of the piece inside an input row, or -1
 #pragma unroll
   for (int k = 0; k < KMAX; ++k) {
     const int j = tid + 256 * k;
     const int gg = j % G, ww = w_in0 + j / G;
-    src_off[k] = (j < row_vecs && ww >= 0 && ww < g.W) ? (int64_t)ww * C8 + gg : -1;
+    src_off[k] = (j < row_vecs && ww >= 0 && ww < g.W) ? ww * C8 + cb * G + gg : -1;
   }
-  // stage the input rows of row tile t into buffer t & 1
-  auto stage = [&](int t) {
-    uint4 *dst = dw_smem + (t & 1) * stage_vecs;
+  auto stage = [&](int sidx) {
+    const int n = sidx / ntiles, t = sidx - n * ntiles;
+    uint4 *dst = dw_smem + (sidx & 1) * stage_vecs;
+    const uint4 *xin = x + (int64_t)n * g.H * g.W * C8;
     const int h_in0 = t * TH * ST - g.pad_h;
     for (int ih = 0; ih < IH; ++ih) {
       const int h = h_in0 + ih;
       const bool hv = h >= 0 && h < g.H;
-      const bf16x8 *rowp = xin + (int64_t)h * g.W * C8;
+      const uint4 *rowp = xin + (int64_t)h * g.W * C8;
 #pragma unroll
       for (int k = 0; k < KMAX; ++k) {
         const int j = tid + 256 * k;
@@ -479,66 +492,64 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  float wv[9][8];
-  float bv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  uint64_t wv[9][2];
+  uint64_t bv[2] = {0, 0};
   if (active) {
 #pragma unroll
     for (int t = 0; t < 9; ++t) {
-      const float4 *wp = (const float4 *)(w + (int64_t)t * g.C + c8 * 8);
-      const float4 a = wp[0], bb = wp[1];
-      wv[t][0] = a.x; wv[t][1] = a.y; wv[t][2] = a.z; wv[t][3] = a.w;
-      wv[t][4] = bb.x; wv[t][5] = bb.y; wv[t][6] = bb.z; wv[t][7] = bb.w;
+      const float4 a = *(const float4 *)(w + (int64_t)t * g.C + c8 * 8 + half * 4);
+      wv[t][0] = dw_pair(__float_as_uint(a.x), __float_as_uint(a.y));
+      wv[t][1] = dw_pair(__float_as_uint(a.z), __float_as_uint(a.w));
     }
     if (bias) {
-      const float4 *bp = (const float4 *)(bias + c8 * 8);
-      const float4 a = bp[0], bb = bp[1];
-      bv[0] = a.x; bv[1] = a.y; bv[2] = a.z; bv[3] = a.w;
-      bv[4] = bb.x; bv[5] = bb.y; bv[6] = bb.z; bv[7] = bb.w;
+      const float4 a = *(const float4 *)(bias + c8 * 8 + half * 4);
+      bv[0] = dw_pair(__float_as_uint(a.x), __float_as_uint(a.y));
+      bv[1] = dw_pair(__float_as_uint(a.z), __float_as_uint(a.w));
     }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 9; ++t) wv[t][0] = wv[t][1] = 0;
   }
-  const int q = q0 + col;
-  const int ntiles = (g.P + TH - 1) / TH;
-  stage(0);
-  for (int t = 0; t < ntiles; ++t) {
-    if (t + 1 < ntiles) {
-      stage(t + 1);
+  stage(s0);
+  for (int sidx = s0; sidx < s1; ++sidx) {
+    if (sidx + 1 < s1) {
+      stage(sidx + 1);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    if (active && q < g.Q) {
-      const uint4 *src = dw_smem + (t & 1) * stage_vecs + (col * ST) * G + gl;
+    if (active) {
+      const int n = sidx / ntiles, t = sidx - n * ntiles;
+      const uint2 *src = reinterpret_cast<const uint2 *>(dw_smem + (sidx & 1) * stage_vecs) +
+                         ((col * ST) * G + gl) * 2 + half;
+      uint2 *yout = y + ((int64_t)n * g.P * g.Q + q) * C8 * 2 + c8 * 2 + half;
       auto load_row = [&](int ih, DwRow &r) {
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
-          const uint4 v = src[(ih * IW + k) * G];
-          const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) r.v[k][j] = u[j];
+          const uint2 v = src[(ih * IW + k) * G * 2];
+          r.v[k][0] = dw_unpack(v.x);
+          r.v[k][1] = dw_unpack(v.y);
         }
       };
       auto emit = [&](int p, const DwRow &a, const DwRow &bq, const DwRow &cq) {
         if (p >= g.P) return;
-        float f[8];
+        uint64_t f0 = bv[0], f1 = bv[1];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = bv[j];
-#pragma unroll
-        for (int k = 0; k < 3; ++k)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {   // a bf16 is the top half of the fp32 of the same value
-            f[2 * j] = fmaf(__uint_as_float(a.v[k][j] << 16), wv[k][2 * j], f[2 * j]);
-            f[2 * j + 1] = fmaf(__uint_as_float(a.v[k][j] & 0xffff0000u), wv[k][2 * j + 1], f[2 * j + 1]);
-            f[2 * j] = fmaf(__uint_as_float(bq.v[k][j] << 16), wv[3 + k][2 * j], f[2 * j]);
-            f[2 * j + 1] = fmaf(__uint_as_float(bq.v[k][j] & 0xffff0000u), wv[3 + k][2 * j + 1], f[2 * j + 1]);
-            f[2 * j] = fmaf(__uint_as_float(cq.v[k][j] << 16), wv[6 + k][2 * j], f[2 * j]);
-            f[2 * j + 1] = fmaf(__uint_as_float(cq.v[k][j] & 0xffff0000u), wv[6 + k][2 * j + 1], f[2 * j + 1]);
-          }
-#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+          f0 = dw_fma2(a.v[k][0], wv[k][0], f0);
+          f1 = dw_fma2(a.v[k][1], wv[k][1], f1);
+          f0 = dw_fma2(bq.v[k][0], wv[3 + k][0], f0);
+          f1 = dw_fma2(bq.v[k][1], wv[3 + k][1], f1);
+          f0 = dw_fma2(cq.v[k][0], wv[6 + k][0], f0);
+          f1 = dw_fma2(cq.v[k][1], wv[6 + k][1], f1);
+        }
         // the activations this kernel takes are all a clamp (a switch over every activation,
         // inlined into each unrolled copy of this body, would not fit the instruction cache)
-        for (int k = 0; k < 8; ++k) f[k] = fminf(fmaxf(f[k], act_lo), act_hi);
-        y[((n * g.P + p) * g.Q + q) * C8 + c8] = pack8(f);
+        uint2 o;
+        o.x = dw_finish(f0, act_lo, act_hi);
+        o.y = dw_finish(f1, act_lo, act_hi);
+        yout[(int64_t)p * g.Q * C8 * 2] = o;
       };
       DwRow r0, r1, r2;
       const int pbase = t * TH;
@@ -548,14 +559,10 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
         for (int pl = 0; pl < TH; pl += 3) {
           load_row(pl + 2, r2);
           emit(pbase + pl, r0, r1, r2);
-          if (pl + 1 < TH) {
-            load_row(pl + 3, r0);
-            emit(pbase + pl + 1, r1, r2, r0);
-          }
-          if (pl + 2 < TH) {
-            load_row(pl + 4, r1);
-            emit(pbase + pl + 2, r2, r0, r1);
-          }
+          load_row(pl + 3, r0);
+          emit(pbase + pl + 1, r1, r2, r0);
+          load_row(pl + 4, r1);
+          emit(pbase + pl + 2, r2, r0, r1);
         }
       } else {
         load_row(0, r0);
@@ -563,16 +570,12 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
           load_row(2 * pl + 1, r1);
           load_row(2 * pl + 2, r2);
           emit(pbase + pl, r0, r1, r2);
-          if (pl + 1 < TH) {
-            load_row(2 * pl + 3, r0);
-            load_row(2 * pl + 4, r1);
-            emit(pbase + pl + 1, r2, r0, r1);
-          }
-          if (pl + 2 < TH) {
-            load_row(2 * pl + 5, r2);
-            load_row(2 * pl + 6, r0);
-            emit(pbase + pl + 2, r1, r2, r0);
-          }
+          load_row(2 * pl + 3, r0);
+          load_row(2 * pl + 4, r1);
+          emit(pbase + pl + 1, r2, r0, r1);
+          load_row(2 * pl + 5, r2);
+          load_row(2 * pl + 6, r0);
+          emit(pbase + pl + 2, r1, r2, r0);
         }
       }
     }
@@ -585,45 +588,82 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
   const int64_t total = (int64_t)g.N * g.P * g.Q * (g.C / 8);
   if (total == 0) return;
   const int C8 = g.C / 8;
-  int G = 8;
-  while (G > 1 && C8 % G) --G;                 // channel groups per CTA: a divisor of C / 8
-  const int cols_max = 256 / G;
   if (g.R == 3 && g.S == 3 && g.stride_h == g.stride_w && (g.stride_h == 1 || g.stride_h == 2) &&
-      (g.act == ACT_IDENTITY || g.act == ACT_RELU || g.act == ACT_CLIP) &&
-      g.Q * 8 >= cols_max * 7 && G >= 2 &&
-      ((cols_max - 1) * g.stride_h + 3) * G <= 1024) {
-    // image rows at least (nearly) as wide as a CTA's column strip: the tiled kernel
+      (g.act == ACT_IDENTITY || g.act == ACT_RELU || g.act == ACT_CLIP)) {
     const int ST = g.stride_h;
-    const float act_lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
-    const float act_hi = g.act == ACT_CLIP ? g.hi : INFINITY;
-    const int tiles_q = (g.Q + cols_max - 1) / cols_max;
-    const int cols = (g.Q + tiles_q - 1) / tiles_q;       // even split of the row
-    int TH = 12;
-    auto stage_bytes = [&](int th) { return (size_t)((th - 1) * ST + 3) * ((cols - 1) * ST + 3) * G * 16; };
-    while (TH > 3 && 2 * stage_bytes(TH) > 100 * 1024) TH -= 3;   // two CTAs per SM
-    const size_t smem = 2 * stage_bytes(TH);
-    const int tiles_c = C8 / G;
-    const unsigned grid = (unsigned)((int64_t)g.N * tiles_q * tiles_c);
-    static bool attr_set[2] = {false, false};
-    if (ST == 1) {
-      if (!attr_set[0]) {
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             200 * 1024);
-        attr_set[0] = true;
+    // Channel groups per CTA (a divisor of C / 8, at most 16) and columns per CTA (128 / G at
+    // most: two threads per channel group and column): the pair that keeps most of the 256
+    // threads busy; among near-equal ones the widest channel run, for contiguous 16-byte pieces.
+    int G = 0, cols = 0, tiles_q = 0;
+    double best = 0.0;
+    for (int cand = 16; cand >= 1; --cand) {
+      if (C8 % cand) continue;
+      const int cmax = 128 / cand;
+      const int tq = (g.Q + cmax - 1) / cmax;
+      const int cl = (g.Q + tq - 1) / tq;
+      const double util = (double)(cl * cand * 2) / 256.0 * (double)g.Q / (double)(cl * tq);
+      if (util > best * 1.05) {
+        best = util;
+        G = cand;
+        cols = cl;
+        tiles_q = tq;
       }
-      depthwise3x3_tile_kernel<1><<<grid, 256, smem, s>>>((const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g,
-                                                         G, cols, TH, tiles_q, tiles_c, act_lo, act_hi);
-    } else {
-      if (!attr_set[1]) {
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             200 * 1024);
-        attr_set[1] = true;
-      }
-      depthwise3x3_tile_kernel<2><<<grid, 256, smem, s>>>((const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g,
-                                                         G, cols, TH, tiles_q, tiles_c, act_lo, act_hi);
     }
-    count(CNT_LAUNCHES);
-    return;
+    const int IW = (cols - 1) * ST + 3;
+    // Rows per tile (a multiple of 3, the register rotation): the choice that stages the fewest
+    // input rows over an image, two stages within half of the shared memory (two CTAs per SM).
+    int TH = 0, ntiles = 0;
+    int64_t best_rows = 0;
+    for (int th = 3; th <= 18; th += 3) {
+      const int ih = (th - 1) * ST + 3;
+      if ((size_t)2 * ih * IW * G * 16 > 100 * 1024) break;
+      const int nt = (g.P + th - 1) / th;
+      const int64_t rows = (int64_t)nt * ih;
+      if (TH == 0 || rows < best_rows) {
+        TH = th;
+        ntiles = nt;
+        best_rows = rows;
+      }
+    }
+    if (G > 0 && TH > 0 && best >= 0.4) {
+      const float act_lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
+      const float act_hi = g.act == ACT_CLIP ? g.hi : INFINITY;
+      const size_t smem = (size_t)2 * ((TH - 1) * ST + 3) * IW * G * 16;
+      const int tiles_c = C8 / G;
+      // Runs of (image, row tile) pairs: one wave of equal runs over the CTA slots when the
+      // strips alone do not fill them, else one run per strip.
+      const int run_total = g.N * ntiles;
+      const int base = tiles_q * tiles_c;
+      const int slots = rt().num_sms * 2;
+      int runs = slots / base;
+      if (runs < 1) runs = 1;
+      if (runs > run_total) runs = run_total;
+      const int run_len = (run_total + runs - 1) / runs;
+      runs = (run_total + run_len - 1) / run_len;
+      const unsigned grid = (unsigned)((int64_t)runs * base);
+      static bool attr_set[2] = {false, false};
+      if (ST == 1) {
+        if (!attr_set[0]) {
+          cudaFuncSetAttribute(depthwise3x3_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               100 * 1024);
+          attr_set[0] = true;
+        }
+        depthwise3x3_tile_kernel<1><<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint2 *)y, g, G,
+                                                           cols, TH, tiles_q, tiles_c, ntiles, run_len,
+                                                           run_total, act_lo, act_hi);
+      } else {
+        if (!attr_set[1]) {
+          cudaFuncSetAttribute(depthwise3x3_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               100 * 1024);
+          attr_set[1] = true;
+        }
+        depthwise3x3_tile_kernel<2><<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint2 *)y, g, G,
+                                                           cols, TH, tiles_q, tiles_c, ntiles, run_len,
+                                                           run_total, act_lo, act_hi);
+      }
+      count(CNT_LAUNCHES);
+      return;
+    }
   }
   if (g.act == ACT_IDENTITY || g.act == ACT_RELU || g.act == ACT_CLIP) {
     const float lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
