@@ -417,6 +417,16 @@ __device__ __forceinline__ uint64_t dw_fma2(uint64_t a, uint64_t b, uint64_t c) 
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+__device__ __forceinline__ uint64_t dw_mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t dw_add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 // two bf16 values in one word -> the fp32 pair (a bf16 is the top half of the fp32 of that value)
 __device__ __forceinline__ uint64_t dw_unpack(uint32_t v) { return dw_pair(v << 16, v & 0xffff0000u); }
 // fp32 pair -> clamp -> two bf16 in one word
@@ -428,15 +438,29 @@ __device__ __forceinline__ uint32_t dw_finish(uint64_t acc, float lo, float hi) 
   const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t *>(&r);
 }
+// The same for bounds that bf16 holds exactly (lower bound 0 or none): the lower bound rides on
+// the conversion, the upper one is a packed minimum after it.  flags: 1 = lower bound 0,
+// 2 = upper bound present (hi2 holds it twice).
+__device__ __forceinline__ uint32_t dw_finish_packed(uint64_t acc, int flags, uint32_t hi2) {
+  float a, b;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(acc));
+  uint32_t r;
+  if (flags & 1)
+    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  if (flags & 2) asm("min.bf16x2 %0, %0, %1;" : "+r"(r) : "r"(hi2));
+  return r;
+}
 struct DwRow {
   uint64_t v[3][2];   // three columns x four channels as fp32 pairs
 };
 
-template <int ST>
+template <int ST, bool PACKED_ACT>
 __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
     const uint4 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
     uint2 *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c, int ntiles,
-    int run_len, int run_total, float act_lo, float act_hi) {
+    int run_len, int run_total, float act_lo, float act_hi, int act_flags, uint32_t act_hi2) {
   extern __shared__ uint4 dw_smem[];
   const int C8 = g.C / 8;
   int b = blockIdx.x;
@@ -457,7 +481,9 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
   const int w_in0 = q0 * ST - g.pad_w;
 
   // Staging: a thread always copies the same 16-byte pieces of a tile row (piece j = tid + 256 k
-  // of the IW * G pieces, at most 2 * 128 + G of them), so their arithmetic is done once.
+  // of the IW * G pieces, at most 2 * 128 + G of them), so their arithmetic is done once.  A piece
+  // outside the image is a copy of zero source bytes, which fills the 16 bytes with zeros: the
+  // loop over the rows has no branch.
   constexpr int KMAX = 2;
   int src_off[KMAX];                            // offset of the piece inside an input row, or -1
 #pragma unroll
@@ -466,27 +492,25 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
     const int gg = j % G, ww = w_in0 + j / G;
     src_off[k] = (j < row_vecs && ww >= 0 && ww < g.W) ? ww * C8 + cb * G + gg : -1;
   }
+  const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(dw_smem);
+  const int row_elems = g.W * C8;
   auto stage = [&](int sidx) {
     const int n = sidx / ntiles, t = sidx - n * ntiles;
-    uint4 *dst = dw_smem + (sidx & 1) * stage_vecs;
-    const uint4 *xin = x + (int64_t)n * g.H * g.W * C8;
+    const uint32_t dst = smem0 + (uint32_t)(((sidx & 1) * stage_vecs + tid) * 16);
+    const uint4 *xin = x + (int64_t)n * g.H * row_elems;
     const int h_in0 = t * TH * ST - g.pad_h;
-    for (int ih = 0; ih < IH; ++ih) {
-      const int h = h_in0 + ih;
-      const bool hv = h >= 0 && h < g.H;
-      const uint4 *rowp = xin + (int64_t)h * g.W * C8;
 #pragma unroll
-      for (int k = 0; k < KMAX; ++k) {
-        const int j = tid + 256 * k;
-        if (j >= row_vecs) break;
-        uint4 *d = dst + ih * row_vecs + j;
-        if (hv && src_off[k] >= 0) {
-          const uint32_t sa = (uint32_t)__cvta_generic_to_shared(d);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(rowp + src_off[k])
-                       : "memory");
-        } else {
-          *d = make_uint4(0, 0, 0, 0);
-        }
+    for (int k = 0; k < KMAX; ++k) {
+      if (tid + 256 * k >= row_vecs) break;
+      const uint4 *colp = xin + max(src_off[k], 0);
+      for (int ih = 0; ih < IH; ++ih) {
+        const int h = h_in0 + ih;
+        const bool ok = (unsigned)h < (unsigned)g.H && src_off[k] >= 0;
+        const uint4 *src = ok ? colp + (int64_t)h * row_elems : x;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                         dst + (uint32_t)((ih * row_vecs + 256 * k) * 16)),
+                     "l"(src), "r"(ok ? 16 : 0)
+                     : "memory");
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -534,21 +558,35 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
       };
       auto emit = [&](int p, const DwRow &a, const DwRow &bq, const DwRow &cq) {
         if (p >= g.P) return;
-        uint64_t f0 = bv[0], f1 = bv[1];
+        // one accumulation chain per filter row and channel pair (six independent chains)
+        uint64_t fa0 = bv[0], fa1 = bv[1], fb0 = 0, fb1 = 0, fc0 = 0, fc1 = 0;
+        fb0 = dw_mul2(bq.v[0][0], wv[3][0]);
+        fb1 = dw_mul2(bq.v[0][1], wv[3][1]);
+        fc0 = dw_mul2(cq.v[0][0], wv[6][0]);
+        fc1 = dw_mul2(cq.v[0][1], wv[6][1]);
+        fa0 = dw_fma2(a.v[0][0], wv[0][0], fa0);
+        fa1 = dw_fma2(a.v[0][1], wv[0][1], fa1);
 #pragma unroll
-        for (int k = 0; k < 3; ++k) {
-          f0 = dw_fma2(a.v[k][0], wv[k][0], f0);
-          f1 = dw_fma2(a.v[k][1], wv[k][1], f1);
-          f0 = dw_fma2(bq.v[k][0], wv[3 + k][0], f0);
-          f1 = dw_fma2(bq.v[k][1], wv[3 + k][1], f1);
-          f0 = dw_fma2(cq.v[k][0], wv[6 + k][0], f0);
-          f1 = dw_fma2(cq.v[k][1], wv[6 + k][1], f1);
+        for (int k = 1; k < 3; ++k) {
+          fa0 = dw_fma2(a.v[k][0], wv[k][0], fa0);
+          fa1 = dw_fma2(a.v[k][1], wv[k][1], fa1);
+          fb0 = dw_fma2(bq.v[k][0], wv[3 + k][0], fb0);
+          fb1 = dw_fma2(bq.v[k][1], wv[3 + k][1], fb1);
+          fc0 = dw_fma2(cq.v[k][0], wv[6 + k][0], fc0);
+          fc1 = dw_fma2(cq.v[k][1], wv[6 + k][1], fc1);
         }
+        const uint64_t f0 = dw_add2(dw_add2(fa0, fb0), fc0);
+        const uint64_t f1 = dw_add2(dw_add2(fa1, fb1), fc1);
         // the activations this kernel takes are all a clamp (a switch over every activation,
         // inlined into each unrolled copy of this body, would not fit the instruction cache)
         uint2 o;
-        o.x = dw_finish(f0, act_lo, act_hi);
-        o.y = dw_finish(f1, act_lo, act_hi);
+        if (PACKED_ACT) {
+          o.x = dw_finish_packed(f0, act_flags, act_hi2);
+          o.y = dw_finish_packed(f1, act_flags, act_hi2);
+        } else {
+          o.x = dw_finish(f0, act_lo, act_hi);
+          o.y = dw_finish(f1, act_lo, act_hi);
+        }
         yout[(int64_t)p * g.Q * C8 * 2] = o;
       };
       DwRow r0, r1, r2;
@@ -641,26 +679,32 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
       const int run_len = (run_total + runs - 1) / runs;
       runs = (run_total + run_len - 1) / run_len;
       const unsigned grid = (unsigned)((int64_t)runs * base);
-      static bool attr_set[2] = {false, false};
-      if (ST == 1) {
-        if (!attr_set[0]) {
-          cudaFuncSetAttribute(depthwise3x3_tile_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               100 * 1024);
-          attr_set[0] = true;
-        }
-        depthwise3x3_tile_kernel<1><<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint2 *)y, g, G,
-                                                           cols, TH, tiles_q, tiles_c, ntiles, run_len,
-                                                           run_total, act_lo, act_hi);
-      } else {
-        if (!attr_set[1]) {
-          cudaFuncSetAttribute(depthwise3x3_tile_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               100 * 1024);
-          attr_set[1] = true;
-        }
-        depthwise3x3_tile_kernel<2><<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint2 *)y, g, G,
-                                                           cols, TH, tiles_q, tiles_c, ntiles, run_len,
-                                                           run_total, act_lo, act_hi);
+      // bounds that bf16 holds exactly go through the packed conversion
+      const __nv_bfloat16 hb = __float2bfloat16_rn(act_hi);
+      const bool packed = (act_lo == 0.0f || act_lo == -INFINITY) &&
+                          (act_hi == INFINITY || __bfloat162float(hb) == act_hi);
+      const int act_flags = (act_lo == 0.0f ? 1 : 0) | (act_hi != INFINITY ? 2 : 0);
+      uint16_t hbits;
+      memcpy(&hbits, &hb, 2);
+      const uint32_t act_hi2 = (uint32_t)hbits * 0x10001u;
+      static bool attr_set = false;
+      if (!attr_set) {
+        const int lim = 100 * 1024;
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        attr_set = true;
       }
+      auto go = [&](auto kern) {
+        kern<<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint2 *)y, g, G, cols, TH, tiles_q,
+                                     tiles_c, ntiles, run_len, run_total, act_lo, act_hi, act_flags,
+                                     act_hi2);
+      };
+      if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true>);
+      else if (ST == 1) go(depthwise3x3_tile_kernel<1, false>);
+      else if (packed) go(depthwise3x3_tile_kernel<2, true>);
+      else go(depthwise3x3_tile_kernel<2, false>);
       count(CNT_LAUNCHES);
       return;
     }
