@@ -401,7 +401,7 @@ __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float 
 // A CTA owns G 8-channel groups (G * 16 bytes of every pixel) of a strip of `cols` output columns
 // and works through a run of row tiles (TH output rows each) that continues from one image into
 // the next, so the grid is cut into equal runs whatever the image size.  The input tile with its
-// halo is staged in shared memory by 16-byte cp.async copies, two tiles deep; what lies outside
+// halo is staged in shared memory by 16-byte cp.async copies, two tiles ahead; what lies outside
 // the image is stored as zeros.  A thread owns FOUR channels of one output column: its nine taps
 // (18 packed fp32 pairs) and the three input rows of the current window, already converted to
 // fp32 pairs, stay in registers, so an input value is converted once and an output row costs
@@ -452,15 +452,19 @@ __device__ __forceinline__ uint32_t dw_finish_packed(uint64_t acc, int flags, ui
   if (flags & 2) asm("min.bf16x2 %0, %0, %1;" : "+r"(r) : "r"(hi2));
   return r;
 }
+template <int NP>
 struct DwRow {
-  uint64_t v[3][2];   // three columns x four channels as fp32 pairs
+  uint64_t v[3][NP];   // three columns x NP channel pairs as fp32 pairs
 };
 
-template <int ST, bool PACKED_ACT>
-__global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
+// CH = channels per thread: 4 (two CTAs per SM); 2 also compiles (four CTAs per SM) but is slower.
+template <int ST, bool PACKED_ACT, int CH>
+__global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel(
     const uint4 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
-    uint2 *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c, int ntiles,
+    uint32_t *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c, int ntiles,
     int run_len, int run_total, float act_lo, float act_hi, int act_flags, uint32_t act_hi2) {
+  constexpr int NP = CH / 2;      // channel pairs (32-bit words of bf16) per thread
+  constexpr int LG = 8 / CH;      // threads per 16-byte channel group
   extern __shared__ uint4 dw_smem[];
   const int C8 = g.C / 8;
   int b = blockIdx.x;
@@ -474,7 +478,7 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
   const int IW = (cols - 1) * ST + 3, IH = (TH - 1) * ST + 3;
   const int row_vecs = IW * G, stage_vecs = IH * row_vecs;
   const int tid = threadIdx.x;
-  const int half = tid & 1, gl = (tid >> 1) % G, col = tid / (2 * G);
+  const int sub = tid % LG, gl = (tid / LG) % G, col = tid / (LG * G);
   const int q = q0 + col;
   const bool active = col < cols && q < g.Q;
   const int c8 = cb * G + gl;
@@ -484,112 +488,129 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
   // of the IW * G pieces, at most 2 * 128 + G of them), so their arithmetic is done once.  A piece
   // outside the image is a copy of zero source bytes, which fills the 16 bytes with zeros: the
   // loop over the rows has no branch.
+  // When a tile row has at most 128 pieces, the threads split into groups that take every
+  // `ngroups`-th row each, so that all warps share the copy work.
   constexpr int KMAX = 2;
+  const int ngroups = row_vecs <= 128 ? 256 / row_vecs : 1;
+  const int grp = ngroups > 1 ? tid / row_vecs : 0;
+  const int jbase = ngroups > 1 ? tid - grp * row_vecs : tid;
   int src_off[KMAX];                            // offset of the piece inside an input row, or -1
 #pragma unroll
   for (int k = 0; k < KMAX; ++k) {
-    const int j = tid + 256 * k;
+    const int j = jbase + 256 * k;
     const int gg = j % G, ww = w_in0 + j / G;
     src_off[k] = (j < row_vecs && ww >= 0 && ww < g.W) ? ww * C8 + cb * G + gg : -1;
   }
   const uint32_t smem0 = (uint32_t)__cvta_generic_to_shared(dw_smem);
   const int row_elems = g.W * C8;
-  auto stage = [&](int sidx) {
-    const int n = sidx / ntiles, t = sidx - n * ntiles;
-    const uint32_t dst = smem0 + (uint32_t)(((sidx & 1) * stage_vecs + tid) * 16);
-    const uint4 *xin = x + (int64_t)n * g.H * row_elems;
-    const int h_in0 = t * TH * ST - g.pad_h;
+  auto stage = [&](int sidx, int into) {
+    if (grp < ngroups) {
+      const int n = sidx / ntiles, t = sidx - n * ntiles;
+      const uint32_t dst = smem0 + (uint32_t)((into * stage_vecs + jbase) * 16);
+      const uint4 *xin = x + (int64_t)n * g.H * row_elems;
+      const int h_in0 = t * TH * ST - g.pad_h;
 #pragma unroll
-    for (int k = 0; k < KMAX; ++k) {
-      if (tid + 256 * k >= row_vecs) break;
-      const uint4 *colp = xin + max(src_off[k], 0);
-      for (int ih = 0; ih < IH; ++ih) {
-        const int h = h_in0 + ih;
-        const bool ok = (unsigned)h < (unsigned)g.H && src_off[k] >= 0;
-        const uint4 *src = ok ? colp + (int64_t)h * row_elems : x;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                         dst + (uint32_t)((ih * row_vecs + 256 * k) * 16)),
-                     "l"(src), "r"(ok ? 16 : 0)
-                     : "memory");
+      for (int k = 0; k < KMAX; ++k) {
+        if (jbase + 256 * k >= row_vecs) break;
+        const uint4 *colp = xin + max(src_off[k], 0);
+        for (int ih = grp; ih < IH; ih += ngroups) {
+          const int h = h_in0 + ih;
+          const bool ok = (unsigned)h < (unsigned)g.H && src_off[k] >= 0;
+          const uint4 *src = ok ? colp + (int64_t)h * row_elems : x;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                           dst + (uint32_t)((ih * row_vecs + 256 * k) * 16)),
+                       "l"(src), "r"(ok ? 16 : 0)
+                       : "memory");
+        }
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  uint64_t wv[9][2];
-  uint64_t bv[2] = {0, 0};
+  uint64_t wv[9][NP];
+  uint64_t bv[NP];
+#pragma unroll
+  for (int j = 0; j < NP; ++j) bv[j] = 0;
   if (active) {
 #pragma unroll
     for (int t = 0; t < 9; ++t) {
-      const float4 a = *(const float4 *)(w + (int64_t)t * g.C + c8 * 8 + half * 4);
-      wv[t][0] = dw_pair(__float_as_uint(a.x), __float_as_uint(a.y));
-      wv[t][1] = dw_pair(__float_as_uint(a.z), __float_as_uint(a.w));
+      const float2 *wp = (const float2 *)(w + (int64_t)t * g.C + c8 * 8 + sub * CH);
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float2 a = wp[j];
+        wv[t][j] = dw_pair(__float_as_uint(a.x), __float_as_uint(a.y));
+      }
     }
     if (bias) {
-      const float4 a = *(const float4 *)(bias + c8 * 8 + half * 4);
-      bv[0] = dw_pair(__float_as_uint(a.x), __float_as_uint(a.y));
-      bv[1] = dw_pair(__float_as_uint(a.z), __float_as_uint(a.w));
+      const float2 *bp = (const float2 *)(bias + c8 * 8 + sub * CH);
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float2 a = bp[j];
+        bv[j] = dw_pair(__float_as_uint(a.x), __float_as_uint(a.y));
+      }
     }
   } else {
 #pragma unroll
-    for (int t = 0; t < 9; ++t) wv[t][0] = wv[t][1] = 0;
+    for (int t = 0; t < 9; ++t)
+#pragma unroll
+      for (int j = 0; j < NP; ++j) wv[t][j] = 0;
   }
-  stage(s0);
+  // Three buffers, one barrier per tile: after the barrier of tile i every thread has finished
+  // tile i - 1, whose buffer then takes tile i + 2.  A group is committed every iteration (an empty
+  // one past the end), so "all but the newest group" always means "tile i has landed".
+  stage(s0, 0);
+  if (s0 + 1 < s1) stage(s0 + 1, 1);
+  else asm volatile("cp.async.commit_group;" ::: "memory");
+  int buf = 0;
   for (int sidx = s0; sidx < s1; ++sidx) {
-    if (sidx + 1 < s1) {
-      stage(sidx + 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
+    if (sidx + 2 < s1) stage(sidx + 2, buf == 0 ? 2 : buf - 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
     if (active) {
       const int n = sidx / ntiles, t = sidx - n * ntiles;
-      const uint2 *src = reinterpret_cast<const uint2 *>(dw_smem + (sidx & 1) * stage_vecs) +
-                         ((col * ST) * G + gl) * 2 + half;
-      uint2 *yout = y + ((int64_t)n * g.P * g.Q + q) * C8 * 2 + c8 * 2 + half;
-      auto load_row = [&](int ih, DwRow &r) {
+      // shared-memory and output positions in 32-bit words (NP words per thread)
+      const uint32_t *src = reinterpret_cast<const uint32_t *>(dw_smem + buf * stage_vecs) +
+                            ((col * ST) * G + gl) * 4 + sub * NP;
+      uint32_t *yout = y + ((int64_t)n * g.P * g.Q + q) * C8 * 4 + c8 * 4 + sub * NP;
+      auto load_row = [&](int ih, DwRow<NP> &r) {
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
-          const uint2 v = src[(ih * IW + k) * G * 2];
-          r.v[k][0] = dw_unpack(v.x);
-          r.v[k][1] = dw_unpack(v.y);
+          const uint32_t *sp = src + (ih * IW + k) * G * 4;
+          if (NP == 2) {
+            const uint2 v = *reinterpret_cast<const uint2 *>(sp);
+            r.v[k][0] = dw_unpack(v.x);
+            r.v[k][NP - 1] = dw_unpack(v.y);
+          } else {
+            r.v[k][0] = dw_unpack(*sp);
+          }
         }
       };
-      auto emit = [&](int p, const DwRow &a, const DwRow &bq, const DwRow &cq) {
+      auto emit = [&](int p, const DwRow<NP> &a, const DwRow<NP> &bq, const DwRow<NP> &cq) {
         if (p >= g.P) return;
-        // one accumulation chain per filter row and channel pair (six independent chains)
-        uint64_t fa0 = bv[0], fa1 = bv[1], fb0 = 0, fb1 = 0, fc0 = 0, fc1 = 0;
-        fb0 = dw_mul2(bq.v[0][0], wv[3][0]);
-        fb1 = dw_mul2(bq.v[0][1], wv[3][1]);
-        fc0 = dw_mul2(cq.v[0][0], wv[6][0]);
-        fc1 = dw_mul2(cq.v[0][1], wv[6][1]);
-        fa0 = dw_fma2(a.v[0][0], wv[0][0], fa0);
-        fa1 = dw_fma2(a.v[0][1], wv[0][1], fa1);
+        // one accumulation chain per filter row and channel pair
+        uint32_t o[NP];
 #pragma unroll
-        for (int k = 1; k < 3; ++k) {
-          fa0 = dw_fma2(a.v[k][0], wv[k][0], fa0);
-          fa1 = dw_fma2(a.v[k][1], wv[k][1], fa1);
-          fb0 = dw_fma2(bq.v[k][0], wv[3 + k][0], fb0);
-          fb1 = dw_fma2(bq.v[k][1], wv[3 + k][1], fb1);
-          fc0 = dw_fma2(cq.v[k][0], wv[6 + k][0], fc0);
-          fc1 = dw_fma2(cq.v[k][1], wv[6 + k][1], fc1);
+        for (int j = 0; j < NP; ++j) {
+          uint64_t fa = dw_fma2(a.v[0][j], wv[0][j], bv[j]);
+          uint64_t fb = dw_mul2(bq.v[0][j], wv[3][j]);
+          uint64_t fc = dw_mul2(cq.v[0][j], wv[6][j]);
+#pragma unroll
+          for (int k = 1; k < 3; ++k) {
+            fa = dw_fma2(a.v[k][j], wv[k][j], fa);
+            fb = dw_fma2(bq.v[k][j], wv[3 + k][j], fb);
+            fc = dw_fma2(cq.v[k][j], wv[6 + k][j], fc);
+          }
+          const uint64_t f = dw_add2(dw_add2(fa, fb), fc);
+          // the activations this kernel takes are all a clamp (a switch over every activation,
+          // inlined into each unrolled copy of this body, would not fit the instruction cache)
+          o[j] = PACKED_ACT ? dw_finish_packed(f, act_flags, act_hi2) : dw_finish(f, act_lo, act_hi);
         }
-        const uint64_t f0 = dw_add2(dw_add2(fa0, fb0), fc0);
-        const uint64_t f1 = dw_add2(dw_add2(fa1, fb1), fc1);
-        // the activations this kernel takes are all a clamp (a switch over every activation,
-        // inlined into each unrolled copy of this body, would not fit the instruction cache)
-        uint2 o;
-        if (PACKED_ACT) {
-          o.x = dw_finish_packed(f0, act_flags, act_hi2);
-          o.y = dw_finish_packed(f1, act_flags, act_hi2);
-        } else {
-          o.x = dw_finish(f0, act_lo, act_hi);
-          o.y = dw_finish(f1, act_lo, act_hi);
-        }
-        yout[(int64_t)p * g.Q * C8 * 2] = o;
+        uint32_t *yp = yout + (int64_t)p * g.Q * C8 * 4;
+        if (NP == 2) *reinterpret_cast<uint2 *>(yp) = make_uint2(o[0], o[NP - 1]);
+        else *yp = o[0];
       };
-      DwRow r0, r1, r2;
+      DwRow<NP> r0, r1, r2;
       const int pbase = t * TH;
       if (ST == 1) {
         load_row(0, r0);
@@ -617,7 +638,7 @@ __global__ void __launch_bounds__(256, 2) depthwise3x3_tile_kernel(
         }
       }
     }
-    __syncthreads();   // the buffer is staged again two tiles on
+    buf = buf == 2 ? 0 : buf + 1;
   }
 }
 
@@ -632,14 +653,25 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
     // Channel groups per CTA (a divisor of C / 8, at most 16) and columns per CTA (128 / G at
     // most: two threads per channel group and column): the pair that keeps most of the 256
     // threads busy; among near-equal ones the widest channel run, for contiguous 16-byte pieces.
+    const float act_lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
+    const float act_hi = g.act == ACT_CLIP ? g.hi : INFINITY;
+    // bounds that bf16 holds exactly go through the packed conversion
+    const __nv_bfloat16 hb = __float2bfloat16_rn(act_hi);
+    const bool packed = (act_lo == 0.0f || act_lo == -INFINITY) &&
+                        (act_hi == INFINITY || __bfloat162float(hb) == act_hi);
+    // Channels per thread: 4.  (2 halves the registers and doubles the resident CTAs, but the
+    // kernel is bound by its instruction count, which grows: measured 1.4x slower.)
+    const int CH = 4;
+    const int LG = 8 / CH;
     int G = 0, cols = 0, tiles_q = 0;
     double best = 0.0;
     for (int cand = 16; cand >= 1; --cand) {
       if (C8 % cand) continue;
-      const int cmax = 128 / cand;
+      const int cmax = 256 / (LG * cand);
+      if (cmax < 1) continue;
       const int tq = (g.Q + cmax - 1) / cmax;
       const int cl = (g.Q + tq - 1) / tq;
-      const double util = (double)(cl * cand * 2) / 256.0 * (double)g.Q / (double)(cl * tq);
+      const double util = (double)(cl * cand * LG) / 256.0 * (double)g.Q / (double)(cl * tq);
       if (util > best * 1.05) {
         best = util;
         G = cand;
@@ -649,12 +681,12 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
     }
     const int IW = (cols - 1) * ST + 3;
     // Rows per tile (a multiple of 3, the register rotation): the choice that stages the fewest
-    // input rows over an image, two stages within half of the shared memory (two CTAs per SM).
+    // input rows over an image, three buffers within the CTA's share of the shared memory.
     int TH = 0, ntiles = 0;
     int64_t best_rows = 0;
     for (int th = 3; th <= 18; th += 3) {
       const int ih = (th - 1) * ST + 3;
-      if ((size_t)2 * ih * IW * G * 16 > 100 * 1024) break;
+      if ((size_t)3 * ih * IW * G * 16 > (size_t)(CH == 4 ? 100 : 50) * 1024) break;
       const int nt = (g.P + th - 1) / th;
       const int64_t rows = (int64_t)nt * ih;
       if (TH == 0 || rows < best_rows) {
@@ -664,25 +696,19 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
       }
     }
     if (G > 0 && TH > 0 && best >= 0.4) {
-      const float act_lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
-      const float act_hi = g.act == ACT_CLIP ? g.hi : INFINITY;
-      const size_t smem = (size_t)2 * ((TH - 1) * ST + 3) * IW * G * 16;
+      const size_t smem = (size_t)3 * ((TH - 1) * ST + 3) * IW * G * 16;
       const int tiles_c = C8 / G;
       // Runs of (image, row tile) pairs: one wave of equal runs over the CTA slots when the
       // strips alone do not fill them, else one run per strip.
       const int run_total = g.N * ntiles;
       const int base = tiles_q * tiles_c;
-      const int slots = rt().num_sms * 2;
+      const int slots = rt().num_sms * (CH == 4 ? 2 : 4);
       int runs = slots / base;
       if (runs < 1) runs = 1;
       if (runs > run_total) runs = run_total;
       const int run_len = (run_total + runs - 1) / runs;
       runs = (run_total + run_len - 1) / run_len;
       const unsigned grid = (unsigned)((int64_t)runs * base);
-      // bounds that bf16 holds exactly go through the packed conversion
-      const __nv_bfloat16 hb = __float2bfloat16_rn(act_hi);
-      const bool packed = (act_lo == 0.0f || act_lo == -INFINITY) &&
-                          (act_hi == INFINITY || __bfloat162float(hb) == act_hi);
       const int act_flags = (act_lo == 0.0f ? 1 : 0) | (act_hi != INFINITY ? 2 : 0);
       uint16_t hbits;
       memcpy(&hbits, &hb, 2);
@@ -690,21 +716,21 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
       static bool attr_set = false;
       if (!attr_set) {
         const int lim = 100 * 1024;
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
         attr_set = true;
       }
       auto go = [&](auto kern) {
-        kern<<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint2 *)y, g, G, cols, TH, tiles_q,
+        kern<<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint32_t *)y, g, G, cols, TH, tiles_q,
                                      tiles_c, ntiles, run_len, run_total, act_lo, act_hi, act_flags,
                                      act_hi2);
       };
-      if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true>);
-      else if (ST == 1) go(depthwise3x3_tile_kernel<1, false>);
-      else if (packed) go(depthwise3x3_tile_kernel<2, true>);
-      else go(depthwise3x3_tile_kernel<2, false>);
+      if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true, 4>);
+      else if (ST == 1) go(depthwise3x3_tile_kernel<1, false, 4>);
+      else if (packed) go(depthwise3x3_tile_kernel<2, true, 4>);
+      else go(depthwise3x3_tile_kernel<2, false, 4>);
       count(CNT_LAUNCHES);
       return;
     }
