@@ -109,7 +109,7 @@ void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int
     dst = scratch_get(layout == PACK_STEM ? 5 : 1, packed_bytes);
   }
   if (!dst) return nullptr;
-  if (layout == PACK_KRSC) launch_pack_krsc_bf16(w, (bf16 *)dst, K, C, R, S, r.stream);
+  if (layout == PACK_KRSC) launch_pack_krsc_bf16(w, (bf16 *)dst, K, C, R, S, Cp, r.stream);
   else if (layout == PACK_DW) launch_pack_dw_f32(w, (float *)dst, C, R, S, r.stream);
   else if (layout == PACK_RAW)
     OCC_CUDA(cudaMemcpyAsync(dst, w, packed_bytes, cudaMemcpyDeviceToDevice, r.stream));
@@ -178,8 +178,9 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
     a.w_step = g.stride_w * Cp;
     a.row_elems = Wp * Cp;
   } else {
-    if (g.C % 16 != 0) return false;
-    a.H = g.H; a.W = g.W; a.Cf = g.C;
+    if (g.C % 8 != 0) return false;
+    Cp = (g.C + 15) / 16 * 16;   // the MMA takes 16 channels at a time: pad with zero channels
+    a.H = g.H; a.W = g.W; a.Cf = Cp;
     a.R = g.R; a.S = g.S;
     a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
   }
@@ -198,19 +199,29 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
     a.w = (const bf16 *)packed_weights(w, PACK_FOLD, (size_t)g.R * g.K * a.Cf * 2, g.K, g.C, g.R,
                                        g.S, Sp, Cp);
   } else {
+    const bf16 *xb = nullptr;
     if (is_bf16(x, g.N, g.C, g.H, g.W)) {
-      a.x = (const bf16 *)x;
-      job.dep_lo[0] = (uintptr_t)x;
-      job.dep_hi[0] = (uintptr_t)x + (size_t)g.N * g.C * g.H * g.W * 2;
+      xb = (const bf16 *)x;
+      if (Cp == g.C) {
+        job.dep_lo[0] = (uintptr_t)x;
+        job.dep_hi[0] = (uintptr_t)x + (size_t)g.N * g.C * g.H * g.W * 2;
+      }
     } else {
       ensure_f32(x);
       bf16 *xc = (bf16 *)scratch_get(0, (size_t)g.N * g.C * g.H * g.W * 2);
       if (!xc) return false;
       launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, r.stream);
-      a.x = xc;
+      xb = xc;
     }
-    a.w = (const bf16 *)packed_weights(w, PACK_KRSC, (size_t)g.R * g.S * g.K * g.C * 2, g.K, g.C,
-                                       g.R, g.S, 0, 0);
+    if (Cp != g.C) {   // the kernel reads the padded copy, made now: no dependence on x later
+      bf16 *xp = (bf16 *)scratch_get(6, (size_t)g.N * Cp * g.H * g.W * 2);
+      if (!xp) return false;
+      launch_pad_channels_bf16(xb, xp, (int64_t)g.N * g.H * g.W, g.C, Cp, r.stream);
+      xb = xp;
+    }
+    a.x = xb;
+    a.w = (const bf16 *)packed_weights(w, PACK_KRSC, (size_t)g.R * g.S * g.K * Cp * 2, g.K, g.C,
+                                       g.R, g.S, 0, Cp);
   }
   if (!a.w) return false;
   bool ready = g_pack_was_resident;

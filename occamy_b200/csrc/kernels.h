@@ -61,7 +61,9 @@ void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t
 void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias, bf16 *y,
                            const ConvGeom &g, cudaStream_t s);
 // Weight packing: fp32 KCRS -> bf16 [R*S][K][C] (dense conv) ...
-void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, cudaStream_t s);
+void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Cp,
+                           cudaStream_t s);
+void launch_pad_channels_bf16(const bf16 *x, bf16 *y, int64_t pixels, int C, int Cp, cudaStream_t s);
 // ... fp32 [C,1,R,S] -> fp32 [R*S][C] (depthwise) ...
 void launch_pack_dw_f32(const float *w, float *out, int C, int R, int S, cudaStream_t s);
 // ... and fp32 KCRS with tiny C -> bf16 [R][K][Sp*Cp] (width taps folded into channels).

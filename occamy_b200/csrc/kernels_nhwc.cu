@@ -750,21 +750,47 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
 // ---------------------------------------------------------------------------
 // Weight packing (runs once per constant; results stay resident)
 // ---------------------------------------------------------------------------
+// [K][C][R*S] fp32 -> [R*S][K][Cp] bf16, channels c >= C (padding up to Cp) zero.
 __global__ void pack_krsc_kernel(const float *__restrict__ w, bf16 *__restrict__ out, int K, int C,
-                                 int RS, int64_t total) {
+                                 int Cp, int RS, int64_t total) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % C);
-    const int k = (int)((i / C) % K);
-    const int t = (int)(i / ((int64_t)C * K));
-    out[i] = __float2bfloat16_rn(w[((int64_t)k * C + c) * RS + t]);
+    const int c = (int)(i % Cp);
+    const int k = (int)((i / Cp) % K);
+    const int t = (int)(i / ((int64_t)Cp * K));
+    out[i] = __float2bfloat16_rn(c < C ? w[((int64_t)k * C + c) * RS + t] : 0.0f);
   }
 }
 
-void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, cudaStream_t s) {
-  const int64_t total = (int64_t)K * C * R * S;
+void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Cp,
+                           cudaStream_t s) {
+  if (Cp < C) Cp = C;
+  const int64_t total = (int64_t)K * Cp * R * S;
   if (total == 0) return;
-  pack_krsc_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, out, K, C, R * S, total);
+  pack_krsc_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, out, K, C, Cp, R * S, total);
+  count(CNT_LAUNCHES);
+}
+
+// [pixels][C8 * 8] bf16 -> [pixels][Cp8 * 8] bf16 with zero channels appended (a channel count
+// that is not a multiple of the MMA's 16 is padded before the tensor-core convolution).
+__global__ void pad_channels_kernel(const bf16x8 *__restrict__ x, bf16x8 *__restrict__ y, int C8,
+                                    int Cp8, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % Cp8);
+    const int64_t px = i / Cp8;
+    bf16x8 v;
+    v.u = make_uint4(0, 0, 0, 0);
+    if (c < C8) v = x[px * C8 + c];
+    y[i] = v;
+  }
+}
+
+void launch_pad_channels_bf16(const bf16 *x, bf16 *y, int64_t pixels, int C, int Cp, cudaStream_t s) {
+  const int64_t total = pixels * (Cp / 8);
+  if (total == 0) return;
+  pad_channels_kernel<<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, Cp / 8,
+                                                        total);
   count(CNT_LAUNCHES);
 }
 

@@ -79,8 +79,8 @@ struct Runtime {
   std::unordered_map<WeightKey, PackedWeight, WeightKeyHash> wcache;
   // host sources whose packed form is resident: source -> (bytes, fingerprint)
   std::unordered_map<const void *, std::pair<size_t, uint64_t>> resident;
-  void *scratch[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-  size_t scratch_bytes[6] = {0, 0, 0, 0, 0, 0};
+  void *scratch[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t scratch_bytes[7] = {0, 0, 0, 0, 0, 0, 0};
   int *dev_err = nullptr;   // device word the kernels' bounded waits report into
   int *host_err = nullptr;  // pinned mirror
   bool log = false;

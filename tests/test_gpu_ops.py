@@ -48,6 +48,8 @@ CONV_CASES = [
     (2, 16, 9, 9, 40, 1, 0, 1, 1),        # 16-channel K block
     (1, 48, 10, 10, 96, 3, 1, 1, 1),      # 48 = 3 x 16-channel blocks
     (1, 320, 7, 7, 1280, 1, 0, 1, 1),     # MobileNetV2 head; K = 5 x 256
+    (2, 24, 14, 14, 144, 1, 0, 1, 1),     # 24 input channels: zero-padded to 32 for the MMA
+    (1, 40, 9, 9, 24, 3, 1, 1, 1),        # 40 -> 48 padded, 3x3 with halo
     (2, 8, 12, 12, 8, 3, 1, 1, 2),        # grouped (CUDA-core path in both modes)
     (2, 20, 9, 9, 10, 3, 0, 1, 1),        # channel counts no tensor-core tile fits
     (2, 32, 16, 16, 32, 3, 1, 1, 32),     # depthwise stride 1
