@@ -401,7 +401,7 @@ float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t
   e.depthwise = depthwise;
   e.fusable = shape_ok && r.mode == MATH_BF16 && g.P > 0 && g.Q > 0 && g.N > 0 &&
               (depthwise ? g.C % 8 == 0
-                         : (g.groups == 1 && g.K % 8 == 0 && (g.C < 16 || g.C % 16 == 0)));
+                         : (g.groups == 1 && g.K % 8 == 0 && (g.C < 16 || g.C % 8 == 0)));
   // the fused convolution + max-pool kernel takes 64-channel stems whose column step is 16 bytes
   e.poolable = e.fusable && !depthwise && g.C <= 4 && g.K == 64 && g.stride_w == 2 && g.Q <= 128 &&
                g.S <= 16 && g.R <= 11;
