@@ -181,6 +181,11 @@ int occamy_get_math_mode(void);
 int occamy_last_error(int clear);
 /* Block until all work enqueued by this library has finished; returns cudaError_t. */
 int occamy_synchronize(void);
+/* Self-test of the kernels' watchdog: enqueues a one-thread kernel that waits on a barrier
+ * nothing will ever signal.  Its wait is the bounded wait of the convolution kernels, so
+ * after about two seconds it gives up and reports; the next occamy_synchronize() then makes
+ * occamy_last_error() return 1099.  Nothing hangs and the context stays usable. */
+void occamy_selftest_bounded_wait(void);
 /* Stream all kernels of this library are launched on (for CUDA-event timing). */
 cudaStream_t occamy_stream(void);
 /* Counters since load: [0] kernel launches, [1] bytes uploaded host->device,
@@ -201,6 +206,10 @@ int64_t occamy_fused_chains(void);
 void occamy_set_cross_call_fusion(int on);
 /* Drop the resident packed-weight cache (forces re-upload and re-pack). */
 void occamy_clear_weight_cache(void);
+/* 0: keep no packed constants between calls (every filter is packed again on every use and
+ * every constant upload crosses PCIe, as in the reference); 1 (default): keep them.  Same
+ * switch as the environment variable OCCAMY_CACHE_WEIGHTS=0|1. */
+void occamy_set_weight_cache(int on);
 
 /* ---- fused convolution for callers that must not allocate ---------------------- */
 /* No counterpart in the reference.  Same arithmetic as DNNConvBiasActivFunc in the bf16
@@ -215,12 +224,23 @@ void occamy_clear_weight_cache(void);
  * Work is enqueued on `stream`; the call does not wait for it.  All calls share the one
  * array: calls whose kernels may overlap on the GPU race, so keep them on one stream or
  * order them with events.  The first call on each device also looks up the array's device
- * address; make it outside any stream capture.  Returns 0, a negative code as above, or a
- * cudaError_t value. */
+ * address (guarded: once per device even if two host threads race to it); make it outside
+ * any stream capture.  Returns 0, a negative code as above (-3 also for extents beyond
+ * INT_MAX, negative pads, or a filter larger than the padded image), or a cudaError_t
+ * value.  A return of 0 says the work was enqueued: a kernel whose bounded waits ran out
+ * afterwards leaves garbage in y and a code in the array's error word, which
+ * occamy_noalloc_last_error() below (and occamy_last_error / occamy_synchronize) report. */
 int occamy_conv_bias_act_noalloc(const float *x, const int64_t dimX[4], const float *w,
                                  const int64_t dimW[4], const float *bias, const int64_t pads[2],
                                  const int64_t strides[2], int64_t activMode, float *y,
                                  cudaStream_t stream);
+/* No counterpart in the reference.  0, or the code (1001..1006) a kernel of an earlier
+ * occamy_conv_bias_act_noalloc call on the current device left when one of its bounded
+ * waits ran out; `clear` != 0 resets it.  Reads one word with a blocking copy and allocates
+ * nothing; synchronise the stream the calls went to before asking. */
+int occamy_noalloc_last_error(int clear);
+/* Bytes of the fixed array available to one call's working copies. */
+int64_t occamy_noalloc_capacity(void);
 
 #ifdef __cplusplus
 }

@@ -26,7 +26,7 @@ REPLAY_SRCS = [os.path.join("host", "replay.cpp")]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-I", CSRC, "-I", INCLUDE]
-NVCC_FLAGS += os.environ.get("OCCAMY_NVCC_EXTRA", "").split()   # e.g. -DOCCAMY_TC_TIMERS
+NVCC_FLAGS += os.environ.get("OCCAMY_NVCC_EXTRA", "").split()   # e.g. -DOCCAMY_TUNING (sweep hooks)
 
 RUNTIME_SO = os.path.join(LIB, "liboccamy_dnn.so")
 RUNTIME_A = os.path.join(LIB, "libcd_dnn_wrapper.a")

@@ -146,12 +146,24 @@ struct ConvJob {
   float *out = nullptr;       // tensor the result goes to
   bool bias_set = false, res_set = false, act_set = false;
   int absorbed = 0;           // later calls folded into this one so far
-  uintptr_t dep_lo[2] = {0, 0}, dep_hi[2] = {0, 0};  // device ranges still to be read
+  // device ranges still to be read: [0] input, [1] residual operand, [2] a bias that is read
+  // from the caller's tensor (no resident copy exists)
+  uintptr_t dep_lo[3] = {0, 0, 0}, dep_hi[3] = {0, 0, 0};
   // folded (few-channel) form: what the fused convolution + pool kernel needs besides `a`
   const bf16 *w_stem = nullptr;   // filter in that kernel's layout, packed while the filter is live
 };
 
 ConvJob g_pending;  // convolution held back while later calls are folded into it
+
+// A bias without a resident copy is read from the caller's tensor when the (possibly held-back)
+// kernel finally runs: until then that tensor must neither be freed nor overwritten.
+void job_track_bias(ConvJob &job, const float *used, const float *callers, int channels) {
+  job.dep_lo[2] = job.dep_hi[2] = 0;
+  if (used && used == callers) {
+    job.dep_lo[2] = (uintptr_t)callers;
+    job.dep_hi[2] = (uintptr_t)callers + (size_t)channels * 4;
+  }
+}
 
 bool prepare_dense(const float *x, const float *w, const float *bias, const ConvGeom &g,
                    ConvJob &job) {
@@ -227,6 +239,7 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
   bool ready = g_pack_was_resident;
   a.bias = bias ? resident_f32(bias, (size_t)g.K * 4) : nullptr;
   if (bias) ready = ready && g_pack_was_resident;
+  job_track_bias(job, a.bias, bias, g.K);
   // filter and bias were on the device before this call: the kernel may fetch them while the
   // kernel before it is still running
   a.consts_ready = ready ? 1 : 0;
@@ -259,6 +272,7 @@ bool prepare_depthwise(const float *x, const float *w, const float *bias, const 
                                           g.S, 0, 0);
   if (!job.dw_w) return false;
   job.bias = bias ? resident_f32(bias, (size_t)g.C * 4) : nullptr;
+  job_track_bias(job, job.bias, bias, g.C);
   job.depthwise = true;
   job.g = g;
   job.bias_set = bias != nullptr;
@@ -298,6 +312,15 @@ void launch_job(ConvJob &job) {
     job.a.residual = (const bf16 *)tmp;
     count(CNT_LAUNCHES);
   }
+  if (ranges_overlap(olo, ohi, job.dep_lo[2], job.dep_hi[2])) {
+    const size_t bytes = job.dep_hi[2] - job.dep_lo[2];
+    void *tmp = scratch_get(7, bytes);
+    OCC_CUDA(cudaMemcpyAsync(tmp, (const void *)job.dep_lo[2], bytes, cudaMemcpyDeviceToDevice,
+                             r.stream));
+    if (job.depthwise) job.bias = (const float *)tmp;
+    else job.a.bias = (const float *)tmp;
+    count(CNT_LAUNCHES);
+  }
   if (job.depthwise) {
     launch_depthwise_bf16(job.dw_x, job.dw_w, job.bias, (bf16 *)job.out, g, r.stream);
   } else {
@@ -324,7 +347,7 @@ void pending_guard_range(const void *p, size_t bytes, bool writes) {
   if (!g_pending.active) return;
   const uintptr_t lo = (uintptr_t)p, hi = lo + bytes;
   if (writes)
-    for (int k = 0; k < 2; ++k)
+    for (int k = 0; k < 3; ++k)
       if (ranges_overlap(lo, hi, g_pending.dep_lo[k], g_pending.dep_hi[k])) {
         if (rt().log) fprintf(stderr, "[occamy] held-back conv runs early: input %d overwritten\n", k);
         flush_pending();
@@ -394,6 +417,7 @@ float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t
   te_dims(e, dX, 4); te_dims(e, dW, 4); te_dims(e, pads, 2); te_dims(e, strides, 2);
   te_i(e, groups); te_i(e, act_mode);
   e.in[0] = (uintptr_t)x; e.in[1] = (uintptr_t)w; e.in[2] = (uintptr_t)bias;
+  e.in_bytes[0] = numel4(dX) * 4; e.in_bytes[1] = numel4(dW) * 4; e.in_bytes[2] = dW[0] * 4;
   e.out = (uintptr_t)y;
   e.dims[0] = g.N; e.dims[1] = g.K; e.dims[2] = g.P; e.dims[3] = g.Q;
   e.out_bytes = (int64_t)g.N * g.K * g.P * g.Q * 4;
@@ -553,6 +577,7 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
     if (kind == 3) {
       te_ptr(e, src);
       e.in[0] = (uintptr_t)src;
+      e.in_bytes[0] = (int64_t)count_;
     }
     e.out = (uintptr_t)dst;
     e.out_bytes = (int64_t)count_;
@@ -622,6 +647,7 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
     te_ptr(e, src);
     te_i(e, (int64_t)count_);
     e.in[0] = (uintptr_t)src;
+    e.in_bytes[0] = (int64_t)count_;
     step(e, false);
     uintptr_t base;
     TensorRec *rec = reg_find(src, &base);
@@ -763,7 +789,7 @@ float *DNNActiveFunc(cudnnContext *, float *x, int64_t dimX[4], int32_t mode, fl
   const int act = mode == 0 ? ACT_SIGMOID : (mode == 1 ? ACT_RELU : (mode == 2 ? ACT_TANH : ACT_IDENTITY));
   Entry e = trace_entry(S_ACTIVE);
   te_ptr(e, x); te_ptr(e, y); te_dims(e, dimX, 4); te_i(e, mode);
-  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = n * 4;
+  e.in[0] = (uintptr_t)x; e.in_bytes[0] = n * 4; e.out = (uintptr_t)y; e.out_bytes = n * 4;
   for (int i = 0; i < 4; ++i) e.dims[i] = dimX[i];
   e.kind = mode == 1 ? CK_RELU : CK_NONE;
   const Role role = step(e, false);
@@ -796,7 +822,7 @@ float *CUDAClipFunc(float *x, float *y, int64_t *dimOut, float lo, float hi, int
   const int64_t n = prod(dimOut, rank);
   Entry e = trace_entry(S_CLIP);
   te_ptr(e, x); te_ptr(e, y); te_dims(e, dimOut, (int)rank); te_f(e, lo); te_f(e, hi);
-  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = n * 4;
+  e.in[0] = (uintptr_t)x; e.in_bytes[0] = n * 4; e.out = (uintptr_t)y; e.out_bytes = n * 4;
   for (int i = 0; i < 4 && i < rank; ++i) e.dims[i] = dimOut[i];
   e.kind = rank == 4 ? CK_CLIP : CK_NONE;
   const Role role = step(e, false);
@@ -848,6 +874,8 @@ float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, 
   if (rank_ok) { te_dims(e, dimA, rankA); te_dims(e, dB, rankA); }
   e.in[0] = (uintptr_t)A; e.in[1] = opMode == 4 ? 0 : (uintptr_t)B; e.out = (uintptr_t)out;
   e.out_bytes = rank_ok ? prod(dimA, rankA) * 4 : 0;
+  e.in_bytes[0] = e.out_bytes;
+  e.in_bytes[1] = rank_ok ? prod(dB, rankA) * 4 : 0;
   for (int i = 0; i < 4 && i < rankA; ++i) e.dims[i] = dimA[i];
   if (opMode == 0 && bias == 1.0f) e.kind = bias_shape ? CK_BIAS_ADD : (same ? CK_SAME_ADD : CK_NONE);
   const Role role = step(e, false);
@@ -864,6 +892,7 @@ float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, 
       const float *bd = resident_f32(B, (size_t)g.K * 4);
       if (g_pending.depthwise) g_pending.bias = bd;
       else g_pending.a.bias = bd;
+      job_track_bias(g_pending, bd, B, g.K);
       if (!g_pack_was_resident) g_pending.a.consts_ready = 0;
       g_pending.bias_set = true;
       pending_retarget(out);
@@ -922,7 +951,8 @@ static float *pool_common(int sym, float *x, int64_t *dI, float *y, int64_t *dO,
   Entry e = trace_entry(sym);
   te_ptr(e, x); te_ptr(e, y); te_dims(e, dI, 4); te_dims(e, dO, 4); te_dims(e, kernel, 2);
   te_dims(e, padding, 4); te_dims(e, stride, 2);
-  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = numel4(dO) * 4;
+  e.in[0] = (uintptr_t)x; e.in_bytes[0] = numel4(dI) * 4; e.out = (uintptr_t)y;
+  e.out_bytes = numel4(dO) * 4;
   if (!avg && kernel[0] == 3 && kernel[1] == 3 && stride[0] == 2 && stride[1] == 2 && ph == 1 &&
       pw == 1 && padding[1] == 1 && padding[3] == 1)
     e.kind = CK_POOL_3S2;
@@ -991,6 +1021,7 @@ float *DNNReduceFunc(cudnnContext *, int32_t rank, float *x, int64_t *dimIn, flo
   if (rank <= 8 && rank > 0) { te_dims(e, dimIn, rank); te_dims(e, dimOut, rank); }
   e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y;
   e.out_bytes = rank <= 8 && rank > 0 ? prod(dimOut, rank) * 4 : 0;
+  e.in_bytes[0] = rank <= 8 && rank > 0 ? prod(dimIn, rank) * 4 : 0;
   step(e, false);
   if (mode != 5 || rank > 8) {
     set_error(995, "reduce: only mode 5 (mean) is implemented");
@@ -1023,6 +1054,8 @@ float *CUBLASMatmul2dFunc(int64_t /*rank*/, float *A, int64_t dimA[2], float *B,
   te_f(e, alpha); te_f(e, beta); te_i(e, transA); te_i(e, transB);
   e.in[0] = (uintptr_t)A; e.in[1] = (uintptr_t)B; e.in[2] = beta != 0.0f ? (uintptr_t)out : 0;
   e.out = (uintptr_t)out; e.out_bytes = (int64_t)M * N * 4;
+  e.in_bytes[0] = dimA[0] * dimA[1] * 4; e.in_bytes[1] = dimB[0] * dimB[1] * 4;
+  e.in_bytes[2] = e.out_bytes;
   step(e, false);
   if (r.log) fprintf(stderr, "[occamy] matmul2d M%d N%d K%d tA%d tB%d\n", M, N, K, (int)transA, (int)transB);
   const bool out_zero = is_zero(out);
@@ -1070,6 +1103,7 @@ float *CUDASoftmaxFunc(float *x, int64_t *dimIn, float *y, int64_t * /*dimOut*/,
   Entry e = trace_entry(S_SOFTMAX);
   te_ptr(e, x); te_ptr(e, y); te_dims(e, dimIn, (int)rank); te_i(e, axis);
   e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = prod(dimIn, rank) * 4;
+  e.in_bytes[0] = e.out_bytes;
   step(e, false);
   ensure_f32(x);
   launch_softmax_f32(x, y, outer, dimIn[axis], inner, r.stream);
@@ -1082,7 +1116,7 @@ static float *copy_common(int sym, float *x, int64_t *dimIn, int64_t rank, float
   const int64_t n = prod(dimIn, rank);
   Entry e = trace_entry(sym);
   te_ptr(e, x); te_ptr(e, y); te_dims(e, dimIn, (int)rank);
-  e.in[0] = (uintptr_t)x; e.out = (uintptr_t)y; e.out_bytes = n * 4;
+  e.in[0] = (uintptr_t)x; e.in_bytes[0] = n * 4; e.out = (uintptr_t)y; e.out_bytes = n * 4;
   step(e, false);
   ensure_f32(x);
   OCC_CUDA(cudaMemcpyAsync(y, x, (size_t)n * 4, cudaMemcpyDeviceToDevice, r.stream));
@@ -1112,6 +1146,10 @@ int occamy_get_math_mode(void) { return (int)rt().mode; }
 
 int occamy_last_error(int clear) {
   Runtime &r = rt();
+  if (r.last_error == 0) {   // a watchdog report of the allocation-free entry point, if any
+    const int na = noalloc_poll_error(clear != 0);
+    if (na > 0) set_error(na, "kernel watchdog (occamy_conv_bias_act_noalloc)");
+  }
   const int e = r.last_error;
   if (clear) r.last_error = 0;
   return e;
@@ -1129,10 +1167,17 @@ int occamy_synchronize(void) {
       cudaMemset(r.dev_err, 0, sizeof(int));
     }
   }
+  const int na = noalloc_poll_error(true);
+  if (na > 0) set_error(na, "kernel watchdog (occamy_conv_bias_act_noalloc)");
   return (int)e;
 }
 
 cudaStream_t occamy_stream(void) { return rt().stream; }
+
+void occamy_selftest_bounded_wait(void) {
+  flush_pending();
+  launch_selftest_bounded_wait(rt().stream);
+}
 
 void occamy_get_counters(int64_t out[8]) {
   Runtime &r = rt();
@@ -1140,6 +1185,7 @@ void occamy_get_counters(int64_t out[8]) {
 }
 
 int64_t occamy_fused_chains(void) { return trace_fused_chains(); }
+void occamy_clear_weight_cache(void);
 
 void occamy_profile_begin(void) {
   Runtime &r = rt();
@@ -1165,6 +1211,11 @@ int occamy_profile_end(float *ms, int cap) {
 void occamy_set_cross_call_fusion(int on) {
   flush_pending();
   trace_set_enabled(on != 0);
+}
+
+void occamy_set_weight_cache(int on) {
+  if (!on) occamy_clear_weight_cache();
+  rt().cache_weights = on != 0;
 }
 
 void occamy_clear_weight_cache(void) {

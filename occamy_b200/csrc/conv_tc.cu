@@ -265,6 +265,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
   }
 }
 
+// ------------------------------------------------------------------ watchdog self-test
+// One thread waits, with the very wait every role of the kernels above uses, on an mbarrier
+// that nobody will ever arrive at.  The wait has to give up at its bound (about two seconds),
+// the kernel then reports code 1099 the way the convolution kernels report theirs and returns:
+// shows on a live GPU that a stuck pipeline ends in an error code, not in a hang.
+__global__ void tc_selftest_wait_kernel(int *err) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait_slow(smem_u32(&bar), 0, &abort_flag)) atomicExch(err, 1099);
+  }
+}
+
+void launch_selftest_bounded_wait(cudaStream_t s) {
+  tc_selftest_wait_kernel<<<1, 32, 0, s>>>(rt().dev_err);
+  count(CNT_LAUNCHES);
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
@@ -292,13 +313,10 @@ static CUtensorMapSwizzle swizzle_for(int row_bytes) {
 }
 
 // bf16 tensor map of rank `rank` (<= 4): dims/box innermost first, strides in bytes for
-// dims 1..rank-1.
-// Off only while a plan is built for the allocation-free entry point, which must not touch
-// the lazily initialised runtime state.
-static bool g_count_encodes = true;
-
+// dims 1..rank-1.  `counted` is false only while a plan is built for the allocation-free
+// entry point, which must not touch the lazily initialised runtime state.
 static bool make_map(CUtensorMap *m, const void *ptr, int rank, const uint64_t *dims,
-                     const uint64_t *strides, const uint32_t *box, int row_bytes) {
+                     const uint64_t *strides, const uint32_t *box, int row_bytes, bool counted) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gd[4], gs[3];
@@ -312,7 +330,7 @@ static bool make_map(CUtensorMap *m, const void *ptr, int rank, const uint64_t *
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(ptr),
                   gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(row_bytes),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (g_count_encodes) count(CNT_TMAP_ENCODES);
+  if (counted) count(CNT_TMAP_ENCODES);
   if (r != CUDA_SUCCESS) {
     set_error(2000 + (int)r, "cuTensorMapEncodeTiled");
     return false;
@@ -352,10 +370,12 @@ static int pick_bk(int Cf) { return Cf % 64 == 0 ? 64 : (Cf % 32 == 0 ? 32 : (Cf
 // busier per instruction, but when a layer has few pixels they leave SMs idle; pick the
 // width with the lowest modelled time: waves x (k-steps x cost per k-step + epilogue slabs).
 static int pick_bn(int K, long sp_tiles, int ksteps, int num_sms) {
-  if (const char *f = getenv("OCCAMY_TC_BN")) {   // tuning aid: force the tile width
+#ifdef OCCAMY_TUNING   // sweep builds only: force the tile width from the environment
+  if (const char *f = getenv("OCCAMY_TC_BN")) {
     const int v = atoi(f);
     if (v == 32 || v == 64 || v == 128 || v == 256) return v;
   }
+#endif
   const int cand[4] = {256, 128, 64, 32};
   const double kcost[4] = {900.0, 780.0, 715.0, 700.0};  // cycles per 64-deep k-step
   int widest = 32;
@@ -428,7 +448,8 @@ static TcFastDiv make_fastdiv(int d) {
 
 static int floordiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 
-static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool allow_halo = true) {
+static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool counted,
+                       bool allow_halo = true) {
   Plan pl;
   memset(&pl, 0, sizeof(pl));
   TcParams &p = pl.p;
@@ -458,12 +479,16 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
   p.gq = Qg;
   p.gp = Pg;
   p.gn = Ng;
+#ifdef OCCAMY_TUNING
   static const bool pn_allowed = !(getenv("OCCAMY_TC_PIXEL_N") && !strcmp(getenv("OCCAMY_TC_PIXEL_N"), "0"));
+  static const bool halo_allowed = !(getenv("OCCAMY_TC_HALO") && !strcmp(getenv("OCCAMY_TC_HALO"), "0"));
+#else
+  constexpr bool pn_allowed = true, halo_allowed = true;
+#endif
   // worth it only where the tensor pipe is the limit: the transposing epilogue is slower
   // than the plain one, which hurts the HBM-bound 1x1 layers
   // 3x3 / stride 1 / pad 1 with 64 -> 64 channels and rows of at most 126 pixels: the input
   // block of a tile is loaded once and the taps are windows of it (TC_MODE_HALO)
-  static const bool halo_allowed = !(getenv("OCCAMY_TC_HALO") && !strcmp(getenv("OCCAMY_TC_HALO"), "0"));
   const bool halo = allow_halo && halo_allowed && !a.out_f32 && a.R == 3 && a.S == 3 &&
                     a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 1 && a.pad_w == 1 &&
                     a.Cf == 64 && a.K == 64 && a.W + 2 <= 128 && a.w_step == 0 && a.Q == a.W &&
@@ -504,12 +529,12 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
     const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)a.W, (uint64_t)a.H, (uint64_t)a.N};
     const uint64_t st[3] = {(uint64_t)a.Cf * 2, (uint64_t)a.W * a.Cf * 2, (uint64_t)a.H * a.W * a.Cf * 2};
     const uint32_t box[4] = {64u, (uint32_t)p.tw, (uint32_t)(p.th + 2), 1u};
-    ok &= make_map(&p.tmA[0], a.x, 4, dims, st, box, 128);
+    ok &= make_map(&p.tmA[0], a.x, 4, dims, st, box, 128, counted);
     p.num_taps = 9;
   } else if (flat) {
     const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)Qg, 1, 1};
     const uint64_t st[3] = {(uint64_t)a.Cf * 2, (uint64_t)Qg * a.Cf * 2, (uint64_t)Qg * a.Cf * 2};
-    ok &= make_map(&p.tmA[0], a.x, 4, dims, st, boxA, bk * 2);
+    ok &= make_map(&p.tmA[0], a.x, 4, dims, st, boxA, bk * 2, counted);
     p.num_taps = 1;
     p.taps[0] = TcTap{0, 0, 0};
   } else {
@@ -534,7 +559,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
                                     (uint64_t)(Hm > 0 ? Hm : 1), (uint64_t)a.N};
           const uint64_t st[3] = {(uint64_t)(sw * px * 2), (uint64_t)(sh * rowe * 2),
                                   (uint64_t)(a.H * rowe * 2)};
-          ok &= make_map(&p.tmA[nmaps], ptr, 4, dims, st, boxA, bk * 2);
+          ok &= make_map(&p.tmA[nmaps], ptr, 4, dims, st, boxA, bk * 2, counted);
           map_of[bh][bw] = nmaps++;
         }
         p.taps[p.num_taps++] = TcTap{map_of[bh][bw], aw, ah};
@@ -544,14 +569,16 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
     const uint64_t dims[3] = {(uint64_t)a.Cf, (uint64_t)a.K, (uint64_t)(a.R * a.S)};
     const uint64_t st[2] = {(uint64_t)a.Cf * 2, (uint64_t)a.K * a.Cf * 2};
     const uint32_t box[3] = {(uint32_t)bk, (uint32_t)bn, 1};
-    ok &= make_map(&p.tmB, a.w, 3, dims, st, box, bk * 2);
+    ok &= make_map(&p.tmB, a.w, 3, dims, st, box, bk * 2, counted);
   }
   // For 256-wide tiles with a long reduction, 32-channel slabs free enough shared memory
   // for a fourth ring stage, which those layers need more than a cheap epilogue.
   const int ksteps64 = (a.R * a.S * a.Cf + 63) / 64;
   int dc = pn ? 64 : (bn < 64 ? bn : (bn == 256 && bk == 64 && ksteps64 >= 16 ? 32 : 64));
-  if (const char *f = getenv("OCCAMY_TC_DC"))   // tuning aid: slab width of the 256-wide tiles
+#ifdef OCCAMY_TUNING
+  if (const char *f = getenv("OCCAMY_TC_DC"))   // slab width of the 256-wide tiles
     if (!pn && bn == 256 && (atoi(f) == 32 || atoi(f) == 64)) dc = atoi(f);
+#endif
   pl.dc = dc;
   pl.mode = a.out_f32 ? (TC_MODE_F32 | TC_MODE_CLAMP)
                       : ((a.residual ? TC_MODE_RES : 0) | (a.act == ACT_RELU ? 0 : TC_MODE_CLAMP) |
@@ -560,8 +587,8 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
     const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
     const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};
     const uint32_t box[4] = {(uint32_t)dc, (uint32_t)p.tw, (uint32_t)p.th, (uint32_t)p.tn};
-    ok &= make_map(&p.tmD, a.y, 4, dims, st, box, dc * 2);
-    if (a.residual) ok &= make_map(&p.tmR, a.residual, 4, dims, st, box, dc * 2);
+    ok &= make_map(&p.tmD, a.y, 4, dims, st, box, dc * 2, counted);
+    if (a.residual) ok &= make_map(&p.tmR, a.residual, 4, dims, st, box, dc * 2, counted);
   }
   // shared memory: ring + output slabs + bias + barriers + alignment
   const size_t stage_bytes = pn     ? (size_t)(128 + 256) * bk * 2
@@ -579,7 +606,9 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
     // slab is consumed faster than the fetch takes: whatever shared memory three ring stages
     // leave goes to slab buffers.
     int min_stages = 3;
-    if (const char *f = getenv("OCCAMY_TC_RES_STAGES")) min_stages = atoi(f) > 1 ? atoi(f) : min_stages;  // tuning aid
+#ifdef OCCAMY_TUNING
+    if (const char *f = getenv("OCCAMY_TC_RES_STAGES")) min_stages = atoi(f) > 1 ? atoi(f) : min_stages;
+#endif
     dbuf = (int)((TC_SMEM_LIMIT - fixed0 - min_stages * stage_bytes) / slab_bytes);
     if (dbuf > 8) dbuf = 8;
     if (dbuf < 3) dbuf = 3;
@@ -594,22 +623,22 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool all
   p.dbuf = dbuf;
   pl.smem = fixed + stages * stage_bytes;
   if (pl.smem < 120 * 1024) pl.smem = 120 * 1024;  // keep one CTA per SM (TMEM is per SM)
+#ifdef OCCAMY_TUNING
   if (getenv("OCCAMY_TC_PLAN_LOG"))
     fprintf(stderr, "[tcplan] K %d Cf %d RS %d px %dx%dx%d box %dx%dx%d bn %d dc %d pn %d bk %d stages %d dbuf %d tiles %d smem %zu\n",
             a.K, a.Cf, a.R * a.S, Qg, Pg, Ng, p.tw, p.th, p.tn, bn, dc, (int)pn, bk, stages, dbuf,
             p.total_tiles, pl.smem);
-  if (halo && !ok) return build_plan(a, err_word, num_sms, false);   // e.g. the block map was refused
+#endif
+  if (halo && !ok) return build_plan(a, err_word, num_sms, counted, false);   // e.g. the block map was refused
   pl.ok = ok;
   return pl;
 }
 
 static void launch_plan_pn(const Plan &pl, int num_sms, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    OCC_CUDA(cudaFuncSetAttribute(tc_conv_pn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  TC_SMEM_LIMIT));
-    attr_set = true;
-  }
+  static unsigned char attr_done[TC_MAX_DEVICES] = {};
+  if (tc_first_use_on_device(attr_done))
+    cudaFuncSetAttribute(tc_conv_pn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         TC_SMEM_LIMIT);
   int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
   tc_launch_pdl(tc_conv_pn_kernel, grid, TC_THREADS, pl.smem, s, pl.p);
 }
@@ -641,7 +670,7 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
   auto it = plans.find(key);
   if (it == plans.end()) {
     if (plans.size() > 4096) plans.clear();
-    it = plans.emplace(key, build_plan(a, rt().dev_err, rt().num_sms)).first;
+    it = plans.emplace(key, build_plan(a, rt().dev_err, rt().num_sms, true)).first;
   }
   const Plan &pl = it->second;
   if (!pl.ok) {
@@ -671,9 +700,7 @@ void launch_tc_conv(const TcConvArgs &a, cudaStream_t s) {
 // rebuilt on every call, the kernel's error word and the SM count come from the caller.
 // Used by the entry point that must not allocate.
 bool launch_tc_conv_stateless(const TcConvArgs &a, int *err_word, int num_sms, cudaStream_t s) {
-  g_count_encodes = false;
-  const Plan pl = build_plan(a, err_word, num_sms);
-  g_count_encodes = true;
+  const Plan pl = build_plan(a, err_word, num_sms, false);
   if (!pl.ok) return false;
   if (pl.p.total_tiles == 0) return true;
   launch_any(pl, num_sms, s);

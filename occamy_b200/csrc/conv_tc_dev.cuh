@@ -218,22 +218,14 @@ __device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {
   float a, b;
   f2_unpack(v, a, b);
   uint32_t r;
-#ifdef OCCAMY_TC_EXP_TRUNC
-  r = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);
-#else
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
-#endif
   return r;
 }
 __device__ __forceinline__ uint32_t f2_to_bf16x2_relu(uint64_t v) {
   float a, b;
   f2_unpack(v, a, b);
   uint32_t r;
-#ifdef OCCAMY_TC_EXP_TRUNC
-  r = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);
-#else
   asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
-#endif
   return r;
 }
 __device__ __forceinline__ void tc_fence_before() {
@@ -875,16 +867,26 @@ inline void tc_launch_pdl(Kernel kernel, int grid, int threads, size_t smem, cud
   cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
+// A function attribute (the dynamic shared memory limit) belongs to the current device.  Each
+// launcher keeps one flag array and asks this helper whether the attribute still has to be set
+// on the device the launch goes to.
+constexpr int TC_MAX_DEVICES = 64;
+inline bool tc_first_use_on_device(unsigned char (&done)[TC_MAX_DEVICES]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= TC_MAX_DEVICES) return true;
+  if (done[dev]) return false;
+  done[dev] = 1;
+  return true;
+}
+
 // Body shared by the launchers: picks the instantiation for `mode`, raises its dynamic
-// shared memory limit once, launches.
+// shared memory limit once per device, launches.
 template <int BN, int DC, int MODE>
 inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  static unsigned char attr_done[TC_MAX_DEVICES] = {};
+  if (tc_first_use_on_device(attr_done))
     cudaFuncSetAttribute(tc_conv_kernel<BN, DC, TC_EW, MODE>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
-    attr_set = true;
-  }
   tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32 * TC_NSTORE + 32, smem,
                 s, p);
 }

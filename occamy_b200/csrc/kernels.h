@@ -119,6 +119,9 @@ void launch_pack_stem_bf16(const float *w, bf16 *out, int C, int R, int S, int C
                            cudaStream_t s);
 bool launch_stem_pool(const StemPoolArgs &a, int *err_word, int num_sms, cudaStream_t s);
 
+// Enqueues a one-thread kernel whose bounded mbarrier wait must run out (see conv_tc.cu).
+void launch_selftest_bounded_wait(cudaStream_t s);
+
 // Returns false when the shape is outside what the kernel supports (caller falls back).
 bool tc_conv_supported(const TcConvArgs &a);
 void launch_tc_conv(const TcConvArgs &a, cudaStream_t s);

@@ -713,14 +713,16 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
       uint16_t hbits;
       memcpy(&hbits, &hb, 2);
       const uint32_t act_hi2 = (uint32_t)hbits * 0x10001u;
-      static bool attr_set = false;
-      if (!attr_set) {
+      static unsigned char attr_done[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev >= 0 && dev < 64 && !attr_done[dev]) {   // function attributes are per device
+        attr_done[dev] = 1;
         const int lim = 100 * 1024;
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        attr_set = true;
       }
       auto go = [&](auto kern) {
         kern<<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint32_t *)y, g, G, cols, TH, tiles_q,

@@ -235,14 +235,16 @@ T *plain_copy(T *in, const int64_t *dimIn, int64_t rank, T *out) {
   return out;
 }
 
-// Batched row-major matmul; B's batch index wraps (broadcast of leading dimensions).
+// Batched row-major matmul.  An operand with fewer leading (batch) dimensions than the output
+// is indexed by the trailing batch indices only, i.e. its batch index wraps - the broadcast
+// rule of the reference kernel (cuda/CUDAMatmulNdFunc.cu:49-58).
 __global__ void matmul_nd_kernel(const float *A, const float *B, float *out, int M, int N, int K,
-                                 int64_t batchB, int64_t total) {
+                                 int64_t batchA, int64_t batchB, int64_t total) {
   for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
        t += (int64_t)gridDim.x * blockDim.x) {
     const int n = (int)(t % N), m = (int)((t / N) % M);
     const int64_t b = t / ((int64_t)M * N);
-    const float *a = A + (b * M + m) * (int64_t)K;
+    const float *a = A + ((b % batchA) * M + m) * (int64_t)K;
     const float *bb = B + (b % batchB) * (int64_t)K * N + n;
     float acc = 0.0f;
     for (int k = 0; k < K; ++k) acc = fmaf(a[k], bb[(int64_t)k * N], acc);
@@ -320,13 +322,14 @@ float *CUDAMatmulNdFunc(float *A, int64_t *dimA, int32_t rankA, float *B, int64_
     return out;
   }
   const int M = (int)dimA[rankA - 2], K = (int)dimA[rankA - 1], N = (int)dimB[rankB - 1];
-  int64_t batchB = prod(dimB, rankB - 2);
+  int64_t batchA = prod(dimA, rankA - 2), batchB = prod(dimB, rankB - 2);
+  if (batchA < 1) batchA = 1;
   if (batchB < 1) batchB = 1;
   const int64_t total = prod(dimOut, rankOut);
   ensure_f32(A);
   ensure_f32(B);
   if (total) {
-    matmul_nd_kernel<<<blocks_for(total), 256, 0, r.stream>>>(A, B, out, M, N, K, batchB, total);
+    matmul_nd_kernel<<<blocks_for(total), 256, 0, r.stream>>>(A, B, out, M, N, K, batchA, batchB, total);
     count(CNT_LAUNCHES);
   }
   mark_f32(out);

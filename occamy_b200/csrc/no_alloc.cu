@@ -19,20 +19,31 @@
 //     or order them with events;
 //   * the first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress) and the SM count; make that first call outside any stream
-//     capture;
+//     capture.  That set-up is guarded (once per device, safe against two host threads making
+//     the first call together); the calls themselves share one array, so serialise them;
+//   * a kernel whose bounded waits ran out (codes 1001..1006) reports into a word kept in the
+//     last 256 bytes of the array.  A call never clears that word, so a report survives
+//     until occamy_noalloc_last_error() - or occamy_last_error() / occamy_synchronize() of the
+//     regular API - has read it; after such a report y holds garbage;
 //   * no cudaMalloc / cudaFree / allocating library call is made, by any call.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <climits>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "kernels.h"
+#include "runtime.h"
 
 #define OCCAMY_NOALLOC_SCRATCH_BYTES (32u << 20)
 #define OCCAMY_NOALLOC_MAX_DEVICES 16
+// The kernels' error word sits at a fixed place, the last 256 bytes of the array; the working
+// copies are carved out of the bytes before it.
+#define OCCAMY_NOALLOC_ERR_OFFSET (OCCAMY_NOALLOC_SCRATCH_BYTES - 256u)
 
 // File-scope device array.  In host code this name is only a handle for
 // cudaGetSymbolAddress; it is never passed to a kernel or used as an address.
@@ -43,11 +54,34 @@ namespace {
 using occ::bf16;
 
 struct DeviceSetup {
+  std::once_flag once;
   bool ready = false;
   unsigned char *scratch = nullptr;  // device address of g_noalloc_scratch on this device
   int num_sms = 0;
 };
 DeviceSetup g_setup[OCCAMY_NOALLOC_MAX_DEVICES];
+
+// Once per device, with that device current: ask the runtime where this device's copy of
+// the array lives.  The host-side symbol itself is not a device address.
+void setup_device(DeviceSetup &su, int dev) {
+  void *ptr = nullptr;
+  cudaError_t ce = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+  if (ce != cudaSuccess || !ptr) {
+    fprintf(stderr, "[occamy_b200] noalloc conv: cudaGetSymbolAddress failed (%s)\n",
+            cudaGetErrorString(ce));
+    return;
+  }
+  int sms = 0;
+  ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (ce != cudaSuccess || sms <= 0) {
+    fprintf(stderr, "[occamy_b200] noalloc conv: cannot read the SM count (%s)\n",
+            cudaGetErrorString(ce));
+    return;
+  }
+  su.scratch = static_cast<unsigned char *>(ptr);
+  su.num_sms = sms;
+  su.ready = true;
+}
 
 // fp32 NCHW -> bf16 NHWC, one thread per output element (c fastest: coalesced writes).
 __global__ void na_nchw_to_nhwc(const float *__restrict__ x, bf16 *__restrict__ y, int C, int HW,
@@ -107,41 +141,32 @@ extern "C" int occamy_conv_bias_act_noalloc(const float *x, const int64_t dimX[4
     return -1;
   }
   DeviceSetup &su = g_setup[dev];
-  if (!su.ready) {
-    // Once per device, with that device current: ask the runtime where this device's
-    // copy of the array lives.  The host-side symbol itself is not a device address.
-    void *ptr = nullptr;
-    ce = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    if (ce != cudaSuccess || !ptr) {
-      fprintf(stderr, "[occamy_b200] noalloc conv: cudaGetSymbolAddress failed (%s)\n",
-              cudaGetErrorString(ce));
-      return -1;
-    }
-    int sms = 0;
-    ce = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (ce != cudaSuccess || sms <= 0) {
-      fprintf(stderr, "[occamy_b200] noalloc conv: cannot read the SM count (%s)\n",
-              cudaGetErrorString(ce));
-      return -1;
-    }
-    su.scratch = static_cast<unsigned char *>(ptr);
-    su.num_sms = sms;
-    su.ready = true;
-  }
+  std::call_once(su.once, setup_device, std::ref(su), dev);
+  if (!su.ready) return -1;
 
+  // every extent is checked as a 64-bit value before it is narrowed
+  for (int i = 0; i < 4; ++i)
+    if (dimX[i] <= 0 || dimX[i] > INT_MAX || dimW[i] <= 0 || dimW[i] > INT_MAX) {
+      fprintf(stderr, "[occamy_b200] noalloc conv: extent out of range\n");
+      return -3;
+    }
+  for (int i = 0; i < 2; ++i)
+    if (pads[i] < 0 || pads[i] > 1024 || strides[i] < 1 || strides[i] > 1024) {
+      fprintf(stderr, "[occamy_b200] noalloc conv: pad / stride out of range\n");
+      return -3;
+    }
   const int N = (int)dimX[0], C = (int)dimX[1], H = (int)dimX[2], W = (int)dimX[3];
   const int K = (int)dimW[0], R = (int)dimW[2], S = (int)dimW[3];
   const int ph = (int)pads[0], pw = (int)pads[1], sh = (int)strides[0], sw = (int)strides[1];
-  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || K <= 0 || R <= 0 || S <= 0 || sh < 1 || sw < 1 ||
-      dimW[1] != C) {
+  if (dimW[1] != C) {
     fprintf(stderr, "[occamy_b200] noalloc conv: inconsistent shape\n");
     return -3;
   }
-  const int P = (H + 2 * ph - R) / sh + 1, Q = (W + 2 * pw - S) / sw + 1;
-  if (P <= 0 || Q <= 0) {
+  if ((int64_t)H + 2 * ph < R || (int64_t)W + 2 * pw < S) {   // the filter does not fit once
     fprintf(stderr, "[occamy_b200] noalloc conv: empty output\n");
     return -3;
   }
+  const int P = (H + 2 * ph - R) / sh + 1, Q = (W + 2 * pw - S) / sw + 1;
   int act;
   float lo = 0.f, hi = 0.f;
   if (activMode == 1) act = occ::ACT_RELU;
@@ -153,22 +178,22 @@ extern "C" int occamy_conv_bias_act_noalloc(const float *x, const int64_t dimX[4
     return -3;
   }
 
-  // carve the fixed array: [x as NHWC bf16][packed filter][y as NHWC bf16][error word]
+  // carve the fixed array: [x as NHWC bf16][packed filter][y as NHWC bf16] ... [error word]
   const size_t x_bytes = align_up((size_t)N * C * H * W * 2, 1024);
   const size_t w_bytes = align_up((size_t)R * S * K * C * 2, 1024);
   const size_t y_bytes = align_up((size_t)N * K * P * Q * 2, 1024);
-  const size_t need = x_bytes + w_bytes + y_bytes + 256;
-  if (need > OCCAMY_NOALLOC_SCRATCH_BYTES) {
+  const size_t need = x_bytes + w_bytes + y_bytes;
+  if (need > OCCAMY_NOALLOC_ERR_OFFSET) {
     fprintf(stderr,
             "[occamy_b200] noalloc conv: needs %zu bytes of scratch, the fixed array holds %u "
             "(use DNNConvBiasActivFunc, which allocates, for problems of this size)\n",
-            need, (unsigned)OCCAMY_NOALLOC_SCRATCH_BYTES);
+            need, (unsigned)OCCAMY_NOALLOC_ERR_OFFSET);
     return -2;
   }
   bf16 *xs = reinterpret_cast<bf16 *>(su.scratch);
   bf16 *ws = reinterpret_cast<bf16 *>(su.scratch + x_bytes);
   bf16 *ys = reinterpret_cast<bf16 *>(su.scratch + x_bytes + w_bytes);
-  int *err_word = reinterpret_cast<int *>(su.scratch + x_bytes + w_bytes + y_bytes);
+  int *err_word = reinterpret_cast<int *>(su.scratch + OCCAMY_NOALLOC_ERR_OFFSET);
 
   occ::TcConvArgs a;
   memset(&a, 0, sizeof(a));
@@ -182,10 +207,9 @@ extern "C" int occamy_conv_bias_act_noalloc(const float *x, const int64_t dimX[4
     return -3;
   }
 
-  // The array keeps whatever the previous call left: the error word must start at zero.
-  // Everything else is fully overwritten before it is read.
-  ce = cudaMemsetAsync(err_word, 0, sizeof(int), stream);
-  if (ce != cudaSuccess) return (int)ce;
+  // The array keeps whatever the previous call left.  The working copies are fully
+  // overwritten before they are read; the error word is zero from load time on and is
+  // deliberately NOT cleared here, so that a report of an earlier call is not lost.
   const int64_t xn = (int64_t)N * C * H * W, wn = (int64_t)R * S * K * C,
                 yn = (int64_t)N * K * P * Q;
   na_nchw_to_nhwc<<<blocks_for(xn, su.num_sms), 256, 0, stream>>>(x, xs, C, H * W, xn);
@@ -198,3 +222,27 @@ extern "C" int occamy_conv_bias_act_noalloc(const float *x, const int64_t dimX[4
   ce = cudaGetLastError();
   return ce == cudaSuccess ? 0 : (int)ce;
 }
+
+// Reads (and with `clear` resets) the error word of the current device's array: 0, or the
+// code 1001..1006 of a kernel whose bounded wait ran out in some earlier call.  A plain
+// blocking copy from the cached address: allocates nothing.  Synchronise the stream the calls
+// went to first; a device on which the entry point was never called reports 0.
+extern "C" int occamy_noalloc_last_error(int clear) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= OCCAMY_NOALLOC_MAX_DEVICES) return 0;
+  DeviceSetup &su = g_setup[dev];
+  if (!su.ready) return 0;
+  int word = 0;
+  if (cudaMemcpy(&word, su.scratch + OCCAMY_NOALLOC_ERR_OFFSET, sizeof(int),
+                 cudaMemcpyDeviceToHost) != cudaSuccess)
+    return -1;
+  if (word && clear) cudaMemset(su.scratch + OCCAMY_NOALLOC_ERR_OFFSET, 0, sizeof(int));
+  return word;
+}
+
+// Bytes of the fixed array that the working copies of one call may use.
+extern "C" int64_t occamy_noalloc_capacity(void) { return (int64_t)OCCAMY_NOALLOC_ERR_OFFSET; }
+
+namespace occ {
+int noalloc_poll_error(bool clear) { return occamy_noalloc_last_error(clear ? 1 : 0); }
+}  // namespace occ

@@ -180,15 +180,26 @@ void *scratch_get(int slot, size_t bytes) {
 }
 
 uint64_t host_hash(const void *src, size_t bytes) {
-  // FNV-1a over the first and last 512 bytes plus the length: cheap fingerprint used to
-  // notice when a host buffer that was taken for a constant has changed.
+  // Fingerprint used to notice that a host buffer taken for a constant has changed: FNV-1a
+  // over the length, the first and last 512 bytes, and 64-byte blocks spread evenly over the
+  // whole buffer (up to 256 of them), so that a change in the interior is seen too.  A few
+  // tens of kilobytes are read whatever the size of the constant.
   const unsigned char *b = (const unsigned char *)src;
   uint64_t h = 1469598103934665603ull ^ bytes;
+  auto mix = [&](size_t lo, size_t hi) {
+    for (size_t i = lo; i < hi; ++i) h = (h ^ b[i]) * 1099511628211ull;
+  };
   const size_t head = bytes < 512 ? bytes : 512;
-  for (size_t i = 0; i < head; ++i) h = (h ^ b[i]) * 1099511628211ull;
-  if (bytes > 512) {
-    const size_t tail0 = bytes - 512 > head ? bytes - 512 : head;
-    for (size_t i = tail0; i < bytes; ++i) h = (h ^ b[i]) * 1099511628211ull;
+  mix(0, head);
+  if (bytes > 512) mix(bytes - 512 > head ? bytes - 512 : head, bytes);
+  if (bytes > 1024) {
+    const size_t inner = bytes - 1024;
+    const size_t blocks = inner / 64 < 256 ? inner / 64 : 256;
+    for (size_t k = 0; k < blocks; ++k) {
+      // block k starts at an even share of the interior, rounded down to 8 bytes
+      const size_t at = 512 + ((inner - 64) * k / (blocks > 1 ? blocks - 1 : 1) & ~(size_t)7);
+      mix(at, at + 64);
+    }
   }
   return h;
 }

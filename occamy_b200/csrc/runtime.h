@@ -79,8 +79,8 @@ struct Runtime {
   std::unordered_map<WeightKey, PackedWeight, WeightKeyHash> wcache;
   // host sources whose packed form is resident: source -> (bytes, fingerprint)
   std::unordered_map<const void *, std::pair<size_t, uint64_t>> resident;
-  void *scratch[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-  size_t scratch_bytes[7] = {0, 0, 0, 0, 0, 0, 0};
+  void *scratch[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t scratch_bytes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   int *dev_err = nullptr;   // device word the kernels' bounded waits report into
   int *host_err = nullptr;  // pinned mirror
   bool log = false;
@@ -120,6 +120,9 @@ void mark_bf16(void *p, int64_t n, int64_t c, int64_t h, int64_t w);
 bool is_zero(const void *p);
 
 void *scratch_get(int slot, size_t bytes);
+// Error word of the allocation-free entry point on the current device (0 when it was never
+// used there); see no_alloc.cu.
+int noalloc_poll_error(bool clear);
 uint64_t host_hash(const void *src, size_t bytes);
 
 inline void count(Counter c, int64_t v = 1) { rt().counters[c] += v; }

@@ -496,12 +496,10 @@ bool launch_stem_pool(const StemPoolArgs &a, int *err_word, int num_sms, cudaStr
   const size_t smem = 1024 + w_bytes + (size_t)ST_NIN * p.slot_bytes + (size_t)ST_NCR * p.cr_bytes +
                       256 + 8 * 64;
   if (smem > (size_t)TC_SMEM_LIMIT || p.units == 0) return false;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static unsigned char attr_done[TC_MAX_DEVICES] = {};
+  if (tc_first_use_on_device(attr_done))
     cudaFuncSetAttribute(stem_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          TC_SMEM_LIMIT);
-    attr_set = true;
-  }
   const int grid = p.units < num_sms ? p.units : num_sms;
   Runtime &r = rt();
   int prof_slot = -1;

@@ -53,8 +53,8 @@ bool is_passive(int sym) {
 bool dies_unread(const std::vector<Entry> &rec, uintptr_t p, int64_t bytes, size_t from) {
   for (size_t t = from; t < rec.size(); ++t) {
     const Entry &e = rec[t];
-    for (int k = 0; k < 3; ++k)
-      if (e.in[k] && e.in[k] >= p && e.in[k] < p + (uintptr_t)bytes) return false;
+    for (int k = 0; k < 3; ++k)   // any overlap with an input counts as a read
+      if (e.in[k] && overlaps(e.in[k], e.in_bytes[k] > 0 ? e.in_bytes[k] : 1, p, bytes)) return false;
     if ((e.sym == S_MEMOFFSET || e.sym == S_MALLOC) && overlaps(e.out, e.out_bytes, p, bytes))
       return true;
     if ((e.sym == S_DEALLOC && e.out == p) || e.sym == S_POOLFREE) return true;

@@ -36,6 +36,7 @@ struct Entry {
   uint64_t sig = 1469598103934665603ull;
   int sym = 0;
   uintptr_t in[3] = {0, 0, 0};
+  int64_t in_bytes[3] = {0, 0, 0};   // fp32 extent of each input (0: unknown, taken as one byte)
   uintptr_t out = 0;
   int64_t out_bytes = 0;   // fp32 extent of `out` (range size for the memory calls)
   int64_t dims[4] = {0, 0, 0, 0};

@@ -79,10 +79,14 @@ _SIGNATURES = {
     "occamy_last_error": (C.c_int, [C.c_int]),
     "occamy_synchronize": (C.c_int, []),
     "occamy_stream": (C.c_void_p, []),
+    "occamy_selftest_bounded_wait": (None, []),
     "occamy_get_counters": (None, [_i64p]),
     "occamy_clear_weight_cache": (None, []),
+    "occamy_set_weight_cache": (None, [C.c_int]),
     "occamy_conv_bias_act_noalloc": (C.c_int, [_f32p, _i64p, _f32p, _i64p, _f32p, _i64p, _i64p,
                                                C.c_int64, _f32p, C.c_void_p]),
+    "occamy_noalloc_last_error": (C.c_int, [C.c_int]),
+    "occamy_noalloc_capacity": (C.c_int64, []),
     "occamy_fused_chains": (C.c_int64, []),
     "occamy_set_cross_call_fusion": (None, [C.c_int]),
     "occamy_profile_begin": (None, []),
@@ -94,7 +98,7 @@ for _r in (2, 3, 4, 6):
     _SIGNATURES[f"CUDATranspose{_r}DInt64Func"] = (C.c_void_p, [C.c_void_p, _i64p, C.c_void_p,
                                                                 _i64p, _i64p, C.c_int64])
 
-MATH_FP32, MATH_BF16 = 0, 1
+MATH_FP32, MATH_BF16, MATH_F16 = 0, 1, 2
 COUNTER_NAMES = ("launches", "h2d_bytes", "h2d_skipped_bytes", "pool_hwm_bytes", "tc_launches",
                  "materializations", "tmap_encodes", "simt_launches")
 

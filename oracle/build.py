@@ -48,9 +48,23 @@ def _wheel_dir(name: str):
         return None
 
 
-def build_reference_wrappers(reference_root: str = "/root/reference", force: bool = False):
+def reference_checkout():
+    """Where a checkout of corelab-src/occamy lies: the directory named by the environment
+    variable OCCAMY_REFERENCE_DIR, else a directory called `reference` beside this repository.
+    None when neither holds the wrappers' sources."""
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for cand in (os.environ.get("OCCAMY_REFERENCE_DIR"), os.path.join(os.path.dirname(here), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src", "Tools", "dnn-wrapper")):
+            return cand
+    return None
+
+
+def build_reference_wrappers(reference_root: str = None, force: bool = False):
     """Compile the reference runtime (cuDNN/cuBLASLt wrappers) unchanged. Returns
     the .so path, or None with a reason string when it cannot be built."""
+    reference_root = reference_root or reference_checkout()
+    if not reference_root:
+        return None, "reference checkout not present"
     wrap = os.path.join(reference_root, "src", "Tools", "dnn-wrapper")
     if not os.path.isdir(wrap):
         return None, "reference checkout not present"

@@ -126,3 +126,10 @@ def flatten(x: Dev):
     r = rt.lib().CUDAFlattenFunc(x.ptr, rt.dims(x.shape), y.ptr, rt.dims(y.shape), 1, len(x.shape))
     assert r == y.ptr
     return y
+
+
+def reshape(x: Dev, new_shape):
+    y = Dev(new_shape)
+    r = rt.lib().CUDAReshapeFunc(x.ptr, rt.dims(x.shape), len(x.shape), y.ptr)
+    assert r == y.ptr
+    return y

@@ -243,3 +243,208 @@ def test_pool_offsets_and_reuse():
     L.wrapDNNMemcpy(back.ctypes.data, p2, 4000, 2, None)
     assert not back.any()
     L.wrapDNNDealloc(base)
+
+
+# (input shape, kernel, pads, strides): every window form the bf16 NHWC pooling kernels have --
+# the compile-time 2x2 and 3x3 windows at strides 1 and 2, and the general loop (7x7, 1x1)
+POOL16_CASES = [((2, 16, 12, 12), (2, 2), (0, 0), (2, 2)), ((2, 16, 13, 11), (3, 3), (1, 1), (2, 2)),
+                ((1, 24, 9, 9), (3, 3), (1, 1), (1, 1)), ((2, 8, 7, 7), (7, 7), (0, 0), (1, 1)),
+                ((1, 32, 10, 8), (2, 2), (0, 0), (1, 1)), ((2, 8, 6, 6), (1, 1), (0, 0), (1, 1)),
+                ((1, 16, 9, 9), (5, 5), (2, 2), (2, 2))]
+
+
+@pytest.mark.parametrize("case", POOL16_CASES)
+@pytest.mark.parametrize("avg", [False, True])
+def test_pool_on_tensor_core_mode_activations(case, avg):
+    """Max and average pooling of a tensor that sits in the tensor-core mode's 16-bit NHWC
+    format: the input is produced on the device by a 1x1 convolution, so the pool call takes
+    the NHWC kernels (the fp32 NCHW ones are covered by test_pool).  Average pooling counts
+    the padding in its divisor, like the reference's cuDNN descriptor
+    (cudnn/CUDNNAveragePoolFunc.cpp:43-60)."""
+    shape, k, p, s = case
+    N, Cc, H, W = shape
+    rt.set_math_mode(rt.MATH_BF16)
+    r = rng(70 + H)
+    x = r.uniform(-1, 1, shape).astype(np.float32)
+    w = he(r, Cc, Cc, 1, 1)
+    c0 = rt.counters()
+    t = A.conv(A.up(x), A.up(w))
+    y = A.pool(t, k, p, s, avg).numpy()
+    c1 = rt.counters()
+    assert c1["tc_launches"] - c0["tc_launches"] == 1      # the producer ran on the tensor cores
+    tw = ref.conv2d(x, w)
+    want = ref.pool2d(tw, k, p, s, avg=avg, count_include_pad=True)
+    assert y.shape == want.shape
+    assert max_rel_err(y, want) <= TOL[rt.MATH_BF16]
+    # against the pool of exactly what the device pooled: only the output rounding is left
+    t16 = t.numpy()
+    exact = ref.pool2d(t16, k, p, s, avg=avg, count_include_pad=True)
+    assert max_rel_err(y, exact) <= (4e-3 if avg else 0.0)
+
+
+def test_reshape_is_a_copy():
+    for mode in MODES:
+        rt.set_math_mode(mode)
+        x = rng(13).normal(0, 1, (2, 8, 3, 5)).astype(np.float32)
+        y = A.reshape(A.up(x), (2, 120)).numpy()
+        assert np.array_equal(y, x.reshape(2, 120))
+    # of a tensor-core mode tensor: NCHW order must come back (FC weights depend on it)
+    rt.set_math_mode(rt.MATH_BF16)
+    r = rng(14)
+    x = r.uniform(-1, 1, (2, 16, 4, 4)).astype(np.float32)
+    w = he(r, 16, 16, 1, 1)
+    t = A.conv(A.up(x), A.up(w))
+    want = t.numpy().reshape(2, 256)
+    assert np.array_equal(A.reshape(t, (2, 256)).numpy(), want)
+    assert np.array_equal(A.flatten(t).numpy(), want)
+
+
+def test_error_codes_for_bad_calls():
+    """Compute entry points have no error channel in the reference ABI (the output pointer is
+    returned whatever happened); here a bad call leaves a sticky code behind."""
+    L = rt.lib()
+    rt.set_math_mode(rt.MATH_BF16)
+    x, w = A.Dev((1, 16, 4, 4)), A.Dev((8, 12, 1, 1))       # filter channels != input channels
+    y = A.Dev((1, 8, 4, 4))
+    L.DNNConvFunc(A.handle(), x.ptr, rt.dims(x.shape), w.ptr, rt.dims(w.shape), None, 0, 1, 1,
+                  rt.dims((0, 0)), rt.dims((1, 1)), y.ptr)
+    assert rt.last_error(clear=True) == 997
+    a = A.Dev((2,) * 9)
+    L.DNNTensorOpFunc(A.handle(), 0, a.ptr, rt.dims((2,) * 9), 9, a.ptr, rt.dims((2,) * 9), 9, a.ptr,
+                      rt.dims((2,) * 9), 9, 1.0)
+    assert rt.last_error(clear=True) == 996
+    b = A.Dev((2, 3))
+    L.DNNTensorOpFunc(A.handle(), 7, b.ptr, rt.dims((2, 3)), 2, b.ptr, rt.dims((2, 3)), 2, b.ptr,
+                      rt.dims((2, 3)), 2, 1.0)               # op mode that does not exist
+    assert rt.last_error(clear=True) == 996
+    L.DNNReduceFunc(A.handle(), 2, b.ptr, rt.dims((2, 3)), b.ptr, rt.dims((2, 1)), 3)   # not the mean
+    assert rt.last_error(clear=True) == 995
+
+
+def test_reading_a_tensor_that_fusion_skipped_is_reported():
+    """conv -> ReLU into a second tensor, twice: the second inference runs them as one kernel
+    and never writes the convolution's own output.  A third inference that follows the same
+    calls and then reads that output leaves the recorded sequence: the read is error 990."""
+    import ctypes as C
+    L = rt.lib()
+    rt.set_math_mode(rt.MATH_BF16)
+    r = rng(15)
+    x = r.uniform(-1, 1, (1, 16, 6, 6)).astype(np.float32)
+    w = he(r, 16, 16, 1, 1)
+    n = 16 * 36 * 4
+
+    def inference(read_conv_output):
+        h, base = C.c_void_p(), C.c_void_p()
+        L.cudnnCreate(C.byref(h))
+        L.wrapDNNMemPoolInit(C.byref(base), 1 << 16)
+        ptr = [C.c_void_p() for _ in range(4)]
+        for i, nbytes in enumerate((n, w.nbytes, n, n)):
+            L.wrapDNNMemOffset(C.byref(ptr[i]), base, i * 8192, nbytes)
+        px, pw, pc, pr = ptr
+        L.wrapDNNMemcpy(px, x.ctypes.data, n, 1, None)
+        L.wrapDNNMemcpy(pw, w.ctypes.data, w.nbytes, 1, None)
+        L.DNNConvFunc(h, px, rt.dims(x.shape), pw, rt.dims(w.shape), None, 0, 1, 1, rt.dims((0, 0)),
+                      rt.dims((1, 1)), pc)
+        L.DNNActiveFunc(h, pc, rt.dims(x.shape), 1, pr)
+        out = np.empty(x.shape, np.float32)
+        L.wrapDNNMemcpy(out.ctypes.data, pr, n, 2, None)
+        conv_out = None
+        if read_conv_output:
+            conv_out = np.empty(x.shape, np.float32)
+            L.wrapDNNMemcpy(conv_out.ctypes.data, pc, n, 2, None)
+        L.wrapDNNDealloc(base)
+        L.cudnnDestroy(h)
+        return out, conv_out
+
+    want = ref.conv2d(x, w, act=1)
+    y0, _ = inference(False)
+    chains = L.occamy_fused_chains()
+    y1, _ = inference(False)
+    assert L.occamy_fused_chains() == chains + 1
+    assert max_rel_err(y0, want) <= 2e-2 and max_rel_err(y1, want) <= 2e-2
+    assert rt.last_error(clear=True) == 0
+    y2, _ = inference(True)
+    assert max_rel_err(y2, want) <= 2e-2          # the fused result itself is fine
+    assert rt.last_error(clear=True) == 990       # ... the skipped tensor is not there to read
+    # that longer sequence is now a recorded program of its own: the convolution's output has a
+    # second reader, so it is written again and the same calls succeed
+    y3, c3 = inference(True)
+    assert rt.last_error(clear=True) == 0
+    assert max_rel_err(c3, ref.conv2d(x, w)) <= 2e-2 and max_rel_err(y3, want) <= 2e-2
+
+
+def test_watchdog_turns_a_stuck_wait_into_an_error_code():
+    """The kernels' waits are bounded: one that can never be satisfied ends after about two
+    seconds with a code in the error word, and the context keeps working."""
+    L = rt.lib()
+    L.occamy_selftest_bounded_wait()
+    rt.synchronize()
+    assert rt.last_error(clear=True) == 1099
+    # the stream and the context are still usable
+    rt.set_math_mode(rt.MATH_BF16)
+    r = rng(16)
+    x = r.uniform(-1, 1, (1, 16, 5, 5)).astype(np.float32)
+    w = he(r, 16, 16, 1, 1)
+    y = A.conv(A.up(x), A.up(w)).numpy()
+    assert max_rel_err(y, ref.conv2d(x, w)) <= 2e-2
+    assert rt.last_error(clear=True) == 0
+
+
+@pytest.mark.parametrize("bias_from", ["device_copy", "no_cache"])
+def test_held_back_conv_with_a_bias_that_is_freed_early(bias_from):
+    """conv -> in-place bias add -> (bias freed) -> ReLU, the order liveness-placed deallocs
+    give.  From the second inference on the convolution is held back and takes the add along;
+    when the bias has no resident copy (it was produced on the device, or the weight cache is
+    off) the kernel reads the caller's bias tensor, so freeing that tensor has to run the
+    held-back kernel first."""
+    import ctypes as C
+    L = rt.lib()
+    rt.set_math_mode(rt.MATH_BF16)
+    if bias_from == "no_cache":
+        L.occamy_set_weight_cache(0)
+    try:
+        r = rng(17)
+        x = r.uniform(-1, 1, (2, 32, 9, 9)).astype(np.float32)
+        w = he(r, 32, 32, 3, 3)
+        b = r.normal(0, 0.5, 32).astype(np.float32)
+        want = ref.conv2d(x, w, b, (1, 1), (1, 1), act=1)
+
+        def malloc(nbytes):
+            p = C.c_void_p()
+            L.wrapDNNMalloc(C.byref(p), nbytes)
+            return p
+
+        def inference():
+            h = C.c_void_p()
+            L.cudnnCreate(C.byref(h))
+            px, pw, pb0, pb1 = malloc(x.nbytes), malloc(w.nbytes), malloc(b.nbytes), malloc(b.nbytes)
+            pc, pr = malloc(x.nbytes), malloc(x.nbytes)
+            L.wrapDNNMemcpy(px, x.ctypes.data, x.nbytes, 1, None)
+            L.wrapDNNMemcpy(pw, w.ctypes.data, w.nbytes, 1, None)
+            L.wrapDNNMemcpy(pb0, b.ctypes.data, b.nbytes, 1, None)
+            bias = pb0
+            if bias_from == "device_copy":
+                L.wrapDNNMemcpy(pb1, pb0, b.nbytes, 3, None)
+                bias = pb1
+            L.DNNConvFunc(h, px, rt.dims(x.shape), pw, rt.dims(w.shape), None, 0, 1, 1,
+                          rt.dims((1, 1)), rt.dims((1, 1)), pc)
+            L.DNNTensorOpFunc(h, 0, pc, rt.dims(x.shape), 4, bias, rt.dims((1, 32, 1, 1)), 4, pc,
+                              rt.dims(x.shape), 4, 1.0)
+            L.wrapDNNDealloc(bias)                      # last use of the bias was the add
+            # the freed bytes are handed out again and overwritten at once
+            junk = malloc(b.nbytes)
+            L.wrapDNNMemcpy(junk, (np.full(32, 1e6, np.float32)).ctypes.data, b.nbytes, 1, None)
+            L.DNNActiveFunc(h, pc, rt.dims(x.shape), 1, pr)
+            out = np.empty(x.shape, np.float32)
+            L.wrapDNNMemcpy(out.ctypes.data, pr, out.nbytes, 2, None)
+            for p in (px, pw, pc, pr, junk, pb1 if bias is pb0 else pb0):
+                L.wrapDNNDealloc(p)
+            L.cudnnDestroy(h)
+            return out
+
+        for i in range(3):
+            y = inference()
+            assert max_rel_err(y, want) <= 2e-2, i
+            assert rt.last_error(clear=True) == 0
+    finally:
+        L.occamy_set_weight_cache(1)

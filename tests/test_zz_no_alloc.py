@@ -12,6 +12,7 @@ import numpy as np
 import pytest
 
 from occamy_b200 import runtime as rt
+from oracle import ref
 
 pytestmark = pytest.mark.gpu
 
@@ -68,7 +69,40 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row(native_libs):
         # same kernel, same operands: the tolerance of the bf16 tests is far from needed
         assert np.abs(y_new - y_ref).max() <= 2e-2 * scale
         assert np.array_equal(y_new, y_ref)
+        # and against the CPU oracle, within the tensor-core mode's bound
+        want = ref.conv2d(x, w, b, (pad, pad), (stride, stride), act=act)
+        assert np.abs(y_new - want).max() <= 2e-2 * np.abs(want).max()
+    assert rt.lib().occamy_noalloc_last_error(0) == 0
     assert rt.last_error(clear=True) == 0
+
+
+def test_noalloc_leaves_free_device_memory_unchanged(native_libs):
+    """The point of the entry point: a call takes no device memory.  The first call on a device
+    is left out of the comparison (the driver loads the kernels' code then); from the second
+    call on, free memory as the driver reports it is the same before and after."""
+    torch = pytest.importorskip("torch")
+    L = rt.lib()
+    r = np.random.Generator(np.random.PCG64(78))
+    x = torch.from_numpy(r.uniform(-1, 1, (2, 64, 28, 28)).astype(np.float32)).cuda()
+    w = torch.from_numpy(r.normal(0, 0.05, (128, 64, 3, 3)).astype(np.float32)).cuda()
+    b = torch.zeros(128, device="cuda")
+    y = torch.empty((2, 128, 28, 28), device="cuda")
+
+    def call():
+        rc = L.occamy_conv_bias_act_noalloc(x.data_ptr(), rt.dims(x.shape), w.data_ptr(),
+                                            rt.dims(w.shape), b.data_ptr(), rt.dims((1, 1)),
+                                            rt.dims((1, 1)), 1, y.data_ptr(), None)
+        torch.cuda.synchronize()
+        return rc
+
+    assert call() == 0
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert call() == 0
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0
+    assert L.occamy_noalloc_last_error(1) == 0
+    assert 0 < L.occamy_noalloc_capacity() < 32 << 20
 
 
 def test_noalloc_rejects_what_does_not_fit(native_libs):
@@ -85,4 +119,12 @@ def test_noalloc_rejects_what_does_not_fit(native_libs):
                                         rt.dims((8, 20, 3, 3)), d.data_ptr(), rt.dims((1, 1)),
                                         rt.dims((1, 1)), 1, d.data_ptr(), None)
     assert rc == -3
+    # extents beyond INT_MAX, a negative pad, a filter larger than the padded image
+    for dx, dw, pads in ((((1 << 33), 16, 8, 8), (16, 16, 3, 3), (1, 1)),
+                         ((1, 16, 8, 8), (16, 16, 3, 3), (-1, 0)),
+                         ((1, 16, 2, 2), (16, 16, 5, 5), (1, 1))):
+        rc = L.occamy_conv_bias_act_noalloc(d.data_ptr(), rt.dims(dx), d.data_ptr(), rt.dims(dw),
+                                            d.data_ptr(), rt.dims(pads), rt.dims((2, 2)), 1,
+                                            d.data_ptr(), None)
+        assert rc == -3, (dx, dw, pads)
     torch.cuda.synchronize()
