@@ -30,7 +30,6 @@ sys.path.insert(0, ROOT)
 import numpy as np  # noqa: E402
 
 GLOBAL_BATCH = 256
-METRIC = "images/sec ResNet-50 b=256"
 
 
 def measured_peaks():
@@ -98,12 +97,12 @@ class ClockSampler:
         return out
 
 
-def cpu_baseline_sample(batch: int, repeats: int):
+def cpu_baseline_sample(batch: int, repeats: int, graph: str = "resnet50"):
     """Times the CPU restatement (oracle port) of the same graph on the host cores."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from helpers import run_graph_oracle
     from occamy_b200 import graphs
-    g = graphs.resnet50(batch=batch, seed=0, variant="v1", softmax=True)
+    g = getattr(graphs, graph)(batch=batch, seed=0)
     x = graphs.make_input(g, 0)
     run_graph_oracle(g, x)  # warm-up (page in the library, OpenMP pool)
     t0 = time.perf_counter()
@@ -122,24 +121,25 @@ def run_reference_arm(args):
         return
     sample_batch = 2
     cores = os.cpu_count() or 1
+    metric = GRAPH_DEFAULTS[args.graph][1]
     for _ in range(max(args.warmup, 1)):
-        cpu_baseline_sample(sample_batch, 1)
+        cpu_baseline_sample(sample_batch, 1, args.graph)
     times = []
     for _ in range(args.steps):
-        _, dt = cpu_baseline_sample(sample_batch, 1)
+        _, dt = cpu_baseline_sample(sample_batch, 1, args.graph)
         times.append(dt)
     ms = 1000.0 * sum(times) / len(times)
     value = sample_batch / (ms / 1000.0)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "images/s",
+        "impl": "reference", "metric": metric, "value": value, "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "ResNet-50 v1 inference, global batch 256 (N(0,1) images, "
-                               "He-normal weights)", "global_batch": GLOBAL_BATCH},
+        "config": workload_config(args.graph, args.batch, int(os.environ.get("WORLD_SIZE", "1")),
+                                  args.fuse),
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port",
-                         "sample": f"{sample_batch} images per step of the batch-256 workload, "
-                                   "fp32 C restatement with OpenMP"},
+                         "sample": f"{sample_batch} images per step of the batch-{args.batch} "
+                                   "workload, fp32 C restatement with OpenMP"},
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -173,7 +173,8 @@ def run_incumbent_arm(args):
         prog.run_raw(binding, x.data_ptr(), 1, [out.data_ptr()], 1)
     torch.cuda.synchronize()
     ms = 1000.0 * (time.perf_counter() - t0) / args.steps
-    print(json.dumps({"impl": "incumbent", "metric": METRIC, "value": args.batch / (ms / 1000.0),
+    print(json.dumps({"impl": "incumbent", "metric": GRAPH_DEFAULTS[args.graph][1],
+                      "value": args.batch / (ms / 1000.0),
                       "unit": "images/s", "n_gpus": 1, "steps": args.steps, "ms_per_step": ms,
                       "dtype": "f32 (cuDNN default math)", "data": "synthetic",
                       "config": {"workload": f"{g.name} batch {args.batch}, reference wrappers "
@@ -182,19 +183,118 @@ def run_incumbent_arm(args):
                                              "inference as the compiled model does"}}), flush=True)
 
 
+# graph -> (global batch of the configuration, metric name, arithmetic mode of the headline run)
+GRAPH_DEFAULTS = {
+    "resnet50": (256, "images/sec ResNet-50 b=256", "bf16"),
+    "mobilenet_v2": (128, "images/sec MobileNetV2 b=128", "fp16"),
+    "vgg16": (64, "images/sec VGG-16 b=64", "bf16"),
+}
+PARITY_TOL = {"fp32": 1e-4, "bf16": 2e-2, "fp16": 2e-2}
+GRAPH_NAMES = {"resnet50": "resnet50_v1", "mobilenet_v2": "mobilenet_v2", "vgg16": "vgg16"}
+
+
+def workload_config(graph, batch, world, fuse):
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": f"{GRAPH_NAMES[graph]} inference, global batch {batch} "
+                        f"({batch // world} per GPU), N(0,1) images, He-normal weights, "
+                        f"replayed fused call sequence (fuse={fuse})",
+            "global_batch": batch, "parallelism": f"dp{world}",
+            "l2": "per-step working set (activations > 1 GB) exceeds the 126 MB L2"}
+
+
+def torch_cpu_baseline(graph_name, batch, threads, seconds=4.0):
+    """Independent CPU number: the same graph evaluated by PyTorch's CPU kernels (oneDNN) with
+    `threads` threads; images/s over about `seconds` of work."""
+    import torch
+    import torch.nn.functional as F
+    from occamy_b200 import graphs
+    g = getattr(graphs, graph_name)(batch=batch, seed=0)
+    x = torch.from_numpy(graphs.make_input(g, 0))
+    consts = {k: torch.from_numpy(v) for k, v in g.consts.items()}
+    old = torch.get_num_threads()
+    torch.set_num_threads(threads)
+
+    def run():
+        vals = {0: x}
+        vals.update(consts)
+        for n in g.nodes:
+            a, i = n.attrs, [vals[v] if v != -1 else None for v in n.ins]
+            if n.op == "conv":
+                r = F.conv2d(i[0], i[1], i[2], a["strides"], a["pads"], 1, a["groups"])
+            elif n.op == "relu":
+                r = F.relu(i[0])
+            elif n.op == "clip":
+                r = i[0].clamp(a["lo"], a["hi"])
+            elif n.op == "add":
+                r = i[0] + i[1]
+            elif n.op == "maxpool":
+                r = F.max_pool2d(i[0], a["kernel"], a["strides"], a["pads"])
+            elif n.op == "avgpool":
+                r = F.avg_pool2d(i[0], a["kernel"], a["strides"], a["pads"])
+            elif n.op == "gap":
+                r = i[0].mean((2, 3), keepdim=True)
+            elif n.op == "flatten":
+                r = i[0].flatten(1)
+            elif n.op == "gemm":
+                r = F.linear(i[0], i[1], i[2])
+            elif n.op == "softmax":
+                r = F.softmax(i[0], a["axis"])
+            else:
+                raise ValueError(n.op)
+            vals[n.out] = r
+        return vals[g.outputs[0]]
+
+    with torch.no_grad():
+        run()
+        t0, reps = time.perf_counter(), 0
+        while time.perf_counter() - t0 < seconds:
+            run()
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+    torch.set_num_threads(old)
+    return batch / dt
+
+
+def incumbent_line(graph, batch, fuse, steps):
+    """The reference's own GPU runtime on this box, in a child process (it brings its own cuDNN
+    and cuBLASLt); None when oracle/_ref was not built."""
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "incumbent",
+                            "--graph", graph, "--batch", str(batch), "--fuse", str(fuse),
+                            "--steps", str(steps), "--warmup", "1"], capture_output=True, text=True,
+                           timeout=600)
+        for ln in reversed(r.stdout.splitlines()):
+            if ln.startswith("{"):
+                d = json.loads(ln)
+                return None if "unavailable" in d else d
+    except Exception:
+        pass
+    return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "incumbent"])
-    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch")
-    ap.add_argument("--math", default="bf16", choices=["bf16", "fp32"])
-    ap.add_argument("--graph", default="resnet50", choices=["resnet50", "mobilenet_v2", "vgg16"])
+    ap.add_argument("--graph", default="resnet50", choices=sorted(GRAPH_DEFAULTS))
+    ap.add_argument("--batch", type=int, default=0, help="global batch (default: the graph's configuration)")
+    ap.add_argument("--math", default="", choices=["", "bf16", "fp16", "fp32"])
     ap.add_argument("--fuse", type=int, default=1)
+    ap.add_argument("--warm-seconds", type=float, default=2.0,
+                    help="keep running warm-up steps until this much time has passed, so that the "
+                         "timed steps see the clocks and power state of a loaded GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the incumbent, PyTorch-CPU and memory-bound-kernel legs")
     ap.add_argument("--per-layer", default="", help="write a per-launch roofline table here")
     args = ap.parse_args()
+    cfg_batch, metric, cfg_math = GRAPH_DEFAULTS[args.graph]
+    if not args.batch:
+        args.batch = cfg_batch
+    if not args.math:
+        args.math = cfg_math
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -218,7 +318,8 @@ def main():
     lo_img, hi_img = sharding.shard_range(args.batch, rank, world)
     per_rank = hi_img - lo_img
 
-    rt.set_math_mode(rt.MATH_BF16 if args.math == "bf16" else rt.MATH_FP32)
+    math_mode = {"bf16": rt.MATH_BF16, "fp16": rt.MATH_F16, "fp32": rt.MATH_FP32}[args.math]
+    rt.set_math_mode(math_mode)
     builder = getattr(graphs, args.graph)
     g = builder(batch=per_rank, seed=0)
     prog = g.to_program()
@@ -228,8 +329,12 @@ def main():
 
     # rank r owns images [r*B/R, (r+1)*B/R) of the seeded global batch
     full = graphs.make_input(builder(batch=1, seed=0), 0).shape[1:]
-    rng = np.random.Generator(np.random.PCG64(1000003 + rank))
-    x_host = torch.from_numpy(rng.standard_normal((per_rank,) + tuple(full), dtype=np.float32)).pin_memory()
+
+    def rank_images(r, count):
+        rg = np.random.Generator(np.random.PCG64(1000003 + r))
+        return rg.standard_normal((per_rank,) + tuple(full), dtype=np.float32)[:count]
+
+    x_host = torch.from_numpy(rank_images(rank, per_rank)).pin_memory()
     x_dev = x_host.cuda(non_blocking=False)
     n_out = g.shapes[g.outputs[0]][1]
     out_dev = torch.empty((per_rank, n_out), dtype=torch.float32, device="cuda")
@@ -244,12 +349,27 @@ def main():
                 sharding.gather_logits(out_dev, gathered)
 
     def step_e2e():
+        """What a compiled model does per inference: host batch in through wrapDNNMemcpy kind 1,
+        result back through the blocking kind 2 copy; the call returns when the result is in host
+        memory (ONNXToDNNCommon.cpp:129-183).  With several ranks the gather sits between the
+        model's device result and the one copy to rank 0's host buffer, and the host waits for
+        it before the next step, just the same."""
+        if world == 1:
+            prog.run_raw(binding, x_host.data_ptr(), 1, [out_host.data_ptr()], 1)
+            return
         prog.run_raw(binding, x_host.data_ptr(), 1, [out_dev.data_ptr()], 3)
         with torch.cuda.stream(stream):
-            if world > 1:
-                src = sharding.gather_logits(out_dev, gathered)
-            else:
-                src = out_dev
+            src = sharding.gather_logits(out_dev, gathered)
+            if rank == 0:
+                out_host.copy_(src, non_blocking=True)
+        stream.synchronize()
+
+    def step_e2e_pipelined():
+        """The same copies without the host wait: a server that keeps several inferences in
+        flight overlaps step i+1's upload with step i's kernels."""
+        prog.run_raw(binding, x_host.data_ptr(), 1, [out_dev.data_ptr()], 3)
+        with torch.cuda.stream(stream):
+            src = sharding.gather_logits(out_dev, gathered) if world > 1 else out_dev
             if rank == 0:
                 out_host[: src.shape[0]].copy_(src, non_blocking=True)
 
@@ -276,29 +396,47 @@ def main():
             ms = float(t.item())
         return ms
 
-    # ---- warm-up (first call packs and caches the weights) ----
-    for _ in range(max(args.warmup, 3)):
+    # ---- warm-up: at least W steps (the first packs and caches the weights), then more until
+    # the GPU has been under load for --warm-seconds; the clock sampler covers all of it ----
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step_resident()
     torch.cuda.synchronize()
     if rt.last_error():
         raise SystemExit("runtime reported an error during warm-up")
-
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_end = time.perf_counter() + args.warm_seconds
+    more = 0
+    while True:
+        go = torch.tensor([1.0 if time.perf_counter() < t_end else 0.0], device="cuda")
+        if world > 1:
+            dist.all_reduce(go, op=dist.ReduceOp.MIN)     # every rank runs the same number
+        if go.item() < 0.5:
+            break
+        for _ in range(10):
+            step_resident()
+        torch.cuda.synchronize()
+        more += 10
+    warm += more
+
     c0 = rt.counters()
     ms_total = timed(step_resident, args.steps)
     c1 = rt.counters()
     for _ in range(3):
         step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
-    clocks = sampler.stop() if sampler else None
+    for _ in range(3):
+        step_e2e_pipelined()
+    ms_pipe = timed(step_e2e_pipelined, args.steps)
 
     # ---- dominant kernel: CUDA-event pair around every tensor-core launch ----
     rt.lib().occamy_profile_begin()
-    prof_steps = 3
+    prof_steps = 5
     for _ in range(prof_steps):
         step_resident()
-    buf = (C.c_float * 4096)()
-    n_prof = rt.lib().occamy_profile_end(buf, 4096)
+    buf = (C.c_float * 8192)()
+    n_prof = rt.lib().occamy_profile_end(buf, 8192)
+    clocks = sampler.stop() if sampler else None
     per_step = n_prof // prof_steps if prof_steps else 0
     tc_ms = [[buf[s * per_step + i] for s in range(prof_steps)] for i in range(per_step)]
     tc_ms = [statistics.median(v) for v in tc_ms]
@@ -307,13 +445,19 @@ def main():
     if err:
         raise SystemExit(f"runtime reported error {err}")
 
+    # ---- parity of what was timed: the logits of a few images against the CPU oracle ----
+    parity = None
+    if rank == 0:
+        parity = check_parity(args, g, builder, prog, binding, x_host, out_host, gathered, world,
+                              per_rank, rank_images, step_e2e)
+
     ms_step = ms_total / args.steps
     value = args.batch / (ms_step / 1000.0)
-    e2e_value = args.batch / (ms_e2e / args.steps / 1000.0)
     peaks = measured_peaks()
     flops = g.conv_flops()            # algorithmic conv + Gemm FLOPs of this rank's batch
     achieved = flops / (tc_total_ms / 1000.0) / 1e12 if tc_total_ms > 0 else 0.0
-    peak = peaks["bf16_tflops_sustained"]
+    # The denominator is the burst figure: each launch is timed alone between two events.
+    peak = peaks["bf16_tflops"]
 
     if args.per_layer and rank == 0:
         write_per_layer(args.per_layer, g, tc_ms, peaks, ms_step)
@@ -323,41 +467,124 @@ def main():
             dist.destroy_process_group()
         return
 
+    def per_s(ms):
+        return args.batch / (ms / args.steps / 1000.0)
+
     line = {
-        "metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "metric": metric, "value": value, "unit": "images/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warm, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16" if args.math == "bf16" else "f32", "data": "synthetic",
-        "config": {"workload": f"{g.name} inference, global batch {args.batch} "
-                               f"({per_rank} per GPU), N(0,1) images, He-normal weights, "
-                               f"replayed fused call sequence (fuse={args.fuse})",
-                   "global_batch": args.batch, "parallelism": f"dp{world}",
-                   "l2": "per-step working set (activations > 1 GB) exceeds the 126 MB L2"},
-        "e2e": {"value": e2e_value, "unit": "images/s",
+        "dtype": {"bf16": "bf16", "fp16": "f16", "fp32": "f32"}[args.math], "data": "synthetic",
+        "config": workload_config(args.graph, args.batch, world, args.fuse),
+        "warm_seconds": args.warm_seconds,
+        "e2e": {"value": per_s(ms_e2e), "unit": "images/s",
                 "h2d_bytes_per_step": int(x_host.numel() * 4 * world),
-                "d2h_bytes_per_step": int(args.batch * n_out * 4)},
+                "d2h_bytes_per_step": int(args.batch * n_out * 4),
+                "how": "host batch in (wrapDNNMemcpy kind 1), blocking copy of the result to the "
+                       "host (kind 2) every inference: the reference's own call sequence"},
+        "e2e_pipelined": {"value": per_s(ms_pipe), "unit": "images/s",
+                          "how": "same copies, no host wait between inferences"},
         "gpu_launches": int(c1["launches"] - c0["launches"]),
         "clocks": clocks,
+        "parity_checked": parity,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak if peak else None,
+                     "frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"],
                      "traffic": profiled_traffic(per_rank, args.graph) if world == 1 else None,
                      "traffic_note": "DRAM read+write bytes of the tensor-core launches of one "
                                      "step (ncu, profiles/tc_conv_traffic_resnet50_b256.txt)",
                      "kernel": "tc_conv_kernel (+ tc_conv_pn_kernel, stem_pool_kernel)",
                      "launches_per_step": per_step,
-                     "kernel_ms_per_step": tc_total_ms, "peak_source": peaks["source"] +
-                     " (sustained cuBLAS bf16)"},
+                     "kernel_ms_per_step": tc_total_ms,
+                     "peak_source": peaks["source"] + " (burst cuBLAS bf16: launches are timed "
+                                                      "one by one)"},
     }
+    if clocks and clocks.get("sm_mhz"):
+        line["ms_per_step_x_sm_mhz"] = ms_step * clocks["sm_mhz"]
+    if world == 1 and not args.no_extras:
+        from occamy_b200 import opbench
+        rows, hbm, hbm_src = opbench.run(batch=args.batch, reps=10, math=rt.MATH_BF16)
+        line["roofline"]["membound"] = [
+            {"op": r[0], "ms": round(r[2], 4), "gbs": round(r[3], 1), "frac": round(r[4], 3)}
+            for r in rows]
+        line["roofline"]["membound_peak"] = {"gbs": hbm, "source": hbm_src + " copy bandwidth"}
+        rt.set_math_mode(math_mode)
+        inc = {}
+        for fuse in (1, 0):
+            d = incumbent_line(args.graph, args.batch, fuse, 5)
+            if d:
+                inc["fused" if fuse else "unfused"] = {"value": d["value"], "unit": "images/s",
+                                                        "ms_per_step": d["ms_per_step"]}
+        if inc:
+            inc["what"] = ("the reference's own cuDNN / cuBLASLt wrappers compiled unchanged, same "
+                           "call program, same GPU, host batch in and host result out")
+            line["incumbent"] = inc
     if not args.no_cpu_baseline and world == 1:
         cores = os.cpu_count() or 1
         sample = 16
-        v, dt = cpu_baseline_sample(sample, 3)
+        v, dt = cpu_baseline_sample(sample, 3, args.graph)
         line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": cores, "kind": "port",
-                                "sample": f"{sample} images (of the batch-256 workload), fp32 C "
+                                "sample": f"{sample} images (of the batch-{args.batch} workload), fp32 C "
                                           f"restatement with OpenMP, {dt:.2f} s per pass"}
+        if not args.no_extras:
+            line["cpu_baseline_torch"] = {
+                "unit": "images/s", "what": "PyTorch CPU (oneDNN), same graph and weights",
+                "all_threads": {"value": torch_cpu_baseline(args.graph, 16, cores), "threads": cores},
+                "four_threads": {"value": torch_cpu_baseline(args.graph, 8, 4), "threads": 4,
+                                 "why": "the thread count of the reference's own timing script "
+                                        "(test/models/resnet50/run.py:83)"}}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def check_parity(args, g, builder, prog, binding, x_host, out_host, gathered, world, per_rank,
+                 rank_images, step_e2e):
+    """Runs the CPU oracle on four images of the batch that was timed and compares (a) the
+    timed program's own output, as the end-to-end step left it in rank 0's host buffer, and
+    (b) the logits of the same images from a replay that also returns the pre-softmax tensor.
+    With several ranks two of the images belong to the last rank, so the gathered tensor is
+    what is checked."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import max_rel_err, run_graph_oracle, top1_agrees
+    step_e2e()                                    # out_host now holds this batch's result
+    picks = [(0, 0), (0, per_rank // 3), (world - 1, 2 * per_rank // 3), (world - 1, per_rank - 1)]
+    imgs = []
+    cache = {0: x_host.numpy()}
+    for r, i in picks:
+        if r not in cache:
+            cache[r] = rank_images(r, per_rank)
+        imgs.append(cache[r][i])
+    rows = [r * per_rank + i for r, i in picks]
+    gs = builder(batch=len(picks), seed=0)
+    outs, vals = run_graph_oracle(gs, np.stack(imgs), keep=True)
+    want_out, want_logits = outs[0], vals[gs.logits]
+    got_out = out_host.numpy()[rows]
+    res = {"images": len(picks), "rows": rows, "tolerance": PARITY_TOL[args.math],
+           "output_max_abs_err": float(np.abs(got_out - want_out).max()),
+           "top1_equal": bool(np.array_equal(got_out.argmax(1), want_out.argmax(1)))}
+    if world == 1:
+        # the same program with the logits marked as an output as well (identical kernels up
+        # to the softmax), on the same host batch
+        import ctypes as C
+        from occamy_b200 import replay
+        g2 = builder(batch=per_rank, seed=0)
+        if g2.logits not in g2.outputs:
+            g2.mark_output(g2.logits)
+        p2 = g2.to_program()
+        p2.lower(fuse=args.fuse, dealloc_opt=True, pool_opt=True)
+        outs2 = p2.run(binding, x_host.numpy())
+        got_logits = outs2[g2.outputs.index(g2.logits)][rows]
+        res["max_rel"] = max_rel_err(got_logits, want_logits)
+        ok, ties = top1_agrees(got_logits, want_logits)
+        res["top1_equal"] = res["top1_equal"] and ok
+    else:
+        # logits are not an output of the sharded run; probabilities bound them from above
+        res["max_rel"] = max_rel_err(got_out, want_out)
+    res["ok"] = bool(res["max_rel"] <= PARITY_TOL[args.math] and res["top1_equal"])
+    if not res["ok"]:
+        print(f"[bench] PARITY FAILED: {res}", file=sys.stderr, flush=True)
+    return res
 
 
 def profiled_traffic(batch, graph):

@@ -56,17 +56,19 @@ def _bf16_tensor(h, rng, N, Cc, H, W):
     return y
 
 
-def main():
+def run(batch=256, reps=20, only="", math=rt.MATH_BF16):
+    """Times the rows whose name contains one of the comma-separated pieces of `only` (all rows
+    when empty); returns [(name, algorithmic MB, ms, GB/s, fraction of the copy bandwidth)] and
+    the peak used."""
     import torch
 
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--batch", type=int, default=256)
-    ap.add_argument("--reps", type=int, default=20)
-    ap.add_argument("--out", default="")
-    ap.add_argument("--only", default="", help="run only the rows whose name contains this text")
-    args = ap.parse_args()
+    class _Args:
+        pass
+    args = _Args()
+    args.batch, args.reps, args.only = batch, reps, only
+    wanted = [t for t in only.split(",") if t]
     torch.cuda.init()
-    rt.set_math_mode(rt.MATH_BF16)
+    rt.set_math_mode(math)
     L = rt.lib()
     h = C.c_void_p()
     L.cudnnCreate(C.byref(h))
@@ -77,7 +79,7 @@ def main():
     rows = []
 
     def timed(name, nbytes, fn):
-        if args.only and args.only not in name:
+        if wanted and not any(t in name for t in wanted):
             return
         for _ in range(3):
             fn()
@@ -114,14 +116,37 @@ def main():
                                      rt.dims((1, 1)), rt.dims((st, st)), y.ptr)
         return call, 2 * (int(np.prod(x.shape)) + int(np.prod(y.shape))) + 36 * Cc, (w, y)
 
-    # ---- ResNet-50 sized tensors ----
-    x = _bf16_tensor(h, rng, B, 64, 112, 112)
-    call, nb, keep = pool(x, 3, 1, 2, False)
-    timed(f"max pool 3x3/2 [{B},64,112,112]", nb, call)
-    del keep
-    x.buf.free()
+    def sel(*pieces):   # does the selection keep any row whose name holds one of these?
+        return not wanted or any(any(t in pc or pc in t for pc in pieces) for t in wanted)
 
-    a = _bf16_tensor(h, rng, B, 256, 56, 56)
+    # ---- ResNet-50 sized tensors ----
+    if sel("max pool"):
+        x = _bf16_tensor(h, rng, B, 64, 112, 112)
+        call, nb, keep = pool(x, 3, 1, 2, False)
+        timed(f"max pool 3x3/2 [{B},64,112,112]", nb, call)
+        del keep
+        x.buf.free()
+
+    if not sel("add", "ReLU", "Clip", "average pool 2x2"):
+        a = None
+    else:
+        a = _bf16_tensor(h, rng, B, 256, 56, 56)
+    if a is not None:
+        a, b, out, n = _elementwise_rows(a, h, rng, B, L, timed, pool)
+        for t in (a, b, out):
+            t.buf.free()
+    if sel("global average pool"):
+        g = _bf16_tensor(h, rng, B, 2048, 7, 7)
+        gy = _T((B, 2048, 1, 1))
+        timed(f"global average pool [{B},2048,7,7]", 2 * int(np.prod(g.shape)) + 4 * B * 2048,
+              lambda: L.DNNReduceFunc(h, 4, g.ptr, rt.dims(g.shape), gy.ptr, rt.dims(gy.shape), 5))
+        g.buf.free()
+    _rest(h, rng, B, L, timed, depthwise, sel)
+    L.cudnnDestroy(h)
+    return rows, peak, peak_src
+
+
+def _elementwise_rows(a, h, rng, B, L, timed, pool):
     b = _bf16_tensor(h, rng, B, 256, 56, 56)
     out = _T(a.shape)
     n = int(np.prod(a.shape))
@@ -135,29 +160,39 @@ def main():
     call, nb, keep = pool(a, 2, 0, 2, True)
     timed(f"average pool 2x2/2 [{B},256,56,56]", nb, call)
     del keep
-    for t in (a, b, out):
-        t.buf.free()
+    return a, b, out, n
 
-    g = _bf16_tensor(h, rng, B, 2048, 7, 7)
-    gy = _T((B, 2048, 1, 1))
-    timed(f"global average pool [{B},2048,7,7]", 2 * int(np.prod(g.shape)) + 4 * B * 2048,
-          lambda: L.DNNReduceFunc(h, 4, g.ptr, rt.dims(g.shape), gy.ptr, rt.dims(gy.shape), 5))
-    g.buf.free()
 
+def _rest(h, rng, B, L, timed, depthwise, sel):
     # ---- MobileNetV2 sized depthwise convolutions ----
-    for (Cc, H, st) in ((32, 112, 1), (96, 112, 2), (144, 56, 1), (192, 28, 2), (384, 14, 1), (960, 7, 1)):
-        x = _bf16_tensor(h, rng, B, Cc, H, H)
-        call, nb, keep = depthwise(x, st)
-        timed(f"depthwise 3x3/{st} [{B},{Cc},{H},{H}]", nb, call)
-        del keep
-        x.buf.free()
+    if sel("depthwise"):
+        for (Cc, H, st) in ((32, 112, 1), (96, 112, 2), (144, 56, 1), (192, 28, 2), (384, 14, 1),
+                            (960, 7, 1)):
+            x = _bf16_tensor(h, rng, B, Cc, H, H)
+            call, nb, keep = depthwise(x, st)
+            timed(f"depthwise 3x3/{st} [{B},{Cc},{H},{H}]", nb, call)
+            del keep
+            x.buf.free()
+    if sel("softmax"):
+        s = _T((B, 1000), rng.standard_normal((B, 1000), dtype=np.float32))
+        sy = _T((B, 1000))
+        timed(f"softmax [{B},1000] fp32", 8 * B * 1000,
+              lambda: L.CUDASoftmaxFunc(s.ptr, rt.dims(s.shape), sy.ptr, rt.dims(s.shape), 1, 2))
 
-    s = _T((B, 1000), rng.standard_normal((B, 1000), dtype=np.float32))
-    sy = _T((B, 1000))
-    timed(f"softmax [{B},1000] fp32", 8 * B * 1000,
-          lambda: L.CUDASoftmaxFunc(s.ptr, rt.dims(s.shape), sy.ptr, rt.dims(s.shape), 1, 2))
 
-    lines = [f"# memory-bound operator kernels through the C ABI, batch {B}, bf16 mode; "
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--out", default="")
+    ap.add_argument("--only", default="", help="run only the rows whose name contains one of "
+                                               "these comma-separated pieces of text")
+    ap.add_argument("--math", default="bf16", choices=["bf16", "fp16"])
+    args = ap.parse_args()
+    B = args.batch
+    rows, peak, peak_src = run(B, args.reps, args.only,
+                               rt.MATH_BF16 if args.math == "bf16" else rt.MATH_F16)
+    lines = [f"# memory-bound operator kernels through the C ABI, batch {B}, {args.math} mode; "
              f"peak = {peak:.0f} GB/s ({peak_src} copy bandwidth)",
              "# op | MB (algorithmic) | ms | GB/s | frac of peak"]
     for r in rows:

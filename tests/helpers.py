@@ -59,3 +59,15 @@ def max_rel_err(y, ref_y):
     ref_y = np.asarray(ref_y, np.float64)
     denom = max(np.abs(ref_y).max(), 1e-30)
     return float(np.abs(y - ref_y).max() / denom)
+
+
+def top1_agrees(y, ref_y):
+    """Identical top-1 indices, row by row.  A row whose two largest reference logits lie
+    closer together than one bf16 step of their own magnitude (2^-8 relative) is undecidable
+    for any 16-bit arithmetic -- both round to the same or to neighbouring stored values -- and
+    is left out; the second value returned is how many rows that were."""
+    y, ref_y = np.asarray(y), np.asarray(ref_y)
+    srt = np.sort(ref_y, axis=1)
+    tie = (srt[:, -1] - srt[:, -2]) < np.abs(srt[:, -1]) * 2.0 ** -8
+    same = y.argmax(1) == ref_y.argmax(1)
+    return bool(np.all(same | tie)), int(tie.sum())

@@ -10,7 +10,7 @@ fp32 mode: max relative error <= 1e-4 on the logits.
 import numpy as np
 import pytest
 
-from helpers import max_rel_err, run_graph_oracle
+from helpers import max_rel_err, run_graph_oracle, top1_agrees
 from occamy_b200 import graphs, replay
 from occamy_b200 import runtime as rt
 
@@ -41,8 +41,8 @@ def full_batch_vs_sampled_oracle(builder, batch, sample, mode, tol, repeats=2, *
     got = y[list(sample)]
     err = max_rel_err(got, want)
     assert err <= tol, err
-    if mode != rt.MATH_FP32:
-        assert np.array_equal(got.argmax(1), want.argmax(1))
+    ok, ties = top1_agrees(got, want)
+    assert ok and ties <= len(sample) // 3, (got.argmax(1), want.argmax(1), ties)
     return p, y
 
 
@@ -67,7 +67,7 @@ def test_mobilenet_v2_batch128(mode):
 def test_vgg16_batch64(mode):
     """25088 -> 4096 first FC layer, the 822 MB [64,64,224,224] activation and the planner's
     peak: the pool the replayed program asks for is the one the runtime serves."""
-    p, y = full_batch_vs_sampled_oracle(graphs.vgg16, 64, (0, 63), mode,
+    p, y = full_batch_vs_sampled_oracle(graphs.vgg16, 64, (0, 21, 42, 63), mode,
                                         1e-4 if mode == rt.MATH_FP32 else 2e-2, repeats=1)
     assert y.shape == (64, 1000)
     assert rt.counters()["pool_hwm_bytes"] >= p.pool_bytes >= 64 * 64 * 224 * 224 * 4
