@@ -169,11 +169,18 @@ int64_t *CUDATranspose6DInt64Func(int64_t *in, int64_t *dimIn, int64_t *out, int
                                   int64_t *perm, int64_t rank);
 
 /* ---- controls that have no counterpart in the reference ----------------------- */
-/* Arithmetic mode of the convolution / GEMM kernels: 0 = fp32 CUDA-core kernels on the
- * ABI's NCHW fp32 tensors (max rel. error <= 1e-4 against the CPU semantics);
- * 1 = bf16 tcgen05 tensor-core kernels with fp32 accumulation, activations kept as
- * NHWC bf16 between operators (<= 2e-2 on logits).  Also settable with the
- * environment variable OCCAMY_MATH=fp32|bf16 before the first call; default bf16. */
+/* Arithmetic mode of the convolution / GEMM kernels:
+ * 0 = fp32 CUDA-core kernels on the ABI's NCHW fp32 tensors (max rel. error <= 1e-4 against
+ *     the CPU semantics);
+ * 1 = bf16 tcgen05 tensor-core kernels with fp32 accumulation, activations kept as NHWC bf16
+ *     between operators (default; <= 2e-2 on the logits of ResNet-50 and VGG-16);
+ * 2 = the same kernels on fp16 operands and fp16 NHWC activations: three more mantissa bits
+ *     than bf16 (the precision of TF32) at the same speed and bytes, for networks whose
+ *     activations stay below 65504 in magnitude -- MobileNetV2, whose ReLU6 bounds them, needs
+ *     it to stay within 2e-2.  A value beyond that range becomes infinity, never a silently
+ *     wrong finite number.
+ * Also settable with the environment variable OCCAMY_MATH=fp32|bf16|fp16 before the first
+ * call. */
 void occamy_set_math_mode(int mode);
 int occamy_get_math_mode(void);
 /* 0 if every call so far succeeded; otherwise a sticky code (CUDA error, or 1000 + a

@@ -80,7 +80,9 @@ void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int
   uintptr_t base;
   TensorRec *rec = reg_find(w, &base);
   const bool cacheable = r.cache_weights && rec && base == (uintptr_t)w && rec->host_src;
-  WeightKey key{nullptr, 0, layout * 4096 + Sp * 64 + Cp};
+  // fp32 layouts are shared by the two 16-bit modes, 16-bit ones are packed per element type
+  const bool f16 = mode_f16() && layout != PACK_DW && layout != PACK_RAW;
+  WeightKey key{nullptr, 0, layout * 4096 + Sp * 64 + Cp + (f16 ? (1 << 20) : 0)};
   if (cacheable) {
     key.src = rec->host_src;
     key.bytes = rec->host_bytes;
@@ -109,12 +111,12 @@ void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int
     dst = scratch_get(layout == PACK_STEM ? 5 : 1, packed_bytes);
   }
   if (!dst) return nullptr;
-  if (layout == PACK_KRSC) launch_pack_krsc_bf16(w, (bf16 *)dst, K, C, R, S, Cp, r.stream);
+  if (layout == PACK_KRSC) launch_pack_krsc_bf16(w, (bf16 *)dst, K, C, R, S, Cp, f16, r.stream);
   else if (layout == PACK_DW) launch_pack_dw_f32(w, (float *)dst, C, R, S, r.stream);
   else if (layout == PACK_RAW)
     OCC_CUDA(cudaMemcpyAsync(dst, w, packed_bytes, cudaMemcpyDeviceToDevice, r.stream));
   else if (layout == PACK_STEM) launch_pack_stem_bf16(w, (bf16 *)dst, C, R, S, Cp, Sp * Cp, r.stream);
-  else launch_pack_fold_bf16(w, (bf16 *)dst, K, C, R, S, Sp, Cp, r.stream);
+  else launch_pack_fold_bf16(w, (bf16 *)dst, K, C, R, S, Sp, Cp, f16, r.stream);
   return dst;
 }
 
@@ -174,6 +176,7 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
   memset(&a, 0, sizeof(a));
   a.N = g.N; a.K = g.K; a.P = g.P; a.Q = g.Q;
   a.act = g.act; a.lo = g.lo; a.hi = g.hi;
+  a.f16 = mode_f16() ? 1 : 0;
   const bool folded = g.C < 16;
   int Sp = 0, Cp = 0, Wp = 0;
   if (folded) {
@@ -206,13 +209,13 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
     ensure_f32(x);
     bf16 *xf = (bf16 *)scratch_get(0, (size_t)g.N * g.H * Wp * Cp * 2);
     if (!xf) return false;
-    launch_pad_input_bf16(x, xf, g.N, g.C, g.H, g.W, Wp, Cp, g.pad_w, r.stream);
+    launch_pad_input_bf16(x, xf, g.N, g.C, g.H, g.W, Wp, Cp, g.pad_w, mode_f16(), r.stream);
     a.x = xf;
     a.w = (const bf16 *)packed_weights(w, PACK_FOLD, (size_t)g.R * g.K * a.Cf * 2, g.K, g.C, g.R,
                                        g.S, Sp, Cp);
   } else {
     const bf16 *xb = nullptr;
-    if (is_bf16(x, g.N, g.C, g.H, g.W)) {
+    if (is_act16(x, g.N, g.C, g.H, g.W)) {
       xb = (const bf16 *)x;
       if (Cp == g.C) {
         job.dep_lo[0] = (uintptr_t)x;
@@ -222,7 +225,7 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
       ensure_f32(x);
       bf16 *xc = (bf16 *)scratch_get(0, (size_t)g.N * g.C * g.H * g.W * 2);
       if (!xc) return false;
-      launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, r.stream);
+      launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, mode_f16(), r.stream);
       xb = xc;
     }
     if (Cp != g.C) {   // the kernel reads the padded copy, made now: no dependence on x later
@@ -257,7 +260,7 @@ bool prepare_depthwise(const float *x, const float *w, const float *bias, const 
   Runtime &r = rt();
   if (g.C % 8 != 0) return false;
   job.dep_lo[0] = job.dep_hi[0] = 0;
-  if (is_bf16(x, g.N, g.C, g.H, g.W)) {
+  if (is_act16(x, g.N, g.C, g.H, g.W)) {
     job.dw_x = (const bf16 *)x;
     job.dep_lo[0] = (uintptr_t)x;
     job.dep_hi[0] = (uintptr_t)x + (size_t)g.N * g.C * g.H * g.W * 2;
@@ -265,7 +268,7 @@ bool prepare_depthwise(const float *x, const float *w, const float *bias, const 
     ensure_f32(x);
     bf16 *xc = (bf16 *)scratch_get(0, (size_t)g.N * g.C * g.H * g.W * 2);
     if (!xc) return false;
-    launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, r.stream);
+    launch_nchw_f32_to_nhwc_bf16(x, xc, g.N, g.C, g.H, g.W, mode_f16(), r.stream);
     job.dw_x = xc;
   }
   job.dw_w = (const float *)packed_weights(w, PACK_DW, (size_t)g.R * g.S * g.C * 4, g.K, g.C, g.R,
@@ -322,13 +325,13 @@ void launch_job(ConvJob &job) {
     count(CNT_LAUNCHES);
   }
   if (job.depthwise) {
-    launch_depthwise_bf16(job.dw_x, job.dw_w, job.bias, (bf16 *)job.out, g, r.stream);
+    launch_depthwise_bf16(job.dw_x, job.dw_w, job.bias, (bf16 *)job.out, g, mode_f16(), r.stream);
   } else {
     job.a.y = (bf16 *)job.out;
     job.a.act = g.act; job.a.lo = g.lo; job.a.hi = g.hi;
     launch_tc_conv(job.a, r.stream);
   }
-  mark_bf16(job.out, g.N, g.K, g.P, g.Q);
+  mark_act16(job.out, g.N, g.K, g.P, g.Q);
 }
 
 // Executes the held-back convolution as far as it has been built up.
@@ -423,11 +426,11 @@ float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t
   e.out_bytes = (int64_t)g.N * g.K * g.P * g.Q * 4;
   e.kind = (int)act_mode;
   e.depthwise = depthwise;
-  e.fusable = shape_ok && r.mode == MATH_BF16 && g.P > 0 && g.Q > 0 && g.N > 0 &&
+  e.fusable = shape_ok && r.mode != MATH_FP32 && g.P > 0 && g.Q > 0 && g.N > 0 &&
               (depthwise ? g.C % 8 == 0
                          : (g.groups == 1 && g.K % 8 == 0 && (g.C < 16 || g.C % 8 == 0)));
   // the fused convolution + max-pool kernel takes 64-channel stems whose column step is 16 bytes
-  e.poolable = e.fusable && !depthwise && g.C <= 4 && g.K == 64 && g.stride_w == 2 && g.Q <= 128 &&
+  e.poolable = e.fusable && r.mode == MATH_BF16 && !depthwise && g.C <= 4 && g.K == 64 && g.stride_w == 2 && g.Q <= 128 &&
                g.S <= 16 && g.R <= 11;
   const Role role = step(e, false);
 
@@ -440,7 +443,7 @@ float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t
     fprintf(stderr, "[occamy] conv x[%d,%d,%d,%d] w[%d,%d,%d,%d] g%d s%d p%d act%d role%d\n", g.N,
             g.C, g.H, g.W, g.K, (int)dW[1], g.R, g.S, g.groups, g.stride_h, g.pad_h, act,
             (int)role);
-  if (r.mode == MATH_BF16) {
+  if (r.mode != MATH_FP32) {
     ConvJob job;
     const bool ok = depthwise ? prepare_depthwise(x, w, bias, g, job)
                               : (g.groups == 1 && prepare_dense(x, w, bias, g, job));
@@ -652,12 +655,12 @@ cudaError_t wrapDNNMemcpy(void *dst, const void *src, size_t count_, int kind,
     uintptr_t base;
     TensorRec *rec = reg_find(src, &base);
     const void *from = src;
-    if (rec && rec->fmt == FMT_BF16_NHWC && base == (uintptr_t)src) {
+    if (rec && fmt_is_16(rec->fmt) && base == (uintptr_t)src) {
       // convert into scratch instead of in place: the tensor keeps its fast format
       const size_t elems = (size_t)(rec->n * rec->c * rec->h * rec->w);
       float *tmp = (float *)scratch_get(2, elems * 4);
       launch_nhwc_bf16_to_nchw_f32((const bf16 *)src, tmp, (int)rec->n, (int)rec->c, (int)rec->h,
-                                   (int)rec->w, r.stream);
+                                   (int)rec->w, rec->fmt == FMT_F16_NHWC, r.stream);
       count(CNT_MATERIALIZE);
       from = tmp;
     } else {
@@ -805,10 +808,10 @@ float *DNNActiveFunc(cudnnContext *, float *x, int64_t dimX[4], int32_t mode, fl
     }
     flush_pending();
   }
-  if (is_bf16(x, dimX[0], dimX[1], dimX[2], dimX[3])) {
+  if (is_act16(x, dimX[0], dimX[1], dimX[2], dimX[3])) {
     launch_add_act_bf16((const bf16 *)x, nullptr, nullptr, (int)dimX[1], (bf16 *)y, n, act, 0.f,
-                        0.f, r.stream);
-    mark_bf16(y, dimX[0], dimX[1], dimX[2], dimX[3]);
+                        0.f, mode_f16(), r.stream);
+    mark_act16(y, dimX[0], dimX[1], dimX[2], dimX[3]);
     return y;
   }
   ensure_f32(x);
@@ -840,10 +843,10 @@ float *CUDAClipFunc(float *x, float *y, int64_t *dimOut, float lo, float hi, int
     }
     flush_pending();
   }
-  if (rank == 4 && is_bf16(x, dimOut[0], dimOut[1], dimOut[2], dimOut[3])) {
+  if (rank == 4 && is_act16(x, dimOut[0], dimOut[1], dimOut[2], dimOut[3])) {
     launch_add_act_bf16((const bf16 *)x, nullptr, nullptr, (int)dimOut[1], (bf16 *)y, n, ACT_CLIP,
-                        lo, hi, r.stream);
-    mark_bf16(y, dimOut[0], dimOut[1], dimOut[2], dimOut[3]);
+                        lo, hi, mode_f16(), r.stream);
+    mark_act16(y, dimOut[0], dimOut[1], dimOut[2], dimOut[3]);
     return y;
   }
   ensure_f32(x);
@@ -901,7 +904,7 @@ float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, 
     if (e.kind == CK_SAME_ADD && dims_ok && !g_pending.depthwise && !g_pending.res_set &&
         !g_pending.act_set && ((A == g_pending.out) != (B == g_pending.out))) {
       const float *other = A == g_pending.out ? B : A;
-      if (is_bf16(other, g.N, g.K, g.P, g.Q)) {
+      if (is_act16(other, g.N, g.K, g.P, g.Q)) {
         g_pending.a.residual = (const bf16 *)other;
         g_pending.res_set = true;
         g_pending.dep_lo[1] = (uintptr_t)other;
@@ -913,20 +916,20 @@ float *DNNTensorOpFunc(cudnnContext *, int64_t opMode, float *A, int64_t *dimA, 
     flush_pending();
   }
   if (opMode == 0 && rankA == 4 && bias == 1.0f &&
-      is_bf16(A, dimA[0], dimA[1], dimA[2], dimA[3])) {
+      is_act16(A, dimA[0], dimA[1], dimA[2], dimA[3])) {
     const int64_t n = numel4(dimA);
-    if (same && is_bf16(B, dimA[0], dimA[1], dimA[2], dimA[3])) {
+    if (same && is_act16(B, dimA[0], dimA[1], dimA[2], dimA[3])) {
       launch_add_act_bf16((const bf16 *)A, (const bf16 *)B, nullptr, (int)dimA[1], (bf16 *)out, n,
-                          ACT_IDENTITY, 0.f, 0.f, r.stream);
-      mark_bf16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
+                          ACT_IDENTITY, 0.f, 0.f, mode_f16(), r.stream);
+      mark_act16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
       return out;
     }
     if (bias_shape) {
       // a bias vector uploaded from host memory is kept resident like the filters are
       const float *bd = resident_f32(B, (size_t)dimA[1] * 4);
       launch_add_act_bf16((const bf16 *)A, nullptr, bd, (int)dimA[1], (bf16 *)out, n, ACT_IDENTITY,
-                          0.f, 0.f, r.stream);
-      mark_bf16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
+                          0.f, 0.f, mode_f16(), r.stream);
+      mark_act16(out, dimA[0], dimA[1], dimA[2], dimA[3]);
       return out;
     }
   }
@@ -982,7 +985,7 @@ static float *pool_common(int sym, float *x, int64_t *dI, float *y, int64_t *dO,
           j.absorbed++;
           elide(j.out);
           trace_count_chain();
-          mark_bf16(y, N, C, P, Q);
+          mark_act16(y, N, C, P, Q);
           done = true;
         }
       }
@@ -990,10 +993,10 @@ static float *pool_common(int sym, float *x, int64_t *dI, float *y, int64_t *dO,
     if (done) return y;
     flush_pending();
   }
-  if (r.mode == MATH_BF16 && C % 8 == 0 && is_bf16(x, N, C, H, W)) {
+  if (r.mode != MATH_FP32 && C % 8 == 0 && is_act16(x, N, C, H, W)) {
     launch_pool_bf16((const bf16 *)x, (bf16 *)y, N, C, H, W, P, Q, (int)kernel[0], (int)kernel[1],
-                     ph, pw, (int)stride[0], (int)stride[1], avg, r.stream);
-    mark_bf16(y, N, C, P, Q);
+                     ph, pw, (int)stride[0], (int)stride[1], avg, mode_f16(), r.stream);
+    mark_act16(y, N, C, P, Q);
     return y;
   }
   ensure_f32(x);
@@ -1029,9 +1032,9 @@ float *DNNReduceFunc(cudnnContext *, int32_t rank, float *x, int64_t *dimIn, flo
   }
   if (rank == 4 && dimOut[2] == 1 && dimOut[3] == 1 && dimOut[0] == dimIn[0] &&
       dimOut[1] == dimIn[1] && dimIn[1] % 8 == 0 &&
-      is_bf16(x, dimIn[0], dimIn[1], dimIn[2], dimIn[3])) {
+      is_act16(x, dimIn[0], dimIn[1], dimIn[2], dimIn[3])) {
     launch_gap_bf16((const bf16 *)x, y, (int)dimIn[0], (int)(dimIn[2] * dimIn[3]), (int)dimIn[1],
-                    r.stream);
+                    mode_f16(), r.stream);
     mark_f32(y);
     return y;
   }
@@ -1059,7 +1062,7 @@ float *CUBLASMatmul2dFunc(int64_t /*rank*/, float *A, int64_t dimA[2], float *B,
   step(e, false);
   if (r.log) fprintf(stderr, "[occamy] matmul2d M%d N%d K%d tA%d tB%d\n", M, N, K, (int)transA, (int)transB);
   const bool out_zero = is_zero(out);
-  if (r.mode == MATH_BF16 && !transA && transB && alpha == 1.0f && (beta == 0.0f || out_zero) &&
+  if (r.mode != MATH_FP32 && !transA && transB && alpha == 1.0f && (beta == 0.0f || out_zero) &&
       K % 16 == 0 && M > 0) {
     TcConvArgs a;
     memset(&a, 0, sizeof(a));
@@ -1068,6 +1071,7 @@ float *CUBLASMatmul2dFunc(int64_t /*rank*/, float *A, int64_t dimA[2], float *B,
     a.act = ACT_IDENTITY;
     a.out_f32 = out;
     a.ldo = N;
+    a.f16 = mode_f16() ? 1 : 0;
     a.x = (const bf16 *)16;
     a.w = (const bf16 *)16;
     if (tc_conv_supported(a)) {
@@ -1075,7 +1079,7 @@ float *CUBLASMatmul2dFunc(int64_t /*rank*/, float *A, int64_t dimA[2], float *B,
       bf16 *ab = (bf16 *)scratch_get(0, (size_t)M * K * 2);
       const bf16 *wb = (const bf16 *)packed_weights(B, PACK_KRSC, (size_t)N * K * 2, N, K, 1, 1, 0, 0);
       if (ab && wb) {
-        launch_f32_to_bf16(A, ab, (int64_t)M * K, r.stream);
+        launch_f32_to_bf16(A, ab, (int64_t)M * K, mode_f16(), r.stream);
         a.x = ab;
         a.w = wb;
         launch_tc_conv(a, r.stream);
@@ -1141,7 +1145,10 @@ void occamy_internal_opaque_call(void) {
 }
 
 // ---------------------------------------------------------------- controls
-void occamy_set_math_mode(int mode) { rt().mode = mode == 0 ? MATH_FP32 : MATH_BF16; }
+void occamy_set_math_mode(int mode) {
+  flush_pending();   // what is held back was prepared for the mode it arrived in
+  rt().mode = mode == 0 ? MATH_FP32 : (mode == 2 ? MATH_F16 : MATH_BF16);
+}
 int occamy_get_math_mode(void) { return (int)rt().mode; }
 
 int occamy_last_error(int clear) {

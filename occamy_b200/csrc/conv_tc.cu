@@ -489,11 +489,11 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   // than the plain one, which hurts the HBM-bound 1x1 layers
   // 3x3 / stride 1 / pad 1 with 64 -> 64 channels and rows of at most 126 pixels: the input
   // block of a tile is loaded once and the taps are windows of it (TC_MODE_HALO)
-  const bool halo = allow_halo && halo_allowed && !a.out_f32 && a.R == 3 && a.S == 3 &&
+  const bool halo = allow_halo && halo_allowed && !a.f16 && !a.out_f32 && a.R == 3 && a.S == 3 &&
                     a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 1 && a.pad_w == 1 &&
                     a.Cf == 64 && a.K == 64 && a.W + 2 <= 128 && a.w_step == 0 && a.Q == a.W &&
                     a.P == a.H;
-  const bool pn = !halo && pn_allowed && !a.out_f32 && a.K <= 128 && a.R * a.S > 1 &&
+  const bool pn = !halo && pn_allowed && !a.f16 && !a.out_f32 && a.K <= 128 && a.R * a.S > 1 &&
                   a.R * a.S * a.Cf >= 9 * 64;
   pl.pn = pn;
   if (halo) {
@@ -583,6 +583,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   pl.mode = a.out_f32 ? (TC_MODE_F32 | TC_MODE_CLAMP)
                       : ((a.residual ? TC_MODE_RES : 0) | (a.act == ACT_RELU ? 0 : TC_MODE_CLAMP) |
                          (halo ? TC_MODE_HALO : 0));
+  if (a.f16) pl.mode |= TC_MODE_F16;
   if (!a.out_f32) {
     const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
     const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};

@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cmath>
@@ -69,6 +70,9 @@ constexpr int TC_MODE_F32 = 4;     // fp32 row-major output straight to global m
 // buffer.  The tile is th full rows of width W + 2; its two extra columns are junk that the
 // TMA store clips.
 constexpr int TC_MODE_HALO = 8;
+// Operands and output are fp16 instead of bf16 (same MMA kind, same rate, other format bits
+// in the instruction descriptor and other conversion instructions in the epilogue).
+constexpr int TC_MODE_F16 = 16;
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -213,20 +217,35 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-// (a, b) -> bf16x2 with a in the low half; the second form clamps negatives to zero.
+// (a, b) -> two 16-bit values (bf16, or fp16 when F16) with a in the low half; the second form
+// clamps negatives to zero.
+template <bool F16 = false>
 __device__ __forceinline__ uint32_t f2_to_bf16x2(uint64_t v) {
   float a, b;
   f2_unpack(v, a, b);
   uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  if constexpr (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
   return r;
 }
+template <bool F16 = false>
 __device__ __forceinline__ uint32_t f2_to_bf16x2_relu(uint64_t v) {
   float a, b;
   f2_unpack(v, a, b);
   uint32_t r;
-  asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  if constexpr (F16) asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
   return r;
+}
+// two 16-bit values in one word -> packed fp32 pair (low half first)
+template <bool F16>
+__device__ __forceinline__ uint64_t pair16_to_f2(uint32_t w) {
+  if constexpr (F16) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    return f2_pack(t.x, t.y);
+  } else {   // a bf16 is the top half of the fp32 of its value
+    return f2_pack(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -383,13 +402,15 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   constexpr bool CLAMP = (MODE & TC_MODE_CLAMP) != 0;
   constexpr bool F32 = (MODE & TC_MODE_F32) != 0;
   constexpr bool HALO = (MODE & TC_MODE_HALO) != 0;
+  constexpr bool F16 = (MODE & TC_MODE_F16) != 0;
   constexpr int EPI_THREADS = 128 * EW;
   constexpr int STORE_WARP = 2 + 4 * EW;
   constexpr int CW = DC / EW;                  // channels one epilogue thread handles per slab
   constexpr int NSLAB = BN / DC;
   constexpr int SLAB_BYTES = 128 * DC * 2;
-  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                             ((uint32_t)(128 >> 4) << 24);
+  // fp32 accumulator; A and B formats: 1 = bf16, 0 = fp16; N / 8 and M / 16
+  constexpr uint32_t IDESC = (1u << 4) | (F16 ? 0u : ((1u << 7) | (1u << 10))) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 
   extern __shared__ uint8_t smem_raw[];
@@ -768,10 +789,8 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
               const uint4 rv = *reinterpret_cast<const uint4 *>(dptr + soff[c4]);
               const uint32_t w4[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
-              for (int e = 0; e < 4; ++e)   // a bf16 is the top half of the fp32 of its value
-                v2[c4 * 4 + e] = f2_add(v2[c4 * 4 + e],
-                                        f2_pack(__uint_as_float(w4[e] << 16),
-                                                __uint_as_float(w4[e] & 0xffff0000u)));
+              for (int e = 0; e < 4; ++e)
+                v2[c4 * 4 + e] = f2_add(v2[c4 * 4 + e], pair16_to_f2<F16>(w4[e]));
             }
           }
           uint32_t pk[CW / 2];
@@ -780,9 +799,9 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
             if constexpr (CLAMP) {
               float a, b;
               f2_unpack(v2[j], a, b);
-              pk[j] = f2_to_bf16x2(f2_pack(tc_act(a, act_lo, act_hi), tc_act(b, act_lo, act_hi)));
+              pk[j] = f2_to_bf16x2<F16>(f2_pack(tc_act(a, act_lo, act_hi), tc_act(b, act_lo, act_hi)));
             } else {
-              pk[j] = f2_to_bf16x2_relu(v2[j]);   // ReLU rides on the conversion
+              pk[j] = f2_to_bf16x2_relu<F16>(v2[j]);   // ReLU rides on the conversion
             }
           }
 #pragma unroll
@@ -892,6 +911,22 @@ inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t
 }
 template <int BN, int DC, bool WITH_F32, bool WITH_HALO = false>
 inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
+  constexpr int H = TC_MODE_F16;
+  switch (mode) {   // the fp16 flavours first (no halo form among them)
+    case H: tc_launch_one<BN, DC, H>(p, grid, smem, s); return true;
+    case H | TC_MODE_RES: tc_launch_one<BN, DC, H | TC_MODE_RES>(p, grid, smem, s); return true;
+    case H | TC_MODE_CLAMP: tc_launch_one<BN, DC, H | TC_MODE_CLAMP>(p, grid, smem, s); return true;
+    case H | TC_MODE_RES | TC_MODE_CLAMP:
+      tc_launch_one<BN, DC, H | TC_MODE_RES | TC_MODE_CLAMP>(p, grid, smem, s);
+      return true;
+    case H | TC_MODE_F32 | TC_MODE_CLAMP:
+      if constexpr (WITH_F32) {
+        tc_launch_one<BN, DC, H | TC_MODE_F32 | TC_MODE_CLAMP>(p, grid, smem, s);
+        return true;
+      }
+      return false;
+    default: break;
+  }
   switch (mode) {
     case 0: tc_launch_one<BN, DC, 0>(p, grid, smem, s); return true;
     case TC_MODE_RES: tc_launch_one<BN, DC, TC_MODE_RES>(p, grid, smem, s); return true;

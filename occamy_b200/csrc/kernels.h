@@ -43,39 +43,42 @@ void launch_gemm_f32(const float *A, const float *B, float *out, int M, int N, i
 void launch_softmax_f32(const float *x, float *y, int64_t outer, int64_t len, int64_t inner,
                         cudaStream_t s);
 
-// ---- bf16 NHWC kernels (tensor-core mode activations) -------------------------
+// ---- 16-bit NHWC kernels (tensor-core mode activations) -----------------------
+// `bf16 *` is the pointer type of every 16-bit tensor, whichever of the two element types it
+// holds; the `f16` argument of a launcher says which: false = bf16, true = fp16.
 typedef __nv_bfloat16 bf16;
-void launch_nchw_f32_to_nhwc_bf16(const float *x, bf16 *y, int N, int C, int H, int W,
+void launch_nchw_f32_to_nhwc_bf16(const float *x, bf16 *y, int N, int C, int H, int W, bool f16,
                                   cudaStream_t s);
-void launch_nhwc_bf16_to_nchw_f32(const bf16 *x, float *y, int N, int C, int H, int W,
+void launch_nhwc_bf16_to_nchw_f32(const bf16 *x, float *y, int N, int C, int H, int W, bool f16,
                                   cudaStream_t s);
-void launch_f32_to_bf16(const float *x, bf16 *y, int64_t n, cudaStream_t s);
+void launch_f32_to_bf16(const float *x, bf16 *y, int64_t n, bool f16, cudaStream_t s);
 // out = act(a + b) over n elements (b may be null); c-periodic fp32 bias may be added.
 void launch_add_act_bf16(const bf16 *a, const bf16 *b, const float *bias_c, int C, bf16 *out,
-                         int64_t n, int act, float lo, float hi, cudaStream_t s);
+                         int64_t n, int act, float lo, float hi, bool f16, cudaStream_t s);
 void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P, int Q, int kh,
-                      int kw, int pad_h, int pad_w, int sh, int sw, bool avg, cudaStream_t s);
-// Global average pool: x [N, HW, C] bf16 -> y [N, C] fp32.
-void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t s);
-// Depthwise RxS convolution on NHWC bf16, weights fp32 packed [R*S][C], fused bias + act.
+                      int kw, int pad_h, int pad_w, int sh, int sw, bool avg, bool f16,
+                      cudaStream_t s);
+// Global average pool: x [N, HW, C] 16-bit -> y [N, C] fp32.
+void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, bool f16, cudaStream_t s);
+// Depthwise RxS convolution on 16-bit NHWC, weights fp32 packed [R*S][C], fused bias + act.
 void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias, bf16 *y,
-                           const ConvGeom &g, cudaStream_t s);
-// Weight packing: fp32 KCRS -> bf16 [R*S][K][C] (dense conv) ...
-void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Cp,
+                           const ConvGeom &g, bool f16, cudaStream_t s);
+// Weight packing: fp32 KCRS -> 16-bit [R*S][K][C] (dense conv) ...
+void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Cp, bool f16,
                            cudaStream_t s);
 void launch_pad_channels_bf16(const bf16 *x, bf16 *y, int64_t pixels, int C, int Cp, cudaStream_t s);
 // ... fp32 [C,1,R,S] -> fp32 [R*S][C] (depthwise) ...
 void launch_pack_dw_f32(const float *w, float *out, int C, int R, int S, cudaStream_t s);
 // ... and fp32 KCRS with tiny C -> bf16 [R][K][Sp*Cp] (width taps folded into channels).
 void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Sp, int Cp,
-                           cudaStream_t s);
+                           bool f16, cudaStream_t s);
 // Input side of the folded form: x fp32 NCHW (C <= Cp) -> bf16 [N][H][Wp][Cp] with pad_w zero
 // pixels on the left of every row and zeros up to Wp on the right.  The A vector of output
 // column q, Cf = Sp*Cp elements starting at pixel q*stride_w, is then a window of the row;
 // windows of neighbouring columns overlap and a tensor map with a pixel stride shorter than
 // its innermost extent reads them in place.
 void launch_pad_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Wp, int Cp,
-                           int pad_w, cudaStream_t s);
+                           int pad_w, bool f16, cudaStream_t s);
 
 // ---- tcgen05 implicit-GEMM convolution / GEMM --------------------------------
 struct TcConvArgs {
@@ -95,6 +98,7 @@ struct TcConvArgs {
   // Folded form only (else 0): elements between the A vectors of neighbouring output
   // columns, and elements per input row; the vectors overlap when w_step < Cf.
   int w_step, row_elems;
+  int f16;               // operands and bf16-typed pointers hold fp16 (else bf16)
   // Filter (and bias) were resident on the device before this call was made, i.e. no work
   // enqueued earlier in the stream produces them.
   int consts_ready;

@@ -1,6 +1,12 @@
-// Kernels on the tensor-core mode's activation format: bf16, NHWC, C a multiple of 8 so
-// that every thread moves 128 bits (8 channels) per access.  All are HBM-bound; they are
-// written so that consecutive threads touch consecutive 16-byte channel groups.
+// Kernels on the tensor-core modes' activation format: 16-bit elements (bf16 or fp16, the
+// template parameter F16 says which), NHWC, C a multiple of 8 so that every thread moves 128
+// bits (8 channels) per access.  All are HBM-bound; they are written so that consecutive
+// threads touch consecutive 16-byte channel groups.  Pointers to either element type travel
+// as `bf16 *`; the launchers' `f16` argument names the type behind them.
+#include <cuda_fp16.h>
+
+#include <cstring>
+
 #include "kernels.h"
 #include "runtime.h"
 
@@ -24,13 +30,86 @@ static inline int grid_for(int64_t n, int threads) {
   return (int)b;
 }
 
-// Eight bf16 values moved as one 16-byte word: the copy operations go through the uint4 member,
-// so a load or store of a bf16x8 is a single 128-bit access (a member-wise copy of the four pairs
+// ---- conversions between fp32 and the two 16-bit element types ----------------------
+// A pair of 16-bit values in one 32-bit word, first element in the low half.
+template <bool F16>
+__device__ __forceinline__ float2 pair_to_f32(uint32_t v) {
+  if constexpr (F16) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&v));
+  } else {   // a bf16 is the top half of the fp32 of its value
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+  }
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t f32_to_pair(float a, float b) {
+  uint32_t r;
+  if constexpr (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+// the same with negative values clamped to zero by the conversion itself
+template <bool F16>
+__device__ __forceinline__ uint32_t f32_to_pair_relu(float a, float b) {
+  uint32_t r;
+  if constexpr (F16) asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pair_max_nan(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if constexpr (F16) asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pair_min(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if constexpr (F16) asm("min.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  else asm("min.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+template <bool F16>
+__device__ __forceinline__ uint16_t f32_to_elem(float v) {
+  if constexpr (F16) return __half_as_ushort(__float2half_rn(v));
+  else return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+template <bool F16>
+__device__ __forceinline__ float elem_to_f32(uint16_t v) {
+  if constexpr (F16) return __half2float(__ushort_as_half(v));
+  else return __uint_as_float((uint32_t)v << 16);
+}
+// host side: the bits of `v` rounded to the element type, and back
+static uint16_t host_elem_bits(float v, bool f16) {
+  if (f16) {
+    const __half h = __float2half_rn(v);
+    uint16_t b;
+    memcpy(&b, &h, 2);
+    return b;
+  }
+  const __nv_bfloat16 h = __float2bfloat16_rn(v);
+  uint16_t b;
+  memcpy(&b, &h, 2);
+  return b;
+}
+static float host_elem_value(uint16_t bits, bool f16) {
+  if (f16) {
+    __half h;
+    memcpy(&h, &bits, 2);
+    return __half2float(h);
+  }
+  __nv_bfloat16 h;
+  memcpy(&h, &bits, 2);
+  return __bfloat162float(h);
+}
+
+// Eight 16-bit values moved as one 16-byte word: the copy operations go through the uint4
+// member, so a load or store is a single 128-bit access (a member-wise copy of the four pairs
 // compiles to four 32-bit accesses, which costs four times the L1 wavefronts).
 struct alignas(16) bf16x8 {
   union {
     uint4 u;
-    __nv_bfloat162 v[4];
+    uint32_t v[4];
   };
   __device__ __forceinline__ bf16x8() {}
   __device__ __forceinline__ bf16x8(const bf16x8 &o) : u(o.u) {}
@@ -40,31 +119,34 @@ struct alignas(16) bf16x8 {
   }
 };
 
+template <bool F16>
 __device__ __forceinline__ void unpack8(const bf16x8 &p, float *f) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p.v[i]);
+    const float2 t = pair_to_f32<F16>(p.v[i]);
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
 }
+template <bool F16>
 __device__ __forceinline__ bf16x8 pack8(const float *f) {
   bf16x8 p;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) p.v[i] = f32_to_pair<F16>(f[2 * i], f[2 * i + 1]);
   return p;
 }
 
 // ---------------------------------------------------------------------------
 // Layout conversion, per image: [C][HW] fp32 <-> [HW][C] bf16 through a 32x32 tile.
 // ---------------------------------------------------------------------------
-__global__ void nchw_to_nhwc_kernel(const float *__restrict__ x, bf16 *__restrict__ y, int C,
+template <bool F16>
+__global__ void nchw_to_nhwc_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, int C,
                                     int HW) {
   __shared__ float tile[32][33];
   const int n = blockIdx.z;
   const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
   const float *xn = x + (int64_t)n * C * HW;
-  bf16 *yn = y + (int64_t)n * C * HW;
+  uint16_t *yn = y + (int64_t)n * C * HW;
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
     const int c = c0 + i, p = p0 + threadIdx.x;
     tile[i][threadIdx.x] = (c < C && p < HW) ? xn[(int64_t)c * HW + p] : 0.0f;
@@ -72,20 +154,21 @@ __global__ void nchw_to_nhwc_kernel(const float *__restrict__ x, bf16 *__restric
   __syncthreads();
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
     const int p = p0 + i, c = c0 + threadIdx.x;
-    if (p < HW && c < C) yn[(int64_t)p * C + c] = __float2bfloat16_rn(tile[threadIdx.x][i]);
+    if (p < HW && c < C) yn[(int64_t)p * C + c] = f32_to_elem<F16>(tile[threadIdx.x][i]);
   }
 }
 
-__global__ void nhwc_to_nchw_kernel(const bf16 *__restrict__ x, float *__restrict__ y, int C,
+template <bool F16>
+__global__ void nhwc_to_nchw_kernel(const uint16_t *__restrict__ x, float *__restrict__ y, int C,
                                     int HW) {
   __shared__ float tile[32][33];
   const int n = blockIdx.z;
   const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
-  const bf16 *xn = x + (int64_t)n * C * HW;
+  const uint16_t *xn = x + (int64_t)n * C * HW;
   float *yn = y + (int64_t)n * C * HW;
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
     const int p = p0 + i, c = c0 + threadIdx.x;
-    tile[i][threadIdx.x] = (p < HW && c < C) ? __bfloat162float(xn[(int64_t)p * C + c]) : 0.0f;
+    tile[i][threadIdx.x] = (p < HW && c < C) ? elem_to_f32<F16>(xn[(int64_t)p * C + c]) : 0.0f;
   }
   __syncthreads();
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -94,47 +177,52 @@ __global__ void nhwc_to_nchw_kernel(const bf16 *__restrict__ x, float *__restric
   }
 }
 
-void launch_nchw_f32_to_nhwc_bf16(const float *x, bf16 *y, int N, int C, int H, int W,
+void launch_nchw_f32_to_nhwc_bf16(const float *x, bf16 *y, int N, int C, int H, int W, bool f16,
                                   cudaStream_t s) {
   const int HW = H * W;
   if ((int64_t)N * C * HW == 0) return;
   dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
-  nchw_to_nhwc_kernel<<<grid, block, 0, s>>>(x, y, C, HW);
+  if (f16) nchw_to_nhwc_kernel<true><<<grid, block, 0, s>>>(x, (uint16_t *)y, C, HW);
+  else nchw_to_nhwc_kernel<false><<<grid, block, 0, s>>>(x, (uint16_t *)y, C, HW);
   count(CNT_LAUNCHES);
 }
 
-void launch_nhwc_bf16_to_nchw_f32(const bf16 *x, float *y, int N, int C, int H, int W,
+void launch_nhwc_bf16_to_nchw_f32(const bf16 *x, float *y, int N, int C, int H, int W, bool f16,
                                   cudaStream_t s) {
   const int HW = H * W;
   if ((int64_t)N * C * HW == 0) return;
   dim3 grid((HW + 31) / 32, (C + 31) / 32, N), block(32, 8);
-  nhwc_to_nchw_kernel<<<grid, block, 0, s>>>(x, y, C, HW);
+  if (f16) nhwc_to_nchw_kernel<true><<<grid, block, 0, s>>>((const uint16_t *)x, y, C, HW);
+  else nhwc_to_nchw_kernel<false><<<grid, block, 0, s>>>((const uint16_t *)x, y, C, HW);
   count(CNT_LAUNCHES);
 }
 
-__global__ void f32_to_bf16_kernel(const float *__restrict__ x, bf16 *__restrict__ y, int64_t n) {
+template <bool F16>
+__global__ void f32_to_bf16_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, int64_t n) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
        i += (int64_t)gridDim.x * blockDim.x)
-    y[i] = __float2bfloat16_rn(x[i]);
+    y[i] = f32_to_elem<F16>(x[i]);
 }
 
-void launch_f32_to_bf16(const float *x, bf16 *y, int64_t n, cudaStream_t s) {
+void launch_f32_to_bf16(const float *x, bf16 *y, int64_t n, bool f16, cudaStream_t s) {
   if (n == 0) return;
-  f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, s>>>(x, y, n);
+  if (f16) f32_to_bf16_kernel<true><<<grid_for(n, 256), 256, 0, s>>>(x, (uint16_t *)y, n);
+  else f32_to_bf16_kernel<false><<<grid_for(n, 256), 256, 0, s>>>(x, (uint16_t *)y, n);
   count(CNT_LAUNCHES);
 }
 
 // ---------------------------------------------------------------------------
 // out = act(a + b + bias[c]);  b and bias optional.  8 channels per thread.
 // ---------------------------------------------------------------------------
+template <bool F16>
 __global__ void add_act_bf16_kernel(const bf16x8 *a, const bf16x8 *b, const float *bias_c, int C8,
                                     bf16x8 *out, int64_t n8, int act, float lo, float hi) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8;
        i += (int64_t)gridDim.x * blockDim.x) {
     float f[8], g2[8];
-    unpack8(a[i], f);
+    unpack8<F16>(a[i], f);
     if (b) {
-      unpack8(b[i], g2);
+      unpack8<F16>(b[i], g2);
 #pragma unroll
       for (int k = 0; k < 8; ++k) f[k] += g2[k];
     }
@@ -146,15 +234,19 @@ __global__ void add_act_bf16_kernel(const bf16x8 *a, const bf16x8 *b, const floa
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) f[k] = act_apply_b(f[k], act, lo, hi);
-    out[i] = pack8(f);
+    out[i] = pack8<F16>(f);
   }
 }
 
 void launch_add_act_bf16(const bf16 *a, const bf16 *b, const float *bias_c, int C, bf16 *out,
-                         int64_t n, int act, float lo, float hi, cudaStream_t s) {
+                         int64_t n, int act, float lo, float hi, bool f16, cudaStream_t s) {
   if (n == 0) return;
-  add_act_bf16_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>(
-      (const bf16x8 *)a, (const bf16x8 *)b, bias_c, C / 8, (bf16x8 *)out, n / 8, act, lo, hi);
+  if (f16)
+    add_act_bf16_kernel<true><<<grid_for(n / 8, 256), 256, 0, s>>>(
+        (const bf16x8 *)a, (const bf16x8 *)b, bias_c, C / 8, (bf16x8 *)out, n / 8, act, lo, hi);
+  else
+    add_act_bf16_kernel<false><<<grid_for(n / 8, 256), 256, 0, s>>>(
+        (const bf16x8 *)a, (const bf16x8 *)b, bias_c, C / 8, (bf16x8 *)out, n / 8, act, lo, hi);
   count(CNT_LAUNCHES);
 }
 
@@ -162,7 +254,7 @@ void launch_add_act_bf16(const bf16 *a, const bf16 *b, const float *bias_c, int 
 // Pooling on NHWC: one thread per (n, p, q, 8 channels); consecutive threads take
 // consecutive channel groups, so every access of a warp is one contiguous run.
 // ---------------------------------------------------------------------------
-template <bool AVG>
+template <bool AVG, bool F16>
 __global__ void __launch_bounds__(256) pool_bf16_kernel(const bf16x8 *__restrict__ x,
                                                         bf16x8 *__restrict__ y, int C8, int H,
                                                         int W, int P, int Q, int kh, int kw,
@@ -183,17 +275,17 @@ __global__ void __launch_bounds__(256) pool_bf16_kernel(const bf16x8 *__restrict
       for (int h = h0; h < h1; ++h)
         for (int ww = w0; ww < w1; ++ww) {
           float f[8];
-          unpack8(x[((n * H + h) * W + ww) * C8 + c8], f);
+          unpack8<F16>(x[((n * H + h) * W + ww) * C8 + c8], f);
 #pragma unroll
           for (int k = 0; k < 8; ++k) sum[k] += f[k];
         }
       const float inv = 1.0f / (float)(kh * kw);
 #pragma unroll
       for (int k = 0; k < 8; ++k) sum[k] *= inv;
-      y[i] = pack8(sum);
+      y[i] = pack8<F16>(sum);
     } else {
-      // max of bf16 pairs directly (NaN-propagating), no conversion round trip
-      const __nv_bfloat162 ninf = __float2bfloat162_rn(-INFINITY);
+      // max of 16-bit pairs directly (NaN-propagating), no conversion round trip
+      const uint32_t ninf = f32_to_pair<F16>(-INFINITY, -INFINITY);
       bf16x8 m;
 #pragma unroll
       for (int k = 0; k < 4; ++k) m.v[k] = ninf;
@@ -201,7 +293,7 @@ __global__ void __launch_bounds__(256) pool_bf16_kernel(const bf16x8 *__restrict
         for (int ww = w0; ww < w1; ++ww) {
           const bf16x8 v = x[((n * H + h) * W + ww) * C8 + c8];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) m.v[k] = __hmax2_nan(m.v[k], v.v[k]);
+          for (int k = 0; k < 4; ++k) m.v[k] = pair_max_nan<F16>(m.v[k], v.v[k]);
         }
       y[i] = m;
     }
@@ -214,7 +306,7 @@ __global__ void __launch_bounds__(256) pool_bf16_kernel(const bf16x8 *__restrict
 // maximum is unchanged; the average masks it to zero), which leaves no branch between the loads.
 // Neighbouring windows overlap in the L1.  The grid is (chunks of one image's outputs) x images, so
 // a thread needs two short divisions only.
-template <int K, int S, bool AVG>
+template <int K, int S, bool AVG, bool F16>
 __global__ void __launch_bounds__(256) pool_win_bf16_kernel(const bf16x8 *__restrict__ x,
                                                             bf16x8 *__restrict__ y, int C8, int H,
                                                             int W, int Q, int pad_h, int pad_w,
@@ -246,13 +338,13 @@ __global__ void __launch_bounds__(256) pool_win_bf16_kernel(const bf16x8 *__rest
       for (int c = 0; c < K; ++c) {
         const bool in = (unsigned)(h0 + r) < (unsigned)H && (unsigned)(w0 + c) < (unsigned)W;
         float f[8];
-        unpack8(v[r][c], f);
+        unpack8<F16>(v[r][c], f);
 #pragma unroll
         for (int k = 0; k < 8; ++k) sum[k] += in ? f[k] : 0.0f;
       }
 #pragma unroll
     for (int k = 0; k < 8; ++k) sum[k] *= 1.0f / (float)(K * K);
-    out = pack8(sum);
+    out = pack8<F16>(sum);
   } else {
     out = v[0][0];
 #pragma unroll
@@ -260,46 +352,51 @@ __global__ void __launch_bounds__(256) pool_win_bf16_kernel(const bf16x8 *__rest
 #pragma unroll
       for (int c = 0; c < K; ++c)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) out.v[k] = __hmax2_nan(out.v[k], v[r][c].v[k]);
+        for (int k = 0; k < 4; ++k) out.v[k] = pair_max_nan<F16>(out.v[k], v[r][c].v[k]);
   }
   y[(int64_t)n * per_image + j] = out;
 }
 
 template <int K, int S>
 static void launch_pool_win(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P, int Q,
-                            int pad_h, int pad_w, bool avg, cudaStream_t s) {
+                            int pad_h, int pad_w, bool avg, bool f16, cudaStream_t s) {
   const unsigned per_image = (unsigned)((int64_t)P * Q * (C / 8));
   const unsigned chunks = (per_image + 255u) / 256u;
   const unsigned grid = chunks * (unsigned)N;
-  if (avg)
-    pool_win_bf16_kernel<K, S, true><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, Q,
-                                                         pad_h, pad_w, per_image, chunks);
-  else
-    pool_win_bf16_kernel<K, S, false><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, Q,
-                                                          pad_h, pad_w, per_image, chunks);
+  auto go = [&](auto kern) {
+    kern<<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, Q, pad_h, pad_w, per_image,
+                              chunks);
+  };
+  if (avg && f16) go(pool_win_bf16_kernel<K, S, true, true>);
+  else if (avg) go(pool_win_bf16_kernel<K, S, true, false>);
+  else if (f16) go(pool_win_bf16_kernel<K, S, false, true>);
+  else go(pool_win_bf16_kernel<K, S, false, false>);
   count(CNT_LAUNCHES);
 }
 
 void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P, int Q, int kh,
-                      int kw, int pad_h, int pad_w, int sh, int sw, bool avg, cudaStream_t s) {
+                      int kw, int pad_h, int pad_w, int sh, int sw, bool avg, bool f16,
+                      cudaStream_t s) {
   const int64_t total = (int64_t)N * P * Q * (C / 8);
   if (total == 0) return;
   // every window lies at least partly inside the image and the per-image index fits 32 bits
   if (kh == kw && sh == sw && pad_h < kh && pad_w < kw && (P - 1) * sh - pad_h < H &&
       (Q - 1) * sw - pad_w < W && (int64_t)P * Q * (C / 8) < (1ll << 31) - 256 &&
       ((int64_t)P * Q * (C / 8) + 255) / 256 * N < (1ll << 31)) {
-    if (kh == 3 && sh == 2) return launch_pool_win<3, 2>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
-    if (kh == 2 && sh == 2) return launch_pool_win<2, 2>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
-    if (kh == 3 && sh == 1) return launch_pool_win<3, 1>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
-    if (kh == 2 && sh == 1) return launch_pool_win<2, 1>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, s);
+    if (kh == 3 && sh == 2) return launch_pool_win<3, 2>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, f16, s);
+    if (kh == 2 && sh == 2) return launch_pool_win<2, 2>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, f16, s);
+    if (kh == 3 && sh == 1) return launch_pool_win<3, 1>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, f16, s);
+    if (kh == 2 && sh == 1) return launch_pool_win<2, 1>(x, y, N, C, H, W, P, Q, pad_h, pad_w, avg, f16, s);
   }
   const int grid = grid_for(total, 256);
-  if (avg)
-    pool_bf16_kernel<true><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, P, Q,
-                                                kh, kw, pad_h, pad_w, sh, sw, total);
-  else
-    pool_bf16_kernel<false><<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, P, Q,
-                                                 kh, kw, pad_h, pad_w, sh, sw, total);
+  auto go = [&](auto kern) {
+    kern<<<grid, 256, 0, s>>>((const bf16x8 *)x, (bf16x8 *)y, C / 8, H, W, P, Q, kh, kw, pad_h, pad_w, sh,
+                              sw, total);
+  };
+  if (avg && f16) go(pool_bf16_kernel<true, true>);
+  else if (avg) go(pool_bf16_kernel<true, false>);
+  else if (f16) go(pool_bf16_kernel<false, true>);
+  else go(pool_bf16_kernel<false, false>);
   count(CNT_LAUNCHES);
 }
 
@@ -308,6 +405,7 @@ void launch_pool_bf16(const bf16 *x, bf16 *y, int N, int C, int H, int W, int P,
 // pixels with 16-byte loads (a warp covers 4 pixels x 128 bytes), partial sums meet in shared
 // memory.
 constexpr int GAP_ROWS = 16;
+template <bool F16>
 __global__ void __launch_bounds__(8 * GAP_ROWS) gap_bf16_kernel(const bf16x8 *__restrict__ x,
                                                                float *__restrict__ y, int HW, int C8) {
   __shared__ float part[GAP_ROWS][8][8];
@@ -319,7 +417,7 @@ __global__ void __launch_bounds__(8 * GAP_ROWS) gap_bf16_kernel(const bf16x8 *__
     const bf16x8 *xp = x + n * HW * C8 + c8;
     for (int p = prow; p < HW; p += GAP_ROWS) {
       float f[8];
-      unpack8(xp[(int64_t)p * C8], f);
+      unpack8<F16>(xp[(int64_t)p * C8], f);
 #pragma unroll
       for (int k = 0; k < 8; ++k) acc[k] += f[k];
     }
@@ -337,11 +435,12 @@ __global__ void __launch_bounds__(8 * GAP_ROWS) gap_bf16_kernel(const bf16x8 *__
   }
 }
 
-void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t s) {
+void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, bool f16, cudaStream_t s) {
   if ((int64_t)N * C == 0) return;
   const int C8 = C / 8;
   const dim3 grid((unsigned)((C8 + 7) / 8), (unsigned)N);
-  gap_bf16_kernel<<<grid, 8 * GAP_ROWS, 0, s>>>((const bf16x8 *)x, y, HW, C8);
+  if (f16) gap_bf16_kernel<true><<<grid, 8 * GAP_ROWS, 0, s>>>((const bf16x8 *)x, y, HW, C8);
+  else gap_bf16_kernel<false><<<grid, 8 * GAP_ROWS, 0, s>>>((const bf16x8 *)x, y, HW, C8);
   count(CNT_LAUNCHES);
 }
 
@@ -351,7 +450,7 @@ void launch_gap_bf16(const bf16 *x, float *y, int N, int HW, int C, cudaStream_t
 // ---------------------------------------------------------------------------
 // CLAMP: the activation is identity / ReLU / Clip, applied as a clamp to [lo, hi] (the general
 // switch drags the transcendental activations' code into the loop).
-template <bool CLAMP>
+template <bool CLAMP, bool F16>
 __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float *__restrict__ w,
                                       const float *__restrict__ bias, bf16x8 *__restrict__ y,
                                       ConvGeom g, int64_t total, float lo, float hi) {
@@ -381,7 +480,7 @@ __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float 
         const int ww = q * g.stride_w - g.pad_w + s2;
         if (ww < 0 || ww >= g.W) continue;
         float f[8];
-        unpack8(x[((n * g.H + h) * g.W + ww) * C8 + c8], f);
+        unpack8<F16>(x[((n * g.H + h) * g.W + ww) * C8 + c8], f);
         const float4 *wp = (const float4 *)(w + (int64_t)(r * g.S + s2) * g.C + c8 * 8);
         const float4 w0 = wp[0], w1 = wp[1];
         acc[0] = fmaf(f[0], w0.x, acc[0]); acc[1] = fmaf(f[1], w0.y, acc[1]);
@@ -393,7 +492,7 @@ __global__ void depthwise_bf16_kernel(const bf16x8 *__restrict__ x, const float 
 #pragma unroll
     for (int k = 0; k < 8; ++k)
       acc[k] = CLAMP ? fminf(fmaxf(acc[k], lo), hi) : act_apply_b(acc[k], g.act, g.lo, g.hi);
-    y[i] = pack8(acc);
+    y[i] = pack8<F16>(acc);
   }
 }
 
@@ -427,29 +526,30 @@ __device__ __forceinline__ uint64_t dw_add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-// two bf16 values in one word -> the fp32 pair (a bf16 is the top half of the fp32 of that value)
-__device__ __forceinline__ uint64_t dw_unpack(uint32_t v) { return dw_pair(v << 16, v & 0xffff0000u); }
-// fp32 pair -> clamp -> two bf16 in one word
+// two 16-bit values in one word -> the fp32 pair
+template <bool F16>
+__device__ __forceinline__ uint64_t dw_unpack(uint32_t v) {
+  const float2 t = pair_to_f32<F16>(v);
+  return dw_pair(__float_as_uint(t.x), __float_as_uint(t.y));
+}
+// fp32 pair -> clamp -> two 16-bit values in one word
+template <bool F16>
 __device__ __forceinline__ uint32_t dw_finish(uint64_t acc, float lo, float hi) {
   float a, b;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(acc));
   a = fminf(fmaxf(a, lo), hi);
   b = fminf(fmaxf(b, lo), hi);
-  const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<const uint32_t *>(&r);
+  return f32_to_pair<F16>(a, b);
 }
-// The same for bounds that bf16 holds exactly (lower bound 0 or none): the lower bound rides on
-// the conversion, the upper one is a packed minimum after it.  flags: 1 = lower bound 0,
-// 2 = upper bound present (hi2 holds it twice).
+// The same for bounds that the element type holds exactly (lower bound 0 or none): the lower
+// bound rides on the conversion, the upper one is a packed minimum after it.  flags: 1 = lower
+// bound 0, 2 = upper bound present (hi2 holds it twice).
+template <bool F16>
 __device__ __forceinline__ uint32_t dw_finish_packed(uint64_t acc, int flags, uint32_t hi2) {
   float a, b;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(acc));
-  uint32_t r;
-  if (flags & 1)
-    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
-  else
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
-  if (flags & 2) asm("min.bf16x2 %0, %0, %1;" : "+r"(r) : "r"(hi2));
+  uint32_t r = (flags & 1) ? f32_to_pair_relu<F16>(a, b) : f32_to_pair<F16>(a, b);
+  if (flags & 2) r = pair_min<F16>(r, hi2);
   return r;
 }
 template <int NP>
@@ -458,7 +558,7 @@ struct DwRow {
 };
 
 // CH = channels per thread: 4 (two CTAs per SM); 2 also compiles (four CTAs per SM) but is slower.
-template <int ST, bool PACKED_ACT, int CH>
+template <int ST, bool PACKED_ACT, int CH, bool F16>
 __global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel(
     const uint4 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
     uint32_t *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c, int ntiles,
@@ -579,10 +679,10 @@ __global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel
           const uint32_t *sp = src + (ih * IW + k) * G * 4;
           if (NP == 2) {
             const uint2 v = *reinterpret_cast<const uint2 *>(sp);
-            r.v[k][0] = dw_unpack(v.x);
-            r.v[k][NP - 1] = dw_unpack(v.y);
+            r.v[k][0] = dw_unpack<F16>(v.x);
+            r.v[k][NP - 1] = dw_unpack<F16>(v.y);
           } else {
-            r.v[k][0] = dw_unpack(*sp);
+            r.v[k][0] = dw_unpack<F16>(*sp);
           }
         }
       };
@@ -604,7 +704,8 @@ __global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel
           const uint64_t f = dw_add2(dw_add2(fa, fb), fc);
           // the activations this kernel takes are all a clamp (a switch over every activation,
           // inlined into each unrolled copy of this body, would not fit the instruction cache)
-          o[j] = PACKED_ACT ? dw_finish_packed(f, act_flags, act_hi2) : dw_finish(f, act_lo, act_hi);
+          o[j] = PACKED_ACT ? dw_finish_packed<F16>(f, act_flags, act_hi2)
+                            : dw_finish<F16>(f, act_lo, act_hi);
         }
         uint32_t *yp = yout + (int64_t)p * g.Q * C8 * 4;
         if (NP == 2) *reinterpret_cast<uint2 *>(yp) = make_uint2(o[0], o[NP - 1]);
@@ -643,7 +744,7 @@ __global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel
 }
 
 void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias, bf16 *y,
-                           const ConvGeom &g, cudaStream_t s) {
+                           const ConvGeom &g, bool f16, cudaStream_t s) {
   const int64_t total = (int64_t)g.N * g.P * g.Q * (g.C / 8);
   if (total == 0) return;
   const int C8 = g.C / 8;
@@ -655,10 +756,10 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
     // threads busy; among near-equal ones the widest channel run, for contiguous 16-byte pieces.
     const float act_lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
     const float act_hi = g.act == ACT_CLIP ? g.hi : INFINITY;
-    // bounds that bf16 holds exactly go through the packed conversion
-    const __nv_bfloat16 hb = __float2bfloat16_rn(act_hi);
+    // bounds that the element type holds exactly go through the packed conversion
+    const uint16_t hbits = host_elem_bits(act_hi, f16);
     const bool packed = (act_lo == 0.0f || act_lo == -INFINITY) &&
-                        (act_hi == INFINITY || __bfloat162float(hb) == act_hi);
+                        (act_hi == INFINITY || host_elem_value(hbits, f16) == act_hi);
     // Channels per thread: 4.  (2 halves the registers and doubles the resident CTAs, but the
     // kernel is bound by its instruction count, which grows: measured 1.4x slower.)
     const int CH = 4;
@@ -710,8 +811,6 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
       runs = (run_total + run_len - 1) / run_len;
       const unsigned grid = (unsigned)((int64_t)runs * base);
       const int act_flags = (act_lo == 0.0f ? 1 : 0) | (act_hi != INFINITY ? 2 : 0);
-      uint16_t hbits;
-      memcpy(&hbits, &hb, 2);
       const uint32_t act_hi2 = (uint32_t)hbits * 0x10001u;
       static unsigned char attr_done[64] = {};
       int dev = 0;
@@ -719,20 +818,32 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
       if (dev >= 0 && dev < 64 && !attr_done[dev]) {   // function attributes are per device
         attr_done[dev] = 1;
         const int lim = 100 * 1024;
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true, 4, false>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false, 4, false>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 4, false>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false, 4, false>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true, 4, true>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false, 4, true>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 4, true>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false, 4, true>, attr, lim);
       }
       auto go = [&](auto kern) {
         kern<<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint32_t *)y, g, G, cols, TH, tiles_q,
                                      tiles_c, ntiles, run_len, run_total, act_lo, act_hi, act_flags,
                                      act_hi2);
       };
-      if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true, 4>);
-      else if (ST == 1) go(depthwise3x3_tile_kernel<1, false, 4>);
-      else if (packed) go(depthwise3x3_tile_kernel<2, true, 4>);
-      else go(depthwise3x3_tile_kernel<2, false, 4>);
+      if (f16) {
+        if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true, 4, true>);
+        else if (ST == 1) go(depthwise3x3_tile_kernel<1, false, 4, true>);
+        else if (packed) go(depthwise3x3_tile_kernel<2, true, 4, true>);
+        else go(depthwise3x3_tile_kernel<2, false, 4, true>);
+      } else {
+        if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true, 4, false>);
+        else if (ST == 1) go(depthwise3x3_tile_kernel<1, false, 4, false>);
+        else if (packed) go(depthwise3x3_tile_kernel<2, true, 4, false>);
+        else go(depthwise3x3_tile_kernel<2, false, 4, false>);
+      }
       count(CNT_LAUNCHES);
       return;
     }
@@ -740,11 +851,18 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
   if (g.act == ACT_IDENTITY || g.act == ACT_RELU || g.act == ACT_CLIP) {
     const float lo = g.act == ACT_RELU ? 0.0f : (g.act == ACT_CLIP ? g.lo : -INFINITY);
     const float hi = g.act == ACT_CLIP ? g.hi : INFINITY;
-    depthwise_bf16_kernel<true><<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, w_rsc, bias,
-                                                                      (bf16x8 *)y, g, total, lo, hi);
+    if (f16)
+      depthwise_bf16_kernel<true, true><<<grid_for(total, 256), 256, 0, s>>>(
+          (const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g, total, lo, hi);
+    else
+      depthwise_bf16_kernel<true, false><<<grid_for(total, 256), 256, 0, s>>>(
+          (const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g, total, lo, hi);
+  } else if (f16) {
+    depthwise_bf16_kernel<false, true><<<grid_for(total, 256), 256, 0, s>>>(
+        (const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g, total, 0.f, 0.f);
   } else {
-    depthwise_bf16_kernel<false><<<grid_for(total, 256), 256, 0, s>>>((const bf16x8 *)x, w_rsc, bias,
-                                                                       (bf16x8 *)y, g, total, 0.f, 0.f);
+    depthwise_bf16_kernel<false, false><<<grid_for(total, 256), 256, 0, s>>>(
+        (const bf16x8 *)x, w_rsc, bias, (bf16x8 *)y, g, total, 0.f, 0.f);
   }
   count(CNT_LAUNCHES);
 }
@@ -753,23 +871,27 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
 // Weight packing (runs once per constant; results stay resident)
 // ---------------------------------------------------------------------------
 // [K][C][R*S] fp32 -> [R*S][K][Cp] bf16, channels c >= C (padding up to Cp) zero.
-__global__ void pack_krsc_kernel(const float *__restrict__ w, bf16 *__restrict__ out, int K, int C,
+template <bool F16>
+__global__ void pack_krsc_kernel(const float *__restrict__ w, uint16_t *__restrict__ out, int K, int C,
                                  int Cp, int RS, int64_t total) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int c = (int)(i % Cp);
     const int k = (int)((i / Cp) % K);
     const int t = (int)(i / ((int64_t)Cp * K));
-    out[i] = __float2bfloat16_rn(c < C ? w[((int64_t)k * C + c) * RS + t] : 0.0f);
+    out[i] = f32_to_elem<F16>(c < C ? w[((int64_t)k * C + c) * RS + t] : 0.0f);
   }
 }
 
-void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Cp,
+void launch_pack_krsc_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Cp, bool f16,
                            cudaStream_t s) {
   if (Cp < C) Cp = C;
   const int64_t total = (int64_t)K * Cp * R * S;
   if (total == 0) return;
-  pack_krsc_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, out, K, C, Cp, R * S, total);
+  if (f16)
+    pack_krsc_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(w, (uint16_t *)out, K, C, Cp, R * S, total);
+  else
+    pack_krsc_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(w, (uint16_t *)out, K, C, Cp, R * S, total);
   count(CNT_LAUNCHES);
 }
 
@@ -815,7 +937,8 @@ void launch_pack_dw_f32(const float *w, float *out, int C, int R, int S, cudaStr
 
 // Folded form for convolutions with very few input channels (the RGB stems): the S width
 // taps and the C channels of one filter row become Sp*Cp "channels" of a Rx1 convolution.
-__global__ void pack_fold_kernel(const float *__restrict__ w, bf16 *__restrict__ out, int K, int C,
+template <bool F16>
+__global__ void pack_fold_kernel(const float *__restrict__ w, uint16_t *__restrict__ out, int K, int C,
                                  int R, int S, int Sp, int Cp, int64_t total) {
   const int Cf = Sp * Cp;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
@@ -826,15 +949,18 @@ __global__ void pack_fold_kernel(const float *__restrict__ w, bf16 *__restrict__
     const int s2 = cf / Cp, c = cf % Cp;
     float v = 0.0f;
     if (s2 < S && c < C) v = w[(((int64_t)k * C + c) * R + r) * S + s2];
-    out[i] = __float2bfloat16_rn(v);
+    out[i] = f32_to_elem<F16>(v);
   }
 }
 
 void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S, int Sp, int Cp,
-                           cudaStream_t s) {
+                           bool f16, cudaStream_t s) {
   const int64_t total = (int64_t)R * K * Sp * Cp;
   if (total == 0) return;
-  pack_fold_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, out, K, C, R, S, Sp, Cp, total);
+  if (f16)
+    pack_fold_kernel<true><<<grid_for(total, 256), 256, 0, s>>>(w, (uint16_t *)out, K, C, R, S, Sp, Cp, total);
+  else
+    pack_fold_kernel<false><<<grid_for(total, 256), 256, 0, s>>>(w, (uint16_t *)out, K, C, R, S, Sp, Cp, total);
   count(CNT_LAUNCHES);
 }
 
@@ -842,7 +968,7 @@ void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S
 // One thread per 16-byte piece of an output row, eight image rows per CTA; CP is a template
 // parameter so that the index arithmetic is shifts, and reads of one channel are contiguous
 // along w.
-template <int CP>
+template <int CP, bool F16>
 __global__ void __launch_bounds__(256) pad_input_kernel(const float *__restrict__ x, bf16 *__restrict__ out, int C,
                                  int H, int W, int Wp, int pad_w, int64_t rows_total) {
   constexpr int ROWS = 8;                        // image rows per CTA
@@ -869,29 +995,33 @@ __global__ void __launch_bounds__(256) pad_input_kernel(const float *__restrict_
       float f[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) f[u] = on[u] ? xin[col[u]] : 0.0f;
-      __nv_bfloat162 v[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) v[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
       uint4 pk;
-      pk.x = *reinterpret_cast<uint32_t *>(&v[0]);
-      pk.y = *reinterpret_cast<uint32_t *>(&v[1]);
-      pk.z = *reinterpret_cast<uint32_t *>(&v[2]);
-      pk.w = *reinterpret_cast<uint32_t *>(&v[3]);
+      pk.x = f32_to_pair<F16>(f[0], f[1]);
+      pk.y = f32_to_pair<F16>(f[2], f[3]);
+      pk.z = f32_to_pair<F16>(f[4], f[5]);
+      pk.w = f32_to_pair<F16>(f[6], f[7]);
       *reinterpret_cast<uint4 *>(out + (nh * Wp * CP) + (int64_t)pc * 8) = pk;
     }
   }
 }
 
 void launch_pad_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Wp, int Cp,
-                           int pad_w, cudaStream_t s) {
+                           int pad_w, bool f16, cudaStream_t s) {
   const int pieces_row = Wp * Cp / 8;
   if ((int64_t)N * H * pieces_row == 0) return;
   const int threads = pieces_row >= 256 ? 256 : (pieces_row + 31) / 32 * 32;
   const int64_t rows = (int64_t)N * H;
   const unsigned grid = (unsigned)((rows + 7) / 8);
-  if (Cp == 4) pad_input_kernel<4><<<grid, threads, 0, s>>>(x, out, C, H, W, Wp, pad_w, rows);
-  else if (Cp == 8) pad_input_kernel<8><<<grid, threads, 0, s>>>(x, out, C, H, W, Wp, pad_w, rows);
-  else pad_input_kernel<16><<<grid, threads, 0, s>>>(x, out, C, H, W, Wp, pad_w, rows);
+  auto go = [&](auto kern) { kern<<<grid, threads, 0, s>>>(x, out, C, H, W, Wp, pad_w, rows); };
+  if (f16) {
+    if (Cp == 4) go(pad_input_kernel<4, true>);
+    else if (Cp == 8) go(pad_input_kernel<8, true>);
+    else go(pad_input_kernel<16, true>);
+  } else {
+    if (Cp == 4) go(pad_input_kernel<4, false>);
+    else if (Cp == 8) go(pad_input_kernel<8, false>);
+    else go(pad_input_kernel<16, false>);
+  }
   count(CNT_LAUNCHES);
 }
 

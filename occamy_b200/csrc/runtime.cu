@@ -48,6 +48,7 @@ Runtime &rt() {
   const char *m = getenv("OCCAMY_MATH");
   if (m && (!strcmp(m, "fp32") || !strcmp(m, "0"))) r->mode = MATH_FP32;
   if (m && (!strcmp(m, "bf16") || !strcmp(m, "1"))) r->mode = MATH_BF16;
+  if (m && (!strcmp(m, "fp16") || !strcmp(m, "f16") || !strcmp(m, "2"))) r->mode = MATH_F16;
   const char *l = getenv("OCCAMY_LOG");
   r->log = l && *l && strcmp(l, "0");
   const char *c = getenv("OCCAMY_CACHE_WEIGHTS");
@@ -89,10 +90,13 @@ TensorRec *reg_find(const void *p, uintptr_t *base) {
   return &it->second;
 }
 
-bool is_bf16(const void *p, int64_t n, int64_t c, int64_t h, int64_t w) {
+bool mode_f16() { return rt().mode == MATH_F16; }
+
+bool is_act16(const void *p, int64_t n, int64_t c, int64_t h, int64_t w) {
   uintptr_t base;
   TensorRec *rec = reg_find(p, &base);
-  return rec && base == (uintptr_t)p && rec->fmt == FMT_BF16_NHWC && rec->n == n && rec->c == c &&
+  const Fmt want = mode_f16() ? FMT_F16_NHWC : FMT_BF16_NHWC;
+  return rec && base == (uintptr_t)p && rec->fmt == want && rec->n == n && rec->c == c &&
          rec->h == h && rec->w == w;
 }
 
@@ -114,15 +118,16 @@ void mark_f32(void *p) {
   rec->host_src = nullptr;
 }
 
-void mark_bf16(void *p, int64_t n, int64_t c, int64_t h, int64_t w) {
+void mark_act16(void *p, int64_t n, int64_t c, int64_t h, int64_t w) {
   uintptr_t base;
   TensorRec *rec = reg_find(p, &base);
+  const Fmt fmt = mode_f16() ? FMT_F16_NHWC : FMT_BF16_NHWC;
   if (!rec || base != (uintptr_t)p) {
     // Unknown or interior pointer: record it as its own tensor of the fp32 extent.
-    reg_new(p, (size_t)(n * c * h * w) * 4, FMT_BF16_NHWC);
+    reg_new(p, (size_t)(n * c * h * w) * 4, fmt);
     rec = reg_find(p, &base);
   }
-  rec->fmt = FMT_BF16_NHWC;
+  rec->fmt = fmt;
   rec->n = n;
   rec->c = c;
   rec->h = h;
@@ -151,12 +156,12 @@ void ensure_f32(const void *p) {
                              r.stream));
     r.main_copies++;
     count(CNT_H2D_BYTES, (int64_t)rec->host_bytes);
-  } else if (rec->fmt == FMT_BF16_NHWC) {
+  } else if (fmt_is_16(rec->fmt)) {
     const size_t elems = (size_t)(rec->n * rec->c * rec->h * rec->w);
     void *tmp = scratch_get(3, elems * 2);
     OCC_CUDA(cudaMemcpyAsync(tmp, (void *)base, elems * 2, cudaMemcpyDeviceToDevice, r.stream));
     launch_nhwc_bf16_to_nchw_f32((const bf16 *)tmp, (float *)base, (int)rec->n, (int)rec->c,
-                                 (int)rec->h, (int)rec->w, r.stream);
+                                 (int)rec->h, (int)rec->w, rec->fmt == FMT_F16_NHWC, r.stream);
     count(CNT_MATERIALIZE);
   }
   rec->fmt = FMT_F32;

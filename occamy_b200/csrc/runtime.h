@@ -15,7 +15,10 @@
 
 namespace occ {
 
-enum MathMode { MATH_FP32 = 0, MATH_BF16 = 1 };
+// Arithmetic of the convolution / GEMM kernels and storage of the activations between them:
+// fp32 NCHW throughout; or tensor cores on 16-bit NHWC activations, bf16 (8 mantissa bits, fp32's
+// range) or fp16 (11 mantissa bits, values up to 65504).
+enum MathMode { MATH_FP32 = 0, MATH_BF16 = 1, MATH_F16 = 2 };
 
 // Format of the bytes behind a caller-owned device pointer.
 enum Fmt {
@@ -23,13 +26,15 @@ enum Fmt {
   FMT_ZERO = 1,       // freshly handed out; reads as zero, memset not yet issued
   FMT_BF16_NHWC = 2,  // produced by a tensor-core-mode kernel: bf16, NHWC, dims below
   FMT_PENDING = 3,    // host->device upload deferred (constant already packed on device)
-  FMT_ELIDED = 4      // never written: a cross-call fusion skipped it (reading it is an error)
+  FMT_ELIDED = 4,     // never written: a cross-call fusion skipped it (reading it is an error)
+  FMT_F16_NHWC = 5    // like FMT_BF16_NHWC with fp16 elements (MATH_F16)
 };
+inline bool fmt_is_16(Fmt f) { return f == FMT_BF16_NHWC || f == FMT_F16_NHWC; }
 
 struct TensorRec {
   size_t bytes = 0;  // extent of the allocation handed to the caller
   Fmt fmt = FMT_F32;
-  int64_t n = 0, c = 0, h = 0, w = 0;  // logical NCHW dims when fmt == FMT_BF16_NHWC
+  int64_t n = 0, c = 0, h = 0, w = 0;  // logical NCHW dims of a 16-bit NHWC tensor
   const void *host_src = nullptr;      // source of the last host->device upload, if any
   size_t host_bytes = 0;
   uint64_t host_hash = 0;
@@ -111,11 +116,15 @@ void reg_drop_range(void *p, size_t bytes);
 TensorRec *reg_find(const void *p, uintptr_t *base = nullptr);
 // Make the bytes behind p plain fp32 NCHW (memset, upload or layout conversion as needed).
 void ensure_f32(const void *p);
-// True when p is the base of a bf16 NHWC tensor with exactly these logical dims.
-bool is_bf16(const void *p, int64_t n, int64_t c, int64_t h, int64_t w);
-// Mark p as fully overwritten by an fp32 kernel / by a bf16 NHWC kernel.
+// True when p is the base of a 16-bit NHWC tensor with exactly these logical dims, stored in
+// the element type of the CURRENT mode (a tensor left behind in the other 16-bit type is
+// converted back to fp32 by its next reader, like any other foreign format).
+bool is_act16(const void *p, int64_t n, int64_t c, int64_t h, int64_t w);
+// Mark p as fully overwritten by an fp32 kernel / by a 16-bit NHWC kernel of the current mode.
 void mark_f32(void *p);
-void mark_bf16(void *p, int64_t n, int64_t c, int64_t h, int64_t w);
+void mark_act16(void *p, int64_t n, int64_t c, int64_t h, int64_t w);
+// The current mode stores fp16 (else bf16) in its 16-bit tensors.
+bool mode_f16();
 // A tensor that reads as zero and has not been written since it was handed out.
 bool is_zero(const void *p);
 

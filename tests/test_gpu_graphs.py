@@ -2,7 +2,10 @@
 against the CPU oracle evaluating the same graph on the same seeded tensors.
 
 fp32 mode: max relative error <= 1e-4 per output tensor.
-bf16 tensor-core mode: <= 2e-2 relative on the logits and identical top-1 indices.
+16-bit tensor-core modes: <= 2e-2 relative on the logits and identical top-1 indices -- bf16 for
+ResNet-50 and VGG-16, fp16 for MobileNetV2.  (Why not bf16 there: tests/test_mode_choice.py
+shows on the CPU that rounding nothing but the weights of this random-weight MobileNetV2 to
+bf16 already moves its logits by more than 2e-2.)
 """
 import numpy as np
 import pytest
@@ -76,17 +79,25 @@ def test_resnet50_unfused_no_pool_softmax(mode):
     np.testing.assert_allclose(y.sum(1), 1.0, rtol=1e-5)
 
 
-@pytest.mark.parametrize("mode", [rt.MATH_FP32, rt.MATH_BF16])
+@pytest.mark.parametrize("mode", [rt.MATH_FP32, rt.MATH_F16])
 @pytest.mark.parametrize("fuse", [replay.FUSE_NONE, replay.FUSE_WITH_CLIP])
 def test_mobilenet_v2(mode, fuse):
     g = graphs.mobilenet_v2(batch=2, seed=0, image=96)
     x = graphs.make_input(g, 0)
-    (y,), _ = run_both(g, x, mode, fuse)
+    (y,), _ = run_both(g, x, mode, fuse, repeats=2)
     (want,) = run_graph_oracle(g, x)
-    # bf16 activation storage alone (emulated on the CPU: every tensor rounded to bf16, fp32
-    # arithmetic) puts this 53-layer random-weight network 4.8e-2 from the fp32 result, so the
-    # 2e-2 bound that holds for ResNet-50 and VGG-16 cannot hold here; top-1 must still agree.
-    check_logits(y, want, mode, bf16_tol=8e-2)
+    check_logits(y, want, mode)
+
+
+def test_mobilenet_v2_bf16_runs_and_keeps_top1():
+    """bf16 mode on this network is outside the 2e-2 contract (8 mantissa bits are not enough,
+    whatever the kernels do) but it must still run and rank the classes the same way."""
+    g = graphs.mobilenet_v2(batch=2, seed=0, image=96)
+    x = graphs.make_input(g, 0)
+    (y,), _ = run_both(g, x, rt.MATH_BF16, replay.FUSE_WITH_CLIP, repeats=2)
+    (want,) = run_graph_oracle(g, x)
+    assert max_rel_err(y, want) <= 8e-2
+    assert top1_agrees(y, want)[0]
 
 
 @pytest.mark.parametrize("mode", [rt.MATH_FP32, rt.MATH_BF16])
@@ -144,7 +155,7 @@ def test_cross_call_fusion(case):
     reference's fusion on (plus the stem convolution with its max pool); conv + bias add +
     ReLU/Clip (+ residual) without it."""
     name, fuse, chains = case
-    rt.set_math_mode(rt.MATH_BF16)
+    rt.set_math_mode(rt.MATH_BF16 if name == "resnet50" else rt.MATH_F16)
     g = getattr(graphs, name)(batch=2, seed=4, image=64)
     x = graphs.make_input(g, 4)
     p = g.to_program()
@@ -160,14 +171,8 @@ def test_cross_call_fusion(case):
     (y2,) = p.run(b, x)
     assert n1 - n0 == chains
     assert np.array_equal(y1, y2)
-    tol = 2e-2 if name == "resnet50" else 8e-2
-    assert max_rel_err(y0, want) <= tol and max_rel_err(y1, want) <= tol
-    # top-1 must agree wherever the reference's winning margin exceeds the error actually seen
-    srt = np.sort(want, axis=1)
-    clear = (srt[:, -1] - srt[:, -2]) > 2 * np.abs(y1 - want).max()
-    assert np.array_equal(y1.argmax(1)[clear], want.argmax(1)[clear])
-    if name == "resnet50":
-        assert np.array_equal(y1.argmax(1), want.argmax(1))
+    assert max_rel_err(y0, want) <= 2e-2 and max_rel_err(y1, want) <= 2e-2
+    assert top1_agrees(y1, want) == (True, 0)
     # the fused replay issues fewer kernels than the call-by-call one
     p2 = g.to_program()
     p2.lower(fuse=fuse)
@@ -251,7 +256,7 @@ def test_offline_pool_plan_runs_the_same(name):
     """The runtime takes whatever offsets the caller planned: with the greedy-by-size plan
     (smaller pool, different aliasing between tensors) the result is the same bits as with
     the reference's first-fit plan, call by call and with cross-call fusion."""
-    rt.set_math_mode(rt.MATH_BF16)
+    rt.set_math_mode(rt.MATH_BF16 if name == "resnet50" else rt.MATH_F16)
     g = getattr(graphs, name)(batch=2, seed=5, image=64)
     x = graphs.make_input(g, 6)
     b = replay.Binding()

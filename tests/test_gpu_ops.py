@@ -2,8 +2,8 @@
 the CPU oracle on the same seeded inputs.
 
 Tolerances (per tensor, max|y - ref| / max|ref|):
-  fp32 mode            <= 1e-4
-  bf16 tensor-core mode <= 2e-2
+  fp32 mode                                <= 1e-4
+  bf16 and fp16 tensor-core modes          <= 2e-2
 """
 import numpy as np
 import pytest
@@ -15,8 +15,10 @@ from oracle import ref
 
 pytestmark = pytest.mark.gpu
 
-TOL = {rt.MATH_FP32: 1e-4, rt.MATH_BF16: 2e-2}
-MODES = [rt.MATH_FP32, rt.MATH_BF16]
+TOL = {rt.MATH_FP32: 1e-4, rt.MATH_BF16: 2e-2, rt.MATH_F16: 2e-2}
+MODES = [rt.MATH_FP32, rt.MATH_BF16, rt.MATH_F16]
+# output rounding of the 16-bit formats (one step of the stored value, relative)
+STEP = {rt.MATH_BF16: 2.0 ** -8, rt.MATH_F16: 2.0 ** -11}
 
 
 @pytest.fixture(autouse=True)
@@ -253,9 +255,10 @@ POOL16_CASES = [((2, 16, 12, 12), (2, 2), (0, 0), (2, 2)), ((2, 16, 13, 11), (3,
                 ((1, 16, 9, 9), (5, 5), (2, 2), (2, 2))]
 
 
+@pytest.mark.parametrize("mode", [rt.MATH_BF16, rt.MATH_F16])
 @pytest.mark.parametrize("case", POOL16_CASES)
 @pytest.mark.parametrize("avg", [False, True])
-def test_pool_on_tensor_core_mode_activations(case, avg):
+def test_pool_on_tensor_core_mode_activations(case, avg, mode):
     """Max and average pooling of a tensor that sits in the tensor-core mode's 16-bit NHWC
     format: the input is produced on the device by a 1x1 convolution, so the pool call takes
     the NHWC kernels (the fp32 NCHW ones are covered by test_pool).  Average pooling counts
@@ -263,7 +266,7 @@ def test_pool_on_tensor_core_mode_activations(case, avg):
     (cudnn/CUDNNAveragePoolFunc.cpp:43-60)."""
     shape, k, p, s = case
     N, Cc, H, W = shape
-    rt.set_math_mode(rt.MATH_BF16)
+    rt.set_math_mode(mode)
     r = rng(70 + H)
     x = r.uniform(-1, 1, shape).astype(np.float32)
     w = he(r, Cc, Cc, 1, 1)
@@ -275,11 +278,11 @@ def test_pool_on_tensor_core_mode_activations(case, avg):
     tw = ref.conv2d(x, w)
     want = ref.pool2d(tw, k, p, s, avg=avg, count_include_pad=True)
     assert y.shape == want.shape
-    assert max_rel_err(y, want) <= TOL[rt.MATH_BF16]
+    assert max_rel_err(y, want) <= TOL[mode]
     # against the pool of exactly what the device pooled: only the output rounding is left
     t16 = t.numpy()
     exact = ref.pool2d(t16, k, p, s, avg=avg, count_include_pad=True)
-    assert max_rel_err(y, exact) <= (4e-3 if avg else 0.0)
+    assert max_rel_err(y, exact) <= (STEP[mode] if avg else 0.0)
 
 
 def test_reshape_is_a_copy():
@@ -289,7 +292,7 @@ def test_reshape_is_a_copy():
         y = A.reshape(A.up(x), (2, 120)).numpy()
         assert np.array_equal(y, x.reshape(2, 120))
     # of a tensor-core mode tensor: NCHW order must come back (FC weights depend on it)
-    rt.set_math_mode(rt.MATH_BF16)
+    rt.set_math_mode(rt.MATH_F16)
     r = rng(14)
     x = r.uniform(-1, 1, (2, 16, 4, 4)).astype(np.float32)
     w = he(r, 16, 16, 1, 1)
@@ -448,3 +451,29 @@ def test_held_back_conv_with_a_bias_that_is_freed_early(bias_from):
             assert rt.last_error(clear=True) == 0
     finally:
         L.occamy_set_weight_cache(1)
+
+
+def test_fp16_mode_is_finer_than_bf16_and_overflows_to_infinity():
+    """The two 16-bit modes differ only in the element type: fp16 must be about eight times
+    closer to the fp32 result on data of ordinary magnitude, and a value beyond fp16's range
+    must come out as infinity (visible), not as a wrong finite number."""
+    r = rng(18)
+    x = r.uniform(-1, 1, (2, 64, 14, 14)).astype(np.float32)
+    w = he(r, 64, 64, 3, 3)
+    b = r.normal(0, 0.1, 64).astype(np.float32)
+    want = ref.conv2d(x, w, b, (1, 1), (1, 1), act=5)
+    errs = {}
+    for mode in (rt.MATH_BF16, rt.MATH_F16):
+        rt.set_math_mode(mode)
+        y = A.conv(A.up(x), A.up(w), A.up(b), (1, 1), (1, 1), act_mode=5).numpy()
+        errs[mode] = max_rel_err(y, want)
+    assert errs[rt.MATH_F16] <= 2e-3 and errs[rt.MATH_F16] * 3 < errs[rt.MATH_BF16]
+    rt.set_math_mode(rt.MATH_F16)
+    big = A.conv(A.up(x * 1e4), A.up(w * 1e3), A.up(b), (1, 1), (1, 1), act_mode=5).numpy()
+    assert np.isinf(big).any() and not np.isnan(big).any()
+    # a tensor left in one 16-bit type is read correctly after the mode changes
+    rt.set_math_mode(rt.MATH_BF16)
+    t = A.conv(A.up(x), A.up(w), A.up(b), (1, 1), (1, 1), act_mode=1)
+    rt.set_math_mode(rt.MATH_F16)
+    u = A.active(t, 1).numpy()
+    assert max_rel_err(u, np.maximum(want, 0)) <= 2e-2
