@@ -656,14 +656,16 @@ def write_per_layer(path, g, tc_ms, peaks, ms_step):
             break
         ms = tc_ms[idx]
         idx += 1
-        t_tensor = flops / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
+        t_tensor = flops / (peaks["bf16_tflops"] * 1e12) * 1e3   # burst: launches are timed alone
         t_hbm = byts / (peaks["hbm_gbs"] * 1e9) * 1e3
         bound = max(t_tensor, t_hbm)
         rows.append((name, flops / 1e9, byts / 1e6, ms, flops / ms / 1e9 if ms else 0,
                      byts / ms / 1e6 if ms else 0, "tensor" if t_tensor >= t_hbm else "hbm",
                      bound / ms if ms else 0))
     with open(path, "w") as f:
-        f.write(f"# {g.name}: per tensor-core launch, ms_per_step {ms_step:.3f}\n")
+        f.write(f"# {g.name}: per tensor-core launch, ms_per_step {ms_step:.3f}; peaks: "
+                f"{peaks['bf16_tflops']:.1f} TFLOP/s (burst cuBLAS bf16) and {peaks['hbm_gbs']:.1f} GB/s "
+                f"({peaks['source']}); frac = max(tensor time, HBM time) / measured time\n")
         f.write("# layer | GFLOP | MB (bf16 activations, incl. residual operand) | ms | TFLOP/s | GB/s | "
                 "bound | frac of roofline\n")
         for r in rows:

@@ -142,6 +142,8 @@ def run(batch=256, reps=20, only="", math=rt.MATH_BF16):
               lambda: L.DNNReduceFunc(h, 4, g.ptr, rt.dims(g.shape), gy.ptr, rt.dims(gy.shape), 5))
         g.buf.free()
     _rest(h, rng, B, L, timed, depthwise, sel)
+    if any("conv" in t for t in wanted):
+        _conv_rows(h, rng, B, L, timed, wanted)
     L.cudnnDestroy(h)
     return rows, peak, peak_src
 
@@ -161,6 +163,57 @@ def _elementwise_rows(a, h, rng, B, L, timed, pool):
     timed(f"average pool 2x2/2 [{B},256,56,56]", nb, call)
     del keep
     return a, b, out, n
+
+
+# (name, C, K, R, H, stride, residual): tensor-core convolution layers of ResNet-50; timed only when
+# named in `only` (they are the per-layer rows of bench.py's --per-layer table, one at a time)
+CONV_ROWS = [("conv3x3 256->256 @14", 256, 256, 3, 14, 1, False),
+             ("conv3x3 512->512 @7", 512, 512, 3, 7, 1, False),
+             ("conv3x3 128->128 @28", 128, 128, 3, 28, 1, False),
+             ("conv3x3 64->64 @56", 64, 64, 3, 56, 1, False),
+             ("conv1x1 1024->256 @14", 1024, 256, 1, 14, 1, False),
+             ("conv1x1 2048->512 @7", 2048, 512, 1, 7, 1, False),
+             ("conv1x1 256->1024 @14 +res", 256, 1024, 1, 14, 1, True),
+             ("conv1x1 512->2048 @7 +res", 512, 2048, 1, 7, 1, True),
+             ("conv1x1 64->256 @56 +res", 64, 256, 1, 56, 1, True),
+             ("conv1x1 512->128 @28", 512, 128, 1, 28, 1, False)]
+
+
+def _conv_rows(h, rng, B, L, timed, wanted):
+    """Fused convolution (+ bias + ReLU, + residual add through the call sequence a model
+    issues) on device-resident 16-bit tensors; algorithmic bytes as in the per-layer table."""
+    for name, Cc, K, R, H, st, res in CONV_ROWS:
+        if not any(t in name for t in wanted):
+            continue
+        x = _bf16_tensor(h, rng, B, Cc, H, H)
+        w = _T((K, Cc, R, R), rng.standard_normal((K, Cc, R, R), dtype=np.float32) * (2.0 / (Cc * R * R)) ** 0.5)
+        b = _T((K,), rng.standard_normal((K,), dtype=np.float32) * 0.01)
+        P = (H + 2 * (R // 2) - R) // st + 1
+        y = _T((B, K, P, P))
+        pads, strides = rt.dims((R // 2, R // 2)), rt.dims((st, st))
+        nbytes = 2 * (B * Cc * H * H + K * Cc * R * R + B * K * P * P) + 4 * K
+        if res:
+            r_ = _bf16_tensor(h, rng, B, K, P, P)
+            out = _T((B, K, P, P))
+            nbytes += 2 * B * K * P * P
+
+            def call():   # conv (identity) -> add residual -> ReLU: folds into one launch once seen
+                hh = C.c_void_p()
+                L.cudnnCreate(C.byref(hh))
+                L.DNNConvBiasActivFunc(hh, x.ptr, rt.dims(x.shape), w.ptr, rt.dims(w.shape), b.ptr,
+                                       rt.dims((1, K, 1, 1)), None, 0, 1, pads, strides, 5, y.ptr)
+                L.DNNTensorOpFunc(hh, 0, y.ptr, rt.dims(y.shape), 4, r_.ptr, rt.dims(y.shape), 4,
+                                  out.ptr, rt.dims(y.shape), 4, 1.0)
+                L.DNNActiveFunc(hh, out.ptr, rt.dims(y.shape), 1, out.ptr)
+                L.cudnnDestroy(hh)
+        else:
+            def call():
+                L.DNNConvBiasActivFunc(h, x.ptr, rt.dims(x.shape), w.ptr, rt.dims(w.shape), b.ptr,
+                                       rt.dims((1, K, 1, 1)), None, 0, 1, pads, strides, 1, y.ptr)
+        flops = 2.0 * B * K * P * P * Cc * R * R
+        timed(f"{name} [{B}] ({flops / 1e9:.1f} GFLOP)", nbytes, call)
+        for t in (x, w, b, y):
+            t.buf.free()
 
 
 def _rest(h, rng, B, L, timed, depthwise, sel):
