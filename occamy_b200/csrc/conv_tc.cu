@@ -432,6 +432,7 @@ struct Plan {
   int bn;
   int dc;    // channels per output slab
   bool pn;   // pixel-N variant
+  bool pair; // CTA-pair form: the grid is launched as clusters of two
   size_t smem;
   bool ok;
 };
@@ -518,7 +519,19 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
                               (a.R * a.S * a.Cf + 63) / 64, nsm);
   pl.bn = bn;
   p.tiles_k = (a.K + bn - 1) / bn;
-  p.total_tiles = p.tiles_w * p.tiles_h * p.tiles_n * p.tiles_k;
+  p.sp_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
+  // CTA pairs (see TC_MODE_PAIR) for the 256-channel tiles whose reduction is long enough for
+  // the operand traffic into shared memory to be what bounds them
+  const int ksteps64p = (a.R * a.S * a.Cf + 63) / 64;
+#ifdef OCCAMY_TUNING
+  static const bool pair_allowed = !(getenv("OCCAMY_TC_PAIR") && !strcmp(getenv("OCCAMY_TC_PAIR"), "0"));
+#else
+  constexpr bool pair_allowed = true;
+#endif
+  const bool pair = pair_allowed && !pn && !halo && !a.out_f32 && bn == 256 && ksteps64p >= 4 &&
+                    p.sp_tiles >= 2 && nsm >= 2;
+  pl.pair = pair;
+  p.total_tiles = (pair ? (p.sp_tiles + 1) / 2 : p.sp_tiles) * p.tiles_k;
   p.div_k = make_fastdiv(p.tiles_k);
   p.div_w = make_fastdiv(p.tiles_w);
   p.div_h = make_fastdiv(p.tiles_h);
@@ -568,7 +581,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   {
     const uint64_t dims[3] = {(uint64_t)a.Cf, (uint64_t)a.K, (uint64_t)(a.R * a.S)};
     const uint64_t st[2] = {(uint64_t)a.Cf * 2, (uint64_t)a.K * a.Cf * 2};
-    const uint32_t box[3] = {(uint32_t)bk, (uint32_t)bn, 1};
+    const uint32_t box[3] = {(uint32_t)bk, (uint32_t)(pair ? bn / 2 : bn), 1};
     ok &= make_map(&p.tmB, a.w, 3, dims, st, box, bk * 2, counted);
   }
   // For 256-wide tiles with a long reduction, 32-channel slabs free enough shared memory
@@ -584,6 +597,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
                       : ((a.residual ? TC_MODE_RES : 0) | (a.act == ACT_RELU ? 0 : TC_MODE_CLAMP) |
                          (halo ? TC_MODE_HALO : 0));
   if (a.f16) pl.mode |= TC_MODE_F16;
+  if (pair) pl.mode |= TC_MODE_PAIR;
   if (!a.out_f32) {
     const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
     const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};
@@ -594,7 +608,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   // shared memory: ring + output slabs + bias + barriers + alignment
   const size_t stage_bytes = pn     ? (size_t)(128 + 256) * bk * 2
                              : halo ? (size_t)p.halo_a_bytes
-                                    : 128 * bk * 2 + (size_t)bn * bk * 2;
+                                    : 128 * bk * 2 + (size_t)(pair ? bn / 2 : bn) * bk * 2;
   p.bias_floats = (a.K + bn - 1) / bn * bn;
   const size_t slab_bytes = (size_t)128 * dc * 2;
   const size_t fixed0 = pn ? 1024 + 2 * 256 * 128 + 8 * 80
@@ -649,7 +663,10 @@ static void launch_any(const Plan &pl, int num_sms, cudaStream_t s) {
     launch_plan_pn(pl, num_sms, s);
     return;
   }
-  const int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
+  int grid = pl.p.total_tiles < num_sms ? pl.p.total_tiles : num_sms;
+  if (pl.pair) {   // two CTAs per tile index, an even number of CTAs
+    grid = 2 * pl.p.total_tiles < num_sms ? 2 * pl.p.total_tiles : num_sms / 2 * 2;
+  }
   bool ok;
   switch (pl.bn) {
     case 32: ok = tc_launch_32_32(pl.p, pl.mode, grid, pl.smem, s); break;

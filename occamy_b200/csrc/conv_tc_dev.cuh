@@ -56,6 +56,8 @@ struct alignas(64) TcParams {
   int bias_floats;       // K rounded up to whole channel tiles: bias entries kept in shared memory
   int dbuf;              // output slab buffers in shared memory (3..8)
   int n_mma;             // pixel-N variant: N of the MMA (pixels per tile rounded up to 16)
+  int sp_tiles;          // pixel tiles (tiles_w * tiles_h * tiles_n); with TC_MODE_PAIR the tile
+                         // index counts PAIRS of them and total_tiles = ceil(sp_tiles / 2) * tiles_k
   int *err;
 };
 
@@ -73,6 +75,13 @@ constexpr int TC_MODE_HALO = 8;
 // Operands and output are fp16 instead of bf16 (same MMA kind, same rate, other format bits
 // in the instruction descriptor and other conversion instructions in the epilogue).
 constexpr int TC_MODE_F16 = 16;
+// Two CTAs on neighbouring SMs (a cluster of two) work as one 256-pixel x BN tile: each loads
+// its own 128 pixels of A and HALF of the B tile, the first CTA of the pair issues
+// tcgen05.mma.cta_group::2 instructions that read both halves, and each CTA's TMEM receives
+// the accumulator rows of its own pixels.  Shared memory takes in two thirds of the bytes per
+// flop of the single-CTA form, which is what bounds the long-reduction layers.  No multicast
+// load is involved: every TMA load has one destination.
+constexpr int TC_MODE_PAIR = 32;
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -178,6 +187,63 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *m, uint32_t src,
   asm volatile(
       "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(m),
       "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// ---- CTA-pair forms (TC_MODE_PAIR).  `bar` is a shared::cluster address, normally of a
+// barrier in the pair's first CTA; the data always lands in the issuing CTA's own memory.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap *m, uint32_t bar,
+                                                 int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *m, uint32_t bar,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(m), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_map(uint32_t cta_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Completion of the pair's MMAs so far, signalled on the barrier at this offset in both CTAs.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar),
+      "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void mma_lohi_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                              uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n.reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_map(const CUtensorMap *m) {
@@ -359,10 +425,19 @@ struct TcTile {
   int k0, q0, p0, n0;   // first output channel / column / row / image of the tile
 };
 // Tiles are numbered channel-tile fastest, then column, row and image tiles.
-template <int BN>
-__device__ __forceinline__ TcTile tc_decode(const TcParams &p, int tile) {
-  const uint32_t sp = tc_fdiv((uint32_t)tile, p.div_k);
+// In a CTA pair `rank` selects the pixel tile of the pair; the second CTA of an odd last pair
+// gets the first one's tile again (`ghost`): it computes it and stores nothing.
+template <int BN, bool PAIR = false>
+__device__ __forceinline__ TcTile tc_decode(const TcParams &p, int tile, uint32_t rank = 0,
+                                            bool *ghost = nullptr) {
+  uint32_t sp = tc_fdiv((uint32_t)tile, p.div_k);
   const uint32_t kt = (uint32_t)tile - sp * (uint32_t)p.tiles_k;
+  if constexpr (PAIR) {
+    sp = 2u * sp + rank;
+    const bool g = sp >= (uint32_t)p.sp_tiles;
+    if (g) sp -= 1u;
+    if (ghost) *ghost = g;
+  }
   const uint32_t s2 = tc_fdiv(sp, p.div_w);
   const uint32_t wq = sp - s2 * (uint32_t)p.tiles_w;
   const uint32_t nn = tc_fdiv(s2, p.div_h);
@@ -403,6 +478,8 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   constexpr bool F32 = (MODE & TC_MODE_F32) != 0;
   constexpr bool HALO = (MODE & TC_MODE_HALO) != 0;
   constexpr bool F16 = (MODE & TC_MODE_F16) != 0;
+  constexpr bool PAIR = (MODE & TC_MODE_PAIR) != 0;
+  static_assert(!(PAIR && (HALO || F32)), "the CTA-pair form exists for the plain epilogues only");
   constexpr int EPI_THREADS = 128 * EW;
   constexpr int STORE_WARP = 2 + 4 * EW;
   constexpr int CW = DC / EW;                  // channels one epilogue thread handles per slab
@@ -410,8 +487,9 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   constexpr int SLAB_BYTES = 128 * DC * 2;
   // fp32 accumulator; A and B formats: 1 = bf16, 0 = fp16; N / 8 and M / 16
   constexpr uint32_t IDESC = (1u << 4) | (F16 ? 0u : ((1u << 7) | (1u << 10))) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((PAIR ? 256 : 128) >> 4) << 24);
   constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr int BROWS = PAIR ? BN / 2 : BN;    // rows of the B tile this CTA loads
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -419,7 +497,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   const int bk = p.bk, stages = p.stages, dbuf = p.dbuf;
   // halo form: the ring carries input blocks only, the weights of all taps sit behind it
   const uint32_t a_bytes = HALO ? (uint32_t)p.halo_a_bytes : 128u * bk * 2u;
-  const uint32_t b_bytes = (uint32_t)BN * bk * 2u;
+  const uint32_t b_bytes = (uint32_t)BROWS * bk * 2u;
   const uint32_t sA = base;
   const uint32_t sB = sA + stages * a_bytes;
   const uint32_t sD = sB + (HALO ? (uint32_t)p.num_taps : (uint32_t)stages) * b_bytes;   // dbuf output slabs
@@ -440,6 +518,9 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 2 * stages + 6 + 2 * dbuf);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;     // 0: the CTA that issues the MMAs
+  const int tile0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tstep = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     // descriptor fetches are off the critical path of the first loads / stores
@@ -452,8 +533,9 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(tfull_bar(s), 1);
-      // one arrival per epilogue warp: arrivals on one barrier are serialised
-      mbar_init(tempty_bar(s), EPI_THREADS / 32);
+      // one arrival per epilogue warp (of both CTAs of a pair): arrivals on one barrier are
+      // serialised
+      mbar_init(tempty_bar(s), (PAIR ? 2 : 1) * EPI_THREADS / 32);
     }
     for (int s = 0; s < dbuf; ++s) {
       mbar_init(rfull_bar(s), 1);
@@ -464,14 +546,24 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32((const void *)tmem_holder)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {   // the same warp of both CTAs allocates for the pair
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32((const void *)tmem_holder)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32((const void *)tmem_holder)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  // both CTAs' barriers exist before either signals the other's
+  if constexpr (PAIR) cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   const int rows_valid = p.tw * p.th * p.tn;
@@ -481,7 +573,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   // previous kernel in the stream.  Resident weights may be fetched early as well: the
   // producer requests the weight tiles of its first k-steps (halo form: all of them) now.
   int pre_b = 0;   // leading k-steps of the first tile whose weight tile is already on its way
-  if (warp == 0 && lane == 0 && p.consts_ready && (int)blockIdx.x < p.total_tiles) {
+  if (!PAIR && warp == 0 && lane == 0 && p.consts_ready && (int)blockIdx.x < p.total_tiles) {
     if constexpr (HALO) {
       mbar_expect_tx(wfull_bar, (uint32_t)p.num_taps * b_bytes);
       for (int t = 0; t < p.num_taps; ++t)
@@ -533,14 +625,29 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
         }
       } else {
       const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + b_bytes;
-      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-        const TcTile tl = tc_decode<BN>(p, tile);
+      for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
+        const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank);
         for (int t = 0; t < p.num_taps && !err_code; ++t) {
           const TcTap tap = p.taps[t];
           for (int cb = 0; cb < p.cblocks; ++cb) {
             if (!mbar_wait_hot(empty_bar(stage), phase ^ 1u, abort_flag)) {
               err_code = 1;
               break;
+            }
+            if constexpr (PAIR) {
+              // Both CTAs' bytes are counted on the first CTA's barrier, which that CTA arms
+              // for the two of them; each CTA fetches its own pixels and its half of B.
+              const uint32_t fb = cluster_map(full_bar(stage), 0);
+              if (rank == 0) mbar_expect_tx(full_bar(stage), 2u * tx_bytes);
+              tma_load_3d_pair(sB + stage * b_bytes, &p.tmB, fb, cb * bk,
+                               tl.k0 + (int)rank * BROWS, t);
+              tma_load_4d_pair(sA + stage * a_bytes, &p.tmA[tap.map], fb, cb * bk, tl.q0 + tap.dw,
+                               tl.p0 + tap.dh, tl.n0);
+              if (++stage == stages) {
+                stage = 0;
+                phase ^= 1u;
+              }
+              continue;
             }
             if (pre_b > 0) {
               --pre_b;   // this stage's barrier is armed and its weight tile on its way
@@ -561,7 +668,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
     }
   } else if (warp == 1 || (HALO && warp == STORE_WARP + TC_NSTORE)) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       if constexpr (HALO) {
@@ -612,7 +719,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           tc_commit(tfull_bar(my_acc));
         }
       } else {
-      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
+      for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
         if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
           err_code = 2;
           break;
@@ -629,18 +736,24 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
           const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
           for (int kk = 0; kk < bk / 16; ++kk) {
-            tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
-                        accumulate);
+            if constexpr (PAIR)   // the same offsets in the other CTA hold its pixels and B half
+              mma_lohi_pair(d_tmem, (uint32_t)adesc + 2u * kk, (uint32_t)(adesc >> 32),
+                            (uint32_t)bdesc + 2u * kk, (uint32_t)(bdesc >> 32), IDESC, accumulate);
+            else
+              tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
+                          accumulate);
             accumulate = 1;
           }
-          tc_commit(empty_bar(stage));
+          if constexpr (PAIR) tc_commit_pair(empty_bar(stage));   // frees the stage in both CTAs
+          else tc_commit(empty_bar(stage));
           if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (err_code) break;
-        tc_commit(tfull_bar(acc));
+        if constexpr (PAIR) tc_commit_pair(tfull_bar(acc));
+        else tc_commit(tfull_bar(acc));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -660,15 +773,15 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
         auto nslab_of = [&](const TcTile &t) { return min(NSLAB, (p.K - t.k0 + DC - 1) / DC); };
         // cursor over the slabs this thread makes ready: (tile, slab) of slab number r_next
         uint32_t r_next = me;
-        int r_tile = blockIdx.x, r_sl = 0;
-        TcTile rt_ = tc_decode<BN>(p, r_tile);
+        int r_tile = tile0, r_sl = 0;
+        TcTile rt_ = tc_decode<BN, PAIR>(p, r_tile, rank);
         int r_ns = nslab_of(rt_);
         auto r_advance = [&]() {          // one slab further
           if (++r_sl == r_ns) {
             r_sl = 0;
-            r_tile += gridDim.x;
+            r_tile += tstep;
             if (r_tile < p.total_tiles) {
-              rt_ = tc_decode<BN>(p, r_tile);
+              rt_ = tc_decode<BN, PAIR>(p, r_tile, rank);
               r_ns = nslab_of(rt_);
             }
           }
@@ -689,8 +802,9 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
         };
         for (int i = 0; i < dbuf / TC_NSTORE; ++i) ready_one();     // every buffer starts out free
         uint32_t d = 0;   // running slab number
-        for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-          const TcTile tl = tc_decode<BN>(p, tile);
+        for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
+          bool ghost = false;
+          const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank, &ghost);
           const int nslab = nslab_of(tl);
           for (int sl = 0; sl < nslab; ++sl, ++d) {
             if (d % TC_NSTORE != me) continue;
@@ -699,7 +813,8 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
               err_code = 6;
               break;
             }
-            tma_store_4d(&p.tmD, sD + b * SLAB_BYTES, tl.k0 + sl * DC, tl.q0, tl.p0, tl.n0);
+            if (!ghost)   // the duplicate tile of an odd last pair is computed, not stored
+              tma_store_4d(&p.tmD, sD + b * SLAB_BYTES, tl.k0 + sl * DC, tl.q0, tl.p0, tl.n0);
             tma_store_commit();
             // The store has read its buffer out long before my next slab is written (the
             // other store thread's slab comes in between), so wait for that here and give
@@ -733,8 +848,8 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
     uint32_t acc_phase = 0;
     uint32_t buf = 0, buf_phase = 0;         // slab buffer the next slab goes through
 
-    for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-      const TcTile tl = tc_decode<BN>(p, tile);
+    for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
+      const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank);
       const int nslab = min(NSLAB, (p.K - tl.k0 + DC - 1) / DC);
       const float *bias_t = bias_s + tl.k0 + part * CW;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
@@ -748,7 +863,10 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
       auto release_acc = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(cluster_map(tempty_bar(acc), 0));
+          else mbar_arrive(tempty_bar(acc));
+        }
       };
       // one slab: r holds this thread's CW accumulator columns of slab sl
       auto slab = [&](const uint32_t *r, int sl) -> bool {
@@ -854,10 +972,18 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   }
   tc_fence_before();
   __syncthreads();
+  // neither CTA of a pair leaves (or frees TMEM) while the other may still signal its barriers
+  // or have MMAs reading its shared memory
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 2) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(TMEM_COLS)
-                 : "memory");
+    if constexpr (PAIR)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(TMEM_COLS)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(TMEM_COLS)
+                   : "memory");
   }
 }
 
@@ -869,20 +995,28 @@ bool tc_launch_128_64(const TcParams &p, int mode, int grid, size_t smem, cudaSt
 bool tc_launch_64_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
 bool tc_launch_32_32(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
 
-// Launch with programmatic stream serialisation (see pdl_wait).
+// Launch with programmatic stream serialisation (see pdl_wait); `cluster` > 1 launches the
+// grid as thread-block clusters of that many CTAs.
 template <typename Kernel, typename Params>
 inline void tc_launch_pdl(Kernel kernel, int grid, int threads, size_t smem, cudaStream_t s,
-                          const Params &p) {
+                          const Params &p, int cluster = 1) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3((unsigned)threads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
@@ -907,10 +1041,28 @@ inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t
     cudaFuncSetAttribute(tc_conv_kernel<BN, DC, TC_EW, MODE>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
   tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32 * TC_NSTORE + 32, smem,
-                s, p);
+                s, p, (MODE & TC_MODE_PAIR) ? 2 : 1);
 }
 template <int BN, int DC, bool WITH_F32, bool WITH_HALO = false>
 inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
+  if constexpr (BN == 256) {   // the CTA-pair flavours (bf16 and fp16, plain epilogues)
+    constexpr int P2 = TC_MODE_PAIR, H2 = TC_MODE_F16;
+    switch (mode) {
+      case P2: tc_launch_one<BN, DC, P2>(p, grid, smem, s); return true;
+      case P2 | TC_MODE_RES: tc_launch_one<BN, DC, P2 | TC_MODE_RES>(p, grid, smem, s); return true;
+      case P2 | TC_MODE_CLAMP: tc_launch_one<BN, DC, P2 | TC_MODE_CLAMP>(p, grid, smem, s); return true;
+      case P2 | TC_MODE_RES | TC_MODE_CLAMP:
+        tc_launch_one<BN, DC, P2 | TC_MODE_RES | TC_MODE_CLAMP>(p, grid, smem, s);
+        return true;
+      case P2 | H2: tc_launch_one<BN, DC, P2 | H2>(p, grid, smem, s); return true;
+      case P2 | H2 | TC_MODE_RES: tc_launch_one<BN, DC, P2 | H2 | TC_MODE_RES>(p, grid, smem, s); return true;
+      case P2 | H2 | TC_MODE_CLAMP: tc_launch_one<BN, DC, P2 | H2 | TC_MODE_CLAMP>(p, grid, smem, s); return true;
+      case P2 | H2 | TC_MODE_RES | TC_MODE_CLAMP:
+        tc_launch_one<BN, DC, P2 | H2 | TC_MODE_RES | TC_MODE_CLAMP>(p, grid, smem, s);
+        return true;
+      default: break;
+    }
+  }
   constexpr int H = TC_MODE_F16;
   switch (mode) {   // the fp16 flavours first (no halo form among them)
     case H: tc_launch_one<BN, DC, H>(p, grid, smem, s); return true;

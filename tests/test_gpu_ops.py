@@ -477,3 +477,28 @@ def test_fp16_mode_is_finer_than_bf16_and_overflows_to_infinity():
     rt.set_math_mode(rt.MATH_F16)
     u = A.active(t, 1).numpy()
     assert max_rel_err(u, np.maximum(want, 0)) <= 2e-2
+
+
+# Layers large enough for the planner to choose 256-channel tiles with a long reduction, which
+# run as CTA pairs (two SMs per 256-pixel tile).  101 images of 14 x 14 give an odd number of
+# 128-pixel tiles for the 1x1 case, so the last pair has only one real tile.
+PAIR_CASES = [(100, 256, 14, 14, 256, 3, 1), (101, 1024, 14, 14, 256, 1, 0), (37, 512, 7, 7, 768, 3, 1)]
+
+
+@pytest.mark.parametrize("mode", [rt.MATH_BF16, rt.MATH_F16])
+@pytest.mark.parametrize("case", PAIR_CASES)
+@pytest.mark.parametrize("act_mode", [1, 5])
+def test_conv_on_cta_pairs(case, mode, act_mode):
+    N, C, H, W, K, R, pad = case
+    r = rng(hash(case) % 2**31)
+    x = r.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = he(r, K, C, R, R)
+    b = r.normal(0, 0.5, K).astype(np.float32)
+    rt.set_math_mode(mode)
+    y = A.conv(A.up(x), A.up(w), A.up(b), (pad, pad), (1, 1), 1, act_mode).numpy()
+    want = ref.conv2d(x, w, b, (pad, pad), (1, 1), 1, act=act_mode)
+    assert max_rel_err(y, want) <= TOL[mode]
+    # every output pixel and channel was written by exactly the tile that owns it
+    assert np.isfinite(y).all()
+    err = np.abs(y - want).reshape(N, K, -1).max(axis=(1, 2)) / np.abs(want).max()
+    assert err.max() <= TOL[mode]
