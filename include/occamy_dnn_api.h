@@ -213,6 +213,11 @@ int64_t occamy_fused_chains(void);
 void occamy_set_cross_call_fusion(int on);
 /* Drop the resident packed-weight cache (forces re-upload and re-pack). */
 void occamy_clear_weight_cache(void);
+/* fp32 mode: 1 (default) runs dense convolutions (1x1 and 3x3, stride <= 2) and GEMMs on the
+ * tensor cores with every fp32 value carried as three bf16 parts and fp32 accumulation --
+ * the result stays within the fp32 mode's 1e-4 bound; 0 leaves the CUDA-core kernels.
+ * Same switch as the environment variable OCCAMY_FP32_TC=0|1. */
+void occamy_set_fp32_tensor_cores(int on);
 /* 0: keep no packed constants between calls (every filter is packed again on every use and
  * every constant upload crosses PCIe, as in the reference); 1 (default): keep them.  Same
  * switch as the environment variable OCCAMY_CACHE_WEIGHTS=0|1. */

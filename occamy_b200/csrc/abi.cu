@@ -64,7 +64,18 @@ void die(const char *what, cudaError_t e, size_t size) {
   exit(-1);
 }
 
-enum PackLayout { PACK_KRSC = 1, PACK_DW = 2, PACK_FOLD = 3, PACK_RAW = 4, PACK_STEM = 5 };
+enum PackLayout { PACK_KRSC = 1, PACK_DW = 2, PACK_FOLD = 3, PACK_RAW = 4, PACK_STEM = 5, PACK_SPLIT = 6 };
+// fp32 mode: dense convolutions and GEMMs on the tensor cores with split operands (see
+// launch_split3_nchw); off with OCCAMY_FP32_TC=0 or occamy_set_fp32_tensor_cores(0), which
+// leaves the CUDA-core kernels.
+int g_fp32_tc = -1;
+bool fp32_tc_enabled() {
+  if (g_fp32_tc < 0) {
+    const char *e = getenv("OCCAMY_FP32_TC");
+    g_fp32_tc = (e && !strcmp(e, "0")) ? 0 : 1;
+  }
+  return g_fp32_tc == 1;
+}
 
 // Device pointer of the packed form of the filter at `w`; resident across calls when the
 // filter was uploaded from host memory (a compiled model's constant), otherwise packed
@@ -81,7 +92,7 @@ void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int
   TensorRec *rec = reg_find(w, &base);
   const bool cacheable = r.cache_weights && rec && base == (uintptr_t)w && rec->host_src;
   // fp32 layouts are shared by the two 16-bit modes, 16-bit ones are packed per element type
-  const bool f16 = mode_f16() && layout != PACK_DW && layout != PACK_RAW;
+  const bool f16 = mode_f16() && layout != PACK_DW && layout != PACK_RAW && layout != PACK_SPLIT;
   WeightKey key{nullptr, 0, layout * 4096 + Sp * 64 + Cp + (f16 ? (1 << 20) : 0)};
   if (cacheable) {
     key.src = rec->host_src;
@@ -116,6 +127,7 @@ void *packed_weights(const float *w, int layout, size_t packed_bytes, int K, int
   else if (layout == PACK_RAW)
     OCC_CUDA(cudaMemcpyAsync(dst, w, packed_bytes, cudaMemcpyDeviceToDevice, r.stream));
   else if (layout == PACK_STEM) launch_pack_stem_bf16(w, (bf16 *)dst, C, R, S, Cp, Sp * Cp, r.stream);
+  else if (layout == PACK_SPLIT) launch_pack_krsc_split(w, (bf16 *)dst, K, C, R, S, Cp, r.stream);
   else launch_pack_fold_bf16(w, (bf16 *)dst, K, C, R, S, Sp, Cp, f16, r.stream);
   return dst;
 }
@@ -398,6 +410,46 @@ void elide(void *p) {
   trace_note_elided();
 }
 
+// fp32 mode on the tensor cores: x and the filter are carried as three bf16 parts each and the
+// six part products that matter are accumulated in fp32 (TMEM); the result is written as the
+// ABI's fp32 NCHW tensor by the kernel's epilogue.  False when the shape is outside what the
+// kernel takes (the CUDA-core kernel runs then).
+bool conv_f32_on_tensor_cores(const float *x, const float *w, const float *bias, const ConvGeom &g,
+                              float *y) {
+  Runtime &r = rt();
+  if (g.groups != 1 || g.R * g.S * 6 > 64) return false;
+  if (g.act != ACT_IDENTITY && g.act != ACT_RELU && g.act != ACT_CLIP) return false;
+  const int Cp = (g.C + 15) / 16 * 16;
+  TcConvArgs a;
+  memset(&a, 0, sizeof(a));
+  a.N = g.N; a.H = g.H; a.W = g.W; a.Cf = Cp; a.K = g.K; a.P = g.P; a.Q = g.Q; a.R = g.R; a.S = g.S;
+  a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
+  a.act = g.act; a.lo = g.lo; a.hi = g.hi;
+  a.split = 1;
+  a.out_f32 = y;
+  a.out_nchw = 1;
+  a.ldo = g.K;
+  a.x = (const bf16 *)16;
+  a.w = (const bf16 *)16;
+  if (!tc_conv_supported(a)) return false;
+  // Tiny problems stay on the CUDA-core kernel: three extra passes cost more than they save.
+  if ((double)g.N * g.P * g.Q * g.K * g.C * g.R * g.S < 1e6) return false;
+  ensure_f32(x);
+  bf16 *xs = (bf16 *)scratch_get(0, (size_t)3 * g.N * g.H * g.W * Cp * 2);
+  if (!xs) return false;
+  launch_split3_nchw(x, xs, g.N, g.C, Cp, g.H, g.W, r.stream);
+  const bf16 *ws = (const bf16 *)packed_weights(w, PACK_SPLIT, (size_t)6 * g.R * g.S * g.K * Cp * 2, g.K,
+                                                 g.C, g.R, g.S, 0, Cp);
+  if (!ws) return false;
+  a.x = xs;
+  a.w = ws;
+  a.bias = bias ? resident_f32(bias, (size_t)g.K * 4) : nullptr;
+  a.consts_ready = 0;
+  launch_tc_conv(a, r.stream);
+  mark_f32(y);
+  return true;
+}
+
 float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t *dW, float *bias,
                    int64_t groups, const int64_t *pads, const int64_t *strides, int act, float lo,
                    float hi, int64_t act_mode, float *y) {
@@ -464,6 +516,7 @@ float *conv_common(int sym, float *x, const int64_t *dX, float *w, const int64_t
       return y;
     }
   }
+  if (r.mode == MATH_FP32 && fp32_tc_enabled() && conv_f32_on_tensor_cores(x, w, bias, g, y)) return y;
   ensure_f32(x);
   ensure_f32(w);
   if (bias) ensure_f32(bias);
@@ -1088,6 +1141,34 @@ float *CUBLASMatmul2dFunc(int64_t /*rank*/, float *A, int64_t dimA[2], float *B,
       }
     }
   }
+  if (r.mode == MATH_FP32 && fp32_tc_enabled() && !transA && transB && alpha == 1.0f &&
+      (beta == 0.0f || out_zero) && M > 0 && (double)M * N * K >= 1e6) {
+    // the same split-operand scheme as the convolutions, as a 1x1 convolution over M "pixels"
+    const int Kp = (K + 15) / 16 * 16;
+    TcConvArgs a;
+    memset(&a, 0, sizeof(a));
+    a.N = 1; a.H = 1; a.W = M; a.Cf = Kp; a.K = N; a.P = 1; a.Q = M; a.R = 1; a.S = 1;
+    a.stride_h = a.stride_w = 1;
+    a.act = ACT_IDENTITY;
+    a.split = 1;
+    a.out_f32 = out;
+    a.ldo = N;
+    a.x = (const bf16 *)16;
+    a.w = (const bf16 *)16;
+    if (tc_conv_supported(a)) {
+      ensure_f32(A);
+      bf16 *as = (bf16 *)scratch_get(0, (size_t)3 * M * Kp * 2);
+      const bf16 *ws = (const bf16 *)packed_weights(B, PACK_SPLIT, (size_t)6 * N * Kp * 2, N, K, 1, 1, 0, Kp);
+      if (as && ws) {
+        launch_split3_rows(A, as, M, K, Kp, (int)dimA[1], r.stream);
+        a.x = as;
+        a.w = ws;
+        launch_tc_conv(a, r.stream);
+        mark_f32(out);
+        return out;
+      }
+    }
+  }
   ensure_f32(A);
   ensure_f32(B);
   if (beta != 0.0f) ensure_f32(out);
@@ -1219,6 +1300,8 @@ void occamy_set_cross_call_fusion(int on) {
   flush_pending();
   trace_set_enabled(on != 0);
 }
+
+void occamy_set_fp32_tensor_cores(int on) { g_fp32_tc = on ? 1 : 0; }
 
 void occamy_set_weight_cache(int on) {
   if (!on) occamy_clear_weight_cache();

@@ -402,10 +402,13 @@ bool tc_conv_supported(const TcConvArgs &a) {
   if (a.act != ACT_IDENTITY && a.act != ACT_RELU && a.act != ACT_CLIP) return false;
   if (a.stride_h < 1 || a.stride_w < 1 || a.stride_h > 2 || a.stride_w > 2) return false;
   if (a.w_step && ((a.w_step * 2) % 16 || (a.row_elems * 2) % 16 || a.S != 1)) return false;
-  if (a.R * a.S > TC_MAX_TAPS) return false;
+  if (a.R * a.S * (a.split ? 6 : 1) > TC_MAX_TAPS) return false;
   if (!a.out_f32 && a.K % 8 != 0) return false;
-  if (a.out_f32 && !(a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 &&
-                     a.pad_h == 0 && a.pad_w == 0 && !a.residual))
+  if (a.split && (!a.out_f32 || a.w_step || a.f16)) return false;
+  if (a.out_f32 && a.residual) return false;
+  // the row-major fp32 output is indexed by the flattened pixel number (plain GEMM view only)
+  if (a.out_f32 && !a.out_nchw && !(a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 &&
+                                    a.pad_h == 0 && a.pad_w == 0))
     return false;
   if ((uintptr_t)a.x % 16 || (uintptr_t)a.w % 16) return false;
   if (a.y && (uintptr_t)a.y % 16) return false;
@@ -465,6 +468,11 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   p.hi = a.act == ACT_CLIP ? a.hi : INFINITY;
   p.out_f32 = a.out_f32;
   p.ldo = a.ldo;
+  p.out_hw = a.out_f32 && a.out_nchw ? a.P * a.Q : 0;
+  // fp32 operands as three bf16 parts: six (activation part, filter part) products per tap
+  const int parts = a.split ? 3 : 1, combos = a.split ? 6 : 1;
+  static const int a_part[6] = {0, 0, 0, 1, 1, 2};
+  const int64_t plane = (int64_t)a.N * a.H * a.W * a.Cf;   // elements of one activation part
   p.err = err_word;
   p.consts_ready = a.consts_ready;
   const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
@@ -490,7 +498,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   // than the plain one, which hurts the HBM-bound 1x1 layers
   // 3x3 / stride 1 / pad 1 with 64 -> 64 channels and rows of at most 126 pixels: the input
   // block of a tile is loaded once and the taps are windows of it (TC_MODE_HALO)
-  const bool halo = allow_halo && halo_allowed && !a.f16 && !a.out_f32 && a.R == 3 && a.S == 3 &&
+  const bool halo = allow_halo && halo_allowed && !a.f16 && !a.split && !a.out_f32 && a.R == 3 && a.S == 3 &&
                     a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 1 && a.pad_w == 1 &&
                     a.Cf == 64 && a.K == 64 && a.W + 2 <= 128 && a.w_step == 0 && a.Q == a.W &&
                     a.P == a.H;
@@ -514,9 +522,8 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   const int nsm = num_sms > 0 ? num_sms : 148;
   const int bn = pn ? 128
                     : halo ? 64
-                    : a.out_f32 ? (a.K > 32 ? 64 : 32)   // the fp32 head is compiled for these only
                     : pick_bn(a.K, (long)p.tiles_w * p.tiles_h * p.tiles_n,
-                              (a.R * a.S * a.Cf + 63) / 64, nsm);
+                              (a.R * a.S * combos * a.Cf + 63) / 64, nsm);
   pl.bn = bn;
   p.tiles_k = (a.K + bn - 1) / bn;
   p.sp_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
@@ -548,9 +555,10 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   } else if (flat) {
     const uint64_t dims[4] = {(uint64_t)a.Cf, (uint64_t)Qg, 1, 1};
     const uint64_t st[3] = {(uint64_t)a.Cf * 2, (uint64_t)Qg * a.Cf * 2, (uint64_t)Qg * a.Cf * 2};
-    ok &= make_map(&p.tmA[0], a.x, 4, dims, st, boxA, bk * 2, counted);
-    p.num_taps = 1;
-    p.taps[0] = TcTap{0, 0, 0};
+    for (int part = 0; part < parts; ++part)
+      ok &= make_map(&p.tmA[part], a.x + part * plane, 4, dims, st, boxA, bk * 2, counted);
+    p.num_taps = combos;
+    for (int j = 0; j < combos; ++j) p.taps[j] = TcTap{a.split ? a_part[j] : 0, 0, 0};
   } else {
     // one tensor map per (row phase, column phase) of the stride
     const int sh = a.stride_h, sw = a.stride_w;
@@ -573,22 +581,27 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
                                     (uint64_t)(Hm > 0 ? Hm : 1), (uint64_t)a.N};
           const uint64_t st[3] = {(uint64_t)(sw * px * 2), (uint64_t)(sh * rowe * 2),
                                   (uint64_t)(a.H * rowe * 2)};
-          ok &= make_map(&p.tmA[nmaps], ptr, 4, dims, st, boxA, bk * 2, counted);
+          // the maps of one stride phase, one per operand part, sit next to one another
+          for (int part = 0; part < parts; ++part)
+            ok &= make_map(&p.tmA[nmaps * parts + part], ptr + part * plane, 4, dims, st, boxA,
+                           bk * 2, counted);
           map_of[bh][bw] = nmaps++;
         }
-        p.taps[p.num_taps++] = TcTap{map_of[bh][bw], aw, ah};
+        for (int j = 0; j < combos; ++j)
+          p.taps[p.num_taps++] = TcTap{map_of[bh][bw] * parts + (a.split ? a_part[j] : 0), aw, ah};
       }
   }
   {
-    const uint64_t dims[3] = {(uint64_t)a.Cf, (uint64_t)a.K, (uint64_t)(a.R * a.S)};
+    const uint64_t dims[3] = {(uint64_t)a.Cf, (uint64_t)a.K, (uint64_t)(a.R * a.S * combos)};
     const uint64_t st[2] = {(uint64_t)a.Cf * 2, (uint64_t)a.K * a.Cf * 2};
     const uint32_t box[3] = {(uint32_t)bk, (uint32_t)(pair ? bn / 2 : bn), 1};
     ok &= make_map(&p.tmB, a.w, 3, dims, st, box, bk * 2, counted);
   }
   // For 256-wide tiles with a long reduction, 32-channel slabs free enough shared memory
   // for a fourth ring stage, which those layers need more than a cheap epilogue.
-  const int ksteps64 = (a.R * a.S * a.Cf + 63) / 64;
+  const int ksteps64 = (a.R * a.S * combos * a.Cf + 63) / 64;
   int dc = pn ? 64 : (bn < 64 ? bn : (bn == 256 && bk == 64 && ksteps64 >= 16 ? 32 : 64));
+  if (a.out_f32 && bn >= 64) dc = 64;   // the fp32-output flavour is compiled for 64-channel slabs
 #ifdef OCCAMY_TUNING
   if (const char *f = getenv("OCCAMY_TC_DC"))   // slab width of the 256-wide tiles
     if (!pn && bn == 256 && (atoi(f) == 32 || atoi(f) == 64)) dc = atoi(f);
@@ -616,6 +629,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
                            : 1024 + (size_t)p.bias_floats * 4 + 8 * 80 +
                                  (halo ? (size_t)9 * bn * bk * 2 : 0);   // halo: resident weights
   int dbuf = pn ? 0 : (3 + TC_NSTORE - 1) / TC_NSTORE * TC_NSTORE;
+  if (a.out_f32) dbuf = TC_NSTORE;      // written straight from registers: no slabs are staged
   int stages;
   if (!pn && a.residual) {
     // The residual slab of an output slab is fetched into its buffer ahead of time, and a

@@ -17,7 +17,8 @@ constexpr int TC_EW = 2;             // tc_conv_kernel: epilogue warps per TMEM 
 constexpr int TC_NSTORE = 2;         // tc_conv_kernel: slab-store threads (slab buffers: a multiple)
 constexpr int TC_EPI_THREADS = 256;
 constexpr int TC_DBUF = 3;           // output slab buffers in shared memory
-constexpr int TC_MAX_TAPS = 32;
+constexpr int TC_MAX_TAPS = 64;
+constexpr int TC_MAX_AMAPS = 12;      // A tensor maps: 4 stride phases x 3 operand parts
 constexpr int TC_SMEM_LIMIT = 232448;  // 227 KB
 
 // Division of a tile index (< 2^31) by a positive constant: q = umulhi(x, mul) >> shift,
@@ -31,7 +32,7 @@ struct TcTap {
 };
 
 struct alignas(64) TcParams {
-  CUtensorMap tmA[4];
+  CUtensorMap tmA[TC_MAX_AMAPS];
   CUtensorMap tmB;
   CUtensorMap tmD;
   CUtensorMap tmR;
@@ -46,6 +47,9 @@ struct alignas(64) TcParams {
   float lo, hi;
   float *out_f32;
   int ldo;
+  int out_hw;            // fp32 output: 0 = row-major [pixel][ldo]; else P * Q of an NCHW tensor
+                         // [N][K][P][Q] that the epilogue writes directly (one channel per store
+                         // instruction, consecutive lanes on consecutive pixels)
   int m_total;
   int consts_ready;      // filter and bias were resident before the launch: they may be
                          // fetched before the previous kernel in the stream has finished
@@ -852,6 +856,19 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
       const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank);
       const int nslab = min(NSLAB, (p.K - tl.k0 + DC - 1) / DC);
       const float *bias_t = bias_s + tl.k0 + part * CW;
+      bool f32_ok = false;        // fp32 NCHW output: does this thread's row hold a real pixel,
+      int64_t f32_base = 0;       // and where does its channel 0 go
+      if constexpr (F32) {
+        if (p.out_hw) {
+          const int twi = row % p.tw, r2 = row / p.tw;
+          const int thi = r2 % p.th, tni = r2 / p.th;
+          const int q = tl.q0 + twi, pp = tl.p0 + thi, n = tl.n0 + tni;
+          f32_ok = row < rows_valid && q < p.gq && pp < p.gp && n < p.gn;
+          const int64_t lin = ((int64_t)n * p.gp + pp) * p.gq + q;   // pixel number in the grid
+          const int64_t img = lin / p.out_hw;
+          f32_base = img * (int64_t)p.K * p.out_hw + (lin - img * p.out_hw);
+        }
+      }
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
         err_code = 4;
         break;
@@ -884,8 +901,23 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           }
         }
         if constexpr (F32) {
-          const int m = tl.q0 + row;
           const int c0 = tl.k0 + sl * DC + part * CW;
+          if (p.out_hw) {
+            // NCHW: this thread's pixel is (n, pq); channel c lies c * P*Q floats further on
+            if (f32_ok) {
+              float *o = p.out_f32 + f32_base + (int64_t)c0 * p.out_hw;
+#pragma unroll
+              for (int j = 0; j < CW / 2; ++j) {
+                float a, b;
+                f2_unpack(v2[j], a, b);
+                if (c0 + 2 * j < p.K) o[(int64_t)(2 * j) * p.out_hw] = tc_act(a, act_lo, act_hi);
+                if (c0 + 2 * j + 1 < p.K)
+                  o[(int64_t)(2 * j + 1) * p.out_hw] = tc_act(b, act_lo, act_hi);
+              }
+            }
+            return true;
+          }
+          const int m = tl.q0 + row;
           if (row < rows_valid && m < p.m_total) {
             float *o = p.out_f32 + (int64_t)m * p.ldo + c0;
 #pragma unroll

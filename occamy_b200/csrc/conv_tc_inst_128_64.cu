@@ -5,7 +5,7 @@
 namespace occ {
 
 bool tc_launch_128_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
-  return tc_launch_mode<128, 64, false>(p, mode, grid, smem, s);
+  return tc_launch_mode<128, 64, true>(p, mode, grid, smem, s);
 }
 
 }  // namespace occ

@@ -80,6 +80,16 @@ void launch_pack_fold_bf16(const float *w, bf16 *out, int K, int C, int R, int S
 void launch_pad_input_bf16(const float *x, bf16 *out, int N, int C, int H, int W, int Wp, int Cp,
                            int pad_w, bool f16, cudaStream_t s);
 
+// ---- fp32 carried as three bf16 parts (fp32 mode on the tensor cores) ----------
+// x fp32 NCHW -> three consecutive NHWC planes [N][H][W][Cp] (hi, mid, lo), zero channels up to Cp
+void launch_split3_nchw(const float *x, bf16 *y, int N, int C, int Cp, int H, int W, cudaStream_t s);
+// x fp32 [M][K], rows `ld` floats apart -> three consecutive planes [M][Kp]
+void launch_split3_rows(const float *x, bf16 *y, int M, int K, int Kp, int ld, cudaStream_t s);
+// fp32 KCRS -> bf16 [R*S*6][K][Cp]: six filter parts per tap, in the order the kernel pairs
+// them with the activation parts
+void launch_pack_krsc_split(const float *w, bf16 *out, int K, int C, int R, int S, int Cp,
+                            cudaStream_t s);
+
 // ---- tcgen05 implicit-GEMM convolution / GEMM --------------------------------
 struct TcConvArgs {
   const bf16 *x;         // A operand: NHWC bf16 [N][H][W][C] (or folded rows, see w_step)
@@ -87,8 +97,11 @@ struct TcConvArgs {
   const float *bias;     // [K] or null
   const bf16 *residual;  // NHWC bf16 like the output, or null
   bf16 *y;               // NHWC bf16 [N][P][Q][K]      (when out_f32 == null)
-  float *out_f32;        // row-major [N*P*Q][ldo] fp32 (GEMM head), else null
+  float *out_f32;        // fp32 output (else null): row-major [N*P*Q][ldo] (GEMM head) ...
   int ldo;
+  int out_nchw;          // ... or, when set, the NCHW tensor [N][K][P][Q] itself
+  int split;             // fp32 operands as bf16 parts: x points at three planes (hi, mid, lo) of
+                         // N*H*W*Cf elements each, w holds six parts per tap (launch_pack_krsc_split)
   int N, H, W, Cf;       // A tensor dims (W already = Q for the folded form)
   int K, P, Q;
   int R, S;              // taps looped over (S = 1 for the folded form)

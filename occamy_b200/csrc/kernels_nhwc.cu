@@ -868,6 +868,105 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
 }
 
 // ---------------------------------------------------------------------------
+// fp32 on the tensor cores: a value is carried as three bf16 parts, hi + mid + lo, which
+// together hold its 24 mantissa bits.  A product a * w is then the sum of the six part
+// products that matter (hi*hi, hi*mid, hi*lo, mid*hi, mid*mid, lo*hi; the three left out are
+// below 2^-24 of it), each exact in the fp32 accumulator.  These kernels make the parts: the
+// activation as three NHWC planes, the filter with six parts per tap in the matching order.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void split3(float v, uint16_t &hi, uint16_t &mid, uint16_t &lo) {
+  const __nv_bfloat16 h = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(h);            // exact: the part bf16 dropped
+  const __nv_bfloat16 m = __float2bfloat16_rn(r1);
+  const float r2 = r1 - __bfloat162float(m);
+  hi = __bfloat16_as_ushort(h);
+  mid = __bfloat16_as_ushort(m);
+  lo = __bfloat16_as_ushort(__float2bfloat16_rn(r2));
+}
+
+// x fp32 [N][C][HW] -> three planes [N][HW][Cp] bf16 (channels C..Cp-1 zero), `plane` elements
+// apart, through a 32 x 32 tile like the plain layout conversion.
+__global__ void split3_nchw_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, int C, int Cp,
+                                   int HW, int64_t plane) {
+  __shared__ float tile[32][33];
+  const int n = blockIdx.z;
+  const int c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+  const float *xn = x + (int64_t)n * C * HW;
+  uint16_t *yn = y + (int64_t)n * Cp * HW;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int c = c0 + i, p = p0 + threadIdx.x;
+    tile[i][threadIdx.x] = (c < C && p < HW) ? xn[(int64_t)c * HW + p] : 0.0f;
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int p = p0 + i, c = c0 + threadIdx.x;
+    if (p < HW && c < Cp) {
+      uint16_t h, m, l;
+      split3(tile[threadIdx.x][i], h, m, l);
+      const int64_t at = (int64_t)p * Cp + c;
+      yn[at] = h;
+      yn[at + plane] = m;
+      yn[at + 2 * plane] = l;
+    }
+  }
+}
+
+void launch_split3_nchw(const float *x, bf16 *y, int N, int C, int Cp, int H, int W, cudaStream_t s) {
+  const int HW = H * W;
+  if ((int64_t)N * C * HW == 0) return;
+  dim3 grid((HW + 31) / 32, (Cp + 31) / 32, N), block(32, 8);
+  split3_nchw_kernel<<<grid, block, 0, s>>>(x, (uint16_t *)y, C, Cp, HW, (int64_t)N * HW * Cp);
+  count(CNT_LAUNCHES);
+}
+
+// x fp32 [M][K] (row length ld) -> three planes [M][Kp] bf16
+__global__ void split3_rows_kernel(const float *__restrict__ x, uint16_t *__restrict__ y, int K, int Kp,
+                                   int ld, int64_t total, int64_t plane) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int k = (int)(i % Kp);
+    const int64_t m = i / Kp;
+    uint16_t h, md, l;
+    split3(k < K ? x[m * ld + k] : 0.0f, h, md, l);
+    y[i] = h;
+    y[i + plane] = md;
+    y[i + 2 * plane] = l;
+  }
+}
+
+void launch_split3_rows(const float *x, bf16 *y, int M, int K, int Kp, int ld, cudaStream_t s) {
+  const int64_t total = (int64_t)M * Kp;
+  if (total == 0) return;
+  split3_rows_kernel<<<grid_for(total, 256), 256, 0, s>>>(x, (uint16_t *)y, K, Kp, ld, total, total);
+  count(CNT_LAUNCHES);
+}
+
+// [K][C][R*S] fp32 -> [R*S * 6][K][Cp] bf16: per tap the parts (hi, mid, lo, hi, mid, hi), to be
+// multiplied with the activation parts (hi, hi, hi, mid, mid, lo).
+__global__ void pack_krsc_split_kernel(const float *__restrict__ w, uint16_t *__restrict__ out, int K,
+                                       int C, int Cp, int RS, int64_t total) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % Cp);
+    const int k = (int)((i / Cp) % K);
+    const int tj = (int)(i / ((int64_t)Cp * K));
+    const int t = tj / 6, j = tj % 6;
+    uint16_t part[3];
+    split3(c < C ? w[((int64_t)k * C + c) * RS + t] : 0.0f, part[0], part[1], part[2]);
+    const int which = j == 0 ? 0 : (j == 1 ? 1 : (j == 2 ? 2 : (j == 3 ? 0 : (j == 4 ? 1 : 0))));
+    out[i] = part[which];
+  }
+}
+
+void launch_pack_krsc_split(const float *w, bf16 *out, int K, int C, int R, int S, int Cp,
+                            cudaStream_t s) {
+  const int64_t total = (int64_t)K * Cp * R * S * 6;
+  if (total == 0) return;
+  pack_krsc_split_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, (uint16_t *)out, K, C, Cp, R * S, total);
+  count(CNT_LAUNCHES);
+}
+
+// ---------------------------------------------------------------------------
 // Weight packing (runs once per constant; results stay resident)
 // ---------------------------------------------------------------------------
 // [K][C][R*S] fp32 -> [R*S][K][Cp] bf16, channels c >= C (padding up to Cp) zero.

@@ -83,6 +83,7 @@ _SIGNATURES = {
     "occamy_get_counters": (None, [_i64p]),
     "occamy_clear_weight_cache": (None, []),
     "occamy_set_weight_cache": (None, [C.c_int]),
+    "occamy_set_fp32_tensor_cores": (None, [C.c_int]),
     "occamy_conv_bias_act_noalloc": (C.c_int, [_f32p, _i64p, _f32p, _i64p, _f32p, _i64p, _i64p,
                                                C.c_int64, _f32p, C.c_void_p]),
     "occamy_noalloc_last_error": (C.c_int, [C.c_int]),

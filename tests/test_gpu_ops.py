@@ -15,8 +15,17 @@ from oracle import ref
 
 pytestmark = pytest.mark.gpu
 
-TOL = {rt.MATH_FP32: 1e-4, rt.MATH_BF16: 2e-2, rt.MATH_F16: 2e-2}
-MODES = [rt.MATH_FP32, rt.MATH_BF16, rt.MATH_F16]
+# fp32 mode runs dense convolutions and GEMMs on the tensor cores (operands split into bf16
+# parts); FP32_CUDA_CORES is the same mode with that switched off, so that the CUDA-core kernels
+# stay covered.
+FP32_CUDA_CORES = -1
+TOL = {rt.MATH_FP32: 1e-4, FP32_CUDA_CORES: 1e-4, rt.MATH_BF16: 2e-2, rt.MATH_F16: 2e-2}
+MODES = [rt.MATH_FP32, FP32_CUDA_CORES, rt.MATH_BF16, rt.MATH_F16]
+
+
+def set_mode(mode):
+    rt.lib().occamy_set_fp32_tensor_cores(0 if mode == FP32_CUDA_CORES else 1)
+    rt.set_math_mode(rt.MATH_FP32 if mode == FP32_CUDA_CORES else mode)
 # output rounding of the 16-bit formats (one step of the stored value, relative)
 STEP = {rt.MATH_BF16: 2.0 ** -8, rt.MATH_F16: 2.0 ** -11}
 
@@ -26,6 +35,7 @@ def _check_runtime_errors(native_libs):
     rt.last_error(clear=True)
     yield
     rt.synchronize()
+    rt.lib().occamy_set_fp32_tensor_cores(1)
     assert rt.last_error(clear=True) == 0
 
 
@@ -71,7 +81,7 @@ def test_conv(case, mode, act_mode):
     x = r.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
     w = he(r, K, C // groups, R, R)
     b = r.normal(0, 0.5, K).astype(np.float32)
-    rt.set_math_mode(mode)
+    set_mode(mode)
     y = A.conv(A.up(x), A.up(w), A.up(b) if act_mode is not None else None, (pad, pad),
                (stride, stride), groups, act_mode).numpy()
     lo, hi = (0.0, 6.0) if act_mode == 3 else (0.0, 0.0)
@@ -83,7 +93,7 @@ def test_conv(case, mode, act_mode):
 
 @pytest.mark.parametrize("mode", MODES)
 def test_conv_empty_and_tiny(mode):
-    rt.set_math_mode(mode)
+    set_mode(mode)
     r = rng(5)
     # batch 0: nothing to do, pointer still returned
     x0 = A.Dev((0, 16, 4, 4))
@@ -100,7 +110,7 @@ def test_conv_empty_and_tiny(mode):
 def test_unfused_chain_matches_fused(mode):
     """conv -> in-place bias add -> relu (what the compiler emits without fusion), then
     residual add, max pool and global average pool on the same device tensors."""
-    rt.set_math_mode(mode)
+    set_mode(mode)
     r = rng(11)
     x = r.uniform(-1, 1, (2, 64, 14, 14)).astype(np.float32)
     w = he(r, 64, 64, 3, 3)
@@ -184,7 +194,7 @@ def test_reduce_mean(shapes):
                                   (5, 16, 9, 1, 0), (64, 512, 96, 0, 1), (1, 2048, 1000, 0, 1)])
 def test_matmul2d(case, mode):
     M, K, Nn, tA, tB = case
-    rt.set_math_mode(mode)
+    set_mode(mode)
     r = rng(9)
     a = r.normal(0, 1, (K, M) if tA else (M, K)).astype(np.float32)
     b = (r.normal(0, 1, (Nn, K) if tB else (K, Nn)) / np.sqrt(K)).astype(np.float32)
@@ -287,7 +297,7 @@ def test_pool_on_tensor_core_mode_activations(case, avg, mode):
 
 def test_reshape_is_a_copy():
     for mode in MODES:
-        rt.set_math_mode(mode)
+        set_mode(mode)
         x = rng(13).normal(0, 1, (2, 8, 3, 5)).astype(np.float32)
         y = A.reshape(A.up(x), (2, 120)).numpy()
         assert np.array_equal(y, x.reshape(2, 120))
@@ -502,3 +512,26 @@ def test_conv_on_cta_pairs(case, mode, act_mode):
     assert np.isfinite(y).all()
     err = np.abs(y - want).reshape(N, K, -1).max(axis=(1, 2)) / np.abs(want).max()
     assert err.max() <= TOL[mode]
+
+
+def test_fp32_mode_runs_on_the_tensor_cores():
+    """fp32 mode, dense 3x3 and 1x1 convolutions and the classifier GEMM: tensor-core launches
+    are counted, no CUDA-core convolution / GEMM launch is, and the result is within the fp32
+    bound with room to spare (the split operands carry all 24 mantissa bits)."""
+    rt.set_math_mode(rt.MATH_FP32)
+    r = rng(19)
+    x = r.uniform(-1, 1, (4, 96, 28, 28)).astype(np.float32)
+    w3, w1 = he(r, 128, 96, 3, 3), he(r, 64, 128, 1, 1)
+    b3, b1 = r.normal(0, 0.3, 128).astype(np.float32), r.normal(0, 0.3, 64).astype(np.float32)
+    c0 = rt.counters()
+    t = A.conv(A.up(x), A.up(w3), A.up(b3), (1, 1), (2, 2), act_mode=1)
+    y = A.conv(t, A.up(w1), A.up(b1), act_mode=5).numpy()
+    a = r.normal(0, 1, (64, 500)).astype(np.float32)
+    bm = (r.normal(0, 1, (200, 500)) / 22).astype(np.float32)
+    m = A.matmul2d(A.up(a), A.up(bm), 1.0, 1.0, 0, 1).numpy()
+    c1 = rt.counters()
+    assert c1["tc_launches"] - c0["tc_launches"] == 3
+    assert c1["simt_launches"] == c0["simt_launches"]
+    want = ref.conv2d(ref.conv2d(x, w3, b3, (1, 1), (2, 2), act=1), w1, b1, act=5)
+    assert max_rel_err(y, want) <= 2e-5
+    assert max_rel_err(m, ref.matmul2d(a, bm, None, 1.0, 0.0, 0, 1)) <= 2e-5
