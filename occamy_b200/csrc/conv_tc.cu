@@ -369,7 +369,7 @@ static int pick_bk(int Cf) { return Cf % 64 == 0 ? 64 : (Cf % 32 == 0 ? 32 : (Cf
 // Output-channel tile.  Wide tiles re-read the activations less and keep the tensor pipe
 // busier per instruction, but when a layer has few pixels they leave SMs idle; pick the
 // width with the lowest modelled time: waves x (k-steps x cost per k-step + epilogue slabs).
-static int pick_bn(int K, long sp_tiles, int ksteps, int num_sms) {
+static int pick_bn(int K, long sp_tiles, int ksteps, int num_sms, int widest_allowed = 256) {
 #ifdef OCCAMY_TUNING   // sweep builds only: force the tile width from the environment
   if (const char *f = getenv("OCCAMY_TC_BN")) {
     const int v = atoi(f);
@@ -379,7 +379,7 @@ static int pick_bn(int K, long sp_tiles, int ksteps, int num_sms) {
   const int cand[4] = {256, 128, 64, 32};
   const double kcost[4] = {900.0, 780.0, 715.0, 700.0};  // cycles per 64-deep k-step
   int widest = 32;
-  while (widest < K && widest < 256) widest *= 2;
+  while (widest < K && widest < widest_allowed) widest *= 2;
   int best = widest;
   double best_cost = -1.0;
   for (int i = 0; i < 4; ++i) {
@@ -523,7 +523,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   const int bn = pn ? 128
                     : halo ? 64
                     : pick_bn(a.K, (long)p.tiles_w * p.tiles_h * p.tiles_n,
-                              (a.R * a.S * combos * a.Cf + 63) / 64, nsm);
+                              (a.R * a.S * combos * a.Cf + 63) / 64, nsm, a.split ? 128 : 256);
   pl.bn = bn;
   p.tiles_k = (a.K + bn - 1) / bn;
   p.sp_tiles = p.tiles_w * p.tiles_h * p.tiles_n;
@@ -612,6 +612,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
                          (halo ? TC_MODE_HALO : 0));
   if (a.f16) pl.mode |= TC_MODE_F16;
   if (pair) pl.mode |= TC_MODE_PAIR;
+  if (a.split) pl.mode |= TC_MODE_SPLIT;
   if (!a.out_f32) {
     const uint64_t dims[4] = {(uint64_t)a.K, (uint64_t)Qg, (uint64_t)Pg, (uint64_t)Ng};
     const uint64_t st[3] = {(uint64_t)a.K * 2, (uint64_t)Qg * a.K * 2, (uint64_t)Pg * Qg * a.K * 2};

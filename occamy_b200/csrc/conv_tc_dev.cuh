@@ -86,6 +86,12 @@ constexpr int TC_MODE_F16 = 16;
 // flop of the single-CTA form, which is what bounds the long-reduction layers.  No multicast
 // load is involved: every TMA load has one destination.
 constexpr int TC_MODE_PAIR = 32;
+// fp32 operands carried as bf16 parts (six taps per filter tap, see the planner): the hi * hi
+// products go into one accumulator and the five correction products into a second one, which
+// the epilogue adds.  The tensor core truncates when it adds into an fp32 accumulator, a bias
+// toward zero that grows with the number of additions at full magnitude; kept apart, the small
+// terms cost the main sum no additions (and their own truncation is 2^-8 smaller).
+constexpr int TC_MODE_SPLIT = 64;
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -483,7 +489,10 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   constexpr bool HALO = (MODE & TC_MODE_HALO) != 0;
   constexpr bool F16 = (MODE & TC_MODE_F16) != 0;
   constexpr bool PAIR = (MODE & TC_MODE_PAIR) != 0;
+  constexpr bool SPLIT = (MODE & TC_MODE_SPLIT) != 0;
   static_assert(!(PAIR && (HALO || F32)), "the CTA-pair form exists for the plain epilogues only");
+  static_assert(!SPLIT || (F32 && !HALO && BN <= 128), "split operands: fp32 output, four accumulators");
+  constexpr int ACC_COLS = SPLIT ? 2 * BN : BN;   // TMEM columns of one tile's accumulator(s)
   constexpr int EPI_THREADS = 128 * EW;
   constexpr int STORE_WARP = 2 + 4 * EW;
   constexpr int CW = DC / EW;                  // channels one epilogue thread handles per slab
@@ -492,7 +501,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   // fp32 accumulator; A and B formats: 1 = bf16, 0 = fp16; N / 8 and M / 16
   constexpr uint32_t IDESC = (1u << 4) | (F16 ? 0u : ((1u << 7) | (1u << 10))) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((PAIR ? 256 : 128) >> 4) << 24);
-  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
   constexpr int BROWS = PAIR ? BN / 2 : BN;    // rows of the B tile this CTA loads
 
   extern __shared__ uint8_t smem_raw[];
@@ -729,8 +738,10 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        uint32_t accumulate = 0;
+        const uint32_t d_main = tmem_base + (uint32_t)(acc * ACC_COLS);
+        uint32_t d_tmem = d_main;
+        uint32_t accumulate = 0, accumulate_corr = 0;
+        int cb_in_tap = 0, combo = 0;   // split operands: position inside the six-tap group
         for (int ks = 0; ks < ksteps; ++ks) {
           if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
             err_code = 3;
@@ -739,6 +750,21 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
           const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
+          if constexpr (SPLIT) {
+            // tap 0 of every group of six is hi * hi: main accumulator; the rest: corrections
+            const bool corr = combo != 0;
+            d_tmem = corr ? d_main + (uint32_t)BN : d_main;
+            for (int kk = 0; kk < bk / 16; ++kk) {
+              tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
+                          corr ? accumulate_corr : accumulate);
+              if (corr) accumulate_corr = 1;
+              else accumulate = 1;
+            }
+            if (++cb_in_tap == p.cblocks) {
+              cb_in_tap = 0;
+              if (++combo == 6) combo = 0;
+            }
+          } else
           for (int kk = 0; kk < bk / 16; ++kk) {
             if constexpr (PAIR)   // the same offsets in the other CTA hold its pixels and B half
               mma_lohi_pair(d_tmem, (uint32_t)adesc + 2u * kk, (uint32_t)(adesc >> 32),
@@ -875,7 +901,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
       }
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) +
-                             (uint32_t)(acc * BN + part * CW);
+                             (uint32_t)(acc * ACC_COLS + part * CW);
       // every TMEM read of this tile has landed: the MMA warp may overwrite the buffer
       auto release_acc = [&]() {
         tc_fence_before();
@@ -972,8 +998,22 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
       // Slabs in pairs, so that the registers of one slab are loaded while the other is
       // worked on and the loop body (two slabs) stays small.
       uint32_t ra[CW], rb[CW];
-      tc_ld<CW>(t_row, ra);
       bool ok = true;
+      if constexpr (SPLIT) {
+        // main and correction accumulators of a slab are read together and added here
+#pragma unroll 1
+        for (int sl = 0; sl < nslab && ok; ++sl) {
+          tc_ld<CW>(t_row + (uint32_t)(sl * DC), ra);
+          tc_ld<CW>(t_row + (uint32_t)(BN + sl * DC), rb);
+          tc_ld_wait();
+          if (sl + 1 == nslab) release_acc();
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));
+          ok = slab(ra, sl);
+        }
+      } else {
+      tc_ld<CW>(t_row, ra);
 #pragma unroll 1
       for (int sl = 0; sl < nslab && ok; sl += 2) {
         tc_ld_wait();
@@ -986,6 +1026,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           else release_acc();
           ok = slab(rb, sl + 1);
         }
+      }
       }
       if (!ok) {
         err_code = 5;
@@ -1093,6 +1134,12 @@ inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, c
         tc_launch_one<BN, DC, P2 | H2 | TC_MODE_RES | TC_MODE_CLAMP>(p, grid, smem, s);
         return true;
       default: break;
+    }
+  }
+  if constexpr (WITH_F32 && BN <= 128) {
+    if (mode == (TC_MODE_SPLIT | TC_MODE_F32 | TC_MODE_CLAMP)) {
+      tc_launch_one<BN, DC, TC_MODE_SPLIT | TC_MODE_F32 | TC_MODE_CLAMP>(p, grid, smem, s);
+      return true;
     }
   }
   constexpr int H = TC_MODE_F16;
