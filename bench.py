@@ -314,7 +314,11 @@ def main():
         raise SystemExit("bench.py needs a B200: no CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a collective that some rank never joins ends in an error after two minutes, not in a
+        # kernel that spins until the job is killed
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=120))
     lo_img, hi_img = sharding.shard_range(args.batch, rank, world)
     per_rank = hi_img - lo_img
 
@@ -541,13 +545,15 @@ def main():
 def check_parity(args, g, builder, prog, binding, x_host, out_host, gathered, world, per_rank,
                  rank_images, step_e2e):
     """Runs the CPU oracle on four images of the batch that was timed and compares (a) the
-    timed program's own output, as the end-to-end step left it in rank 0's host buffer, and
+    timed program's own output, as the last end-to-end step left it in rank 0's host buffer, and
     (b) the logits of the same images from a replay that also returns the pre-softmax tensor.
     With several ranks two of the images belong to the last rank, so the gathered tensor is
     what is checked."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from helpers import max_rel_err, run_graph_oracle, top1_agrees
-    step_e2e()                                    # out_host now holds this batch's result
+    # out_host holds the result of the last end-to-end step of the timed loops (every step runs
+    # the same batch); no further step is run here: with several ranks a step is a collective
+    # and only rank 0 comes this way
     picks = [(0, 0), (0, per_rank // 3), (world - 1, 2 * per_rank // 3), (world - 1, per_rank - 1)]
     imgs = []
     cache = {0: x_host.numpy()}

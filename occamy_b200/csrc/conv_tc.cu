@@ -627,7 +627,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   p.bias_floats = (a.K + bn - 1) / bn * bn;
   const size_t slab_bytes = (size_t)128 * dc * 2;
   const size_t fixed0 = pn ? 1024 + 2 * 256 * 128 + 8 * 80
-                           : 1024 + (size_t)p.bias_floats * 4 + 8 * 80 +
+                           : (size_t)p.bias_floats * 4 + 8 * 80 +
                                  (halo ? (size_t)9 * bn * bk * 2 : 0);   // halo: resident weights
   int dbuf = pn ? 0 : (3 + TC_NSTORE - 1) / TC_NSTORE * TC_NSTORE;
   if (a.out_f32) dbuf = TC_NSTORE;      // written straight from registers: no slabs are staged

@@ -504,9 +504,17 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
   constexpr int BROWS = PAIR ? BN / 2 : BN;    // rows of the B tile this CTA loads
 
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  // The swizzled operand tiles need 1024-byte alignment.  The kernel has no static shared
+  // memory, so its dynamic block starts on such a boundary and the host budgets no slack for
+  // rounding up; should that ever not hold, the launch reports it instead of running past
+  // the end of its allocation.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if ((smem_u32(smem_raw) & 1023u) != 0u) {
+    if (threadIdx.x == 0) atomicExch(p.err, 1007);
+    return;
+  }
+  const uint32_t base = smem_u32(smem_raw);
+  uint8_t *base_ptr = smem_raw;
   const int bk = p.bk, stages = p.stages, dbuf = p.dbuf;
   // halo form: the ring carries input blocks only, the weights of all taps sit behind it
   const uint32_t a_bytes = HALO ? (uint32_t)p.halo_a_bytes : 128u * bk * 2u;

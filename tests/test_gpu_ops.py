@@ -535,3 +535,41 @@ def test_fp32_mode_runs_on_the_tensor_cores():
     want = ref.conv2d(ref.conv2d(x, w3, b3, (1, 1), (2, 2), act=1), w1, b1, act=5)
     assert max_rel_err(y, want) <= 2e-5
     assert max_rel_err(m, ref.matmul2d(a, bm, None, 1.0, 0.0, 0, 1)) <= 2e-5
+
+
+def test_constant_changed_in_place_is_noticed():
+    """A filter uploaded from host memory is recognised at its next upload (same address, same
+    size) and its packed copy reused.  The fingerprint behind that samples the whole buffer, so
+    a constant whose interior changed -- its first and last 512 bytes untouched -- is packed
+    again instead of being served from the stale copy."""
+    import ctypes as C
+    L = rt.lib()
+    rt.set_math_mode(rt.MATH_BF16)
+    r = rng(20)
+    x = r.uniform(-1, 1, (1, 64, 12, 12)).astype(np.float32)
+    w = he(r, 64, 64, 3, 3)                      # 147 KB: head and tail are 0.7 % of it
+    xd = A.up(x)
+
+    def run():
+        h = C.c_void_p()
+        L.cudnnCreate(C.byref(h))
+        wd, y = C.c_void_p(), A.Dev((1, 64, 12, 12))
+        L.wrapDNNMalloc(C.byref(wd), w.nbytes)
+        L.wrapDNNMemcpy(wd, w.ctypes.data, w.nbytes, 1, None)      # same host address every time
+        L.DNNConvFunc(h, xd.ptr, rt.dims(x.shape), wd, rt.dims(w.shape), None, 0, 1, 1,
+                      rt.dims((1, 1)), rt.dims((1, 1)), y.ptr)
+        out = y.numpy()
+        L.wrapDNNDealloc(wd)
+        L.cudnnDestroy(h)
+        return out
+
+    y0 = run()
+    c0 = rt.counters()
+    y1 = run()
+    assert np.array_equal(y0, y1)
+    assert rt.counters()["h2d_skipped_bytes"] - c0["h2d_skipped_bytes"] == w.nbytes   # reused
+    flat = w.reshape(-1)
+    flat[128:-128] *= -2.0                        # interior only
+    y2 = run()
+    want = ref.conv2d(x, w, None, (1, 1), (1, 1))
+    assert max_rel_err(y2, want) <= 2e-2
