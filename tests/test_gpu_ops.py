@@ -573,3 +573,77 @@ def test_constant_changed_in_place_is_noticed():
     y2 = run()
     want = ref.conv2d(x, w, None, (1, 1), (1, 1))
     assert max_rel_err(y2, want) <= 2e-2
+
+
+GUARD_CASES = [("conv", (1, 32, 13, 11, 24, 3, 1, 1)), ("conv", (3, 512, 7, 7, 512, 3, 1, 1)),
+               ("conv", (2, 24, 14, 14, 144, 1, 0, 1)), ("conv", (2, 3, 64, 64, 64, 7, 3, 2)),
+               ("conv", (2, 256, 28, 28, 128, 1, 0, 2)), ("depthwise", (2, 96, 15, 15, 96, 3, 1, 2)),
+               ("pool", (2, 16, 13, 11)), ("add", (2, 40, 9, 7))]
+
+
+@pytest.mark.parametrize("mode", [rt.MATH_FP32, rt.MATH_BF16, rt.MATH_F16])
+@pytest.mark.parametrize("case", GUARD_CASES)
+def test_kernels_write_nothing_outside_their_output(case, mode):
+    """Stands in for a memory checker: the output tensor sits inside a larger allocation whose
+    bytes before and after it hold a pattern; after the call the pattern must be intact.
+    Ragged shapes on purpose (tiles that overhang the tensor, channel counts below a tile)."""
+    import ctypes as C
+    L = rt.lib()
+    kind, shp = case
+    set_mode(mode)
+    r = rng(21)
+    GUARD = 4096                                   # bytes on either side
+    pattern = np.full(GUARD // 4, -7.25e33, np.float32)
+
+    def guarded(nbytes):
+        base = C.c_void_p()
+        L.wrapDNNMalloc(C.byref(base), GUARD + nbytes + GUARD)
+        L.wrapDNNMemcpy(base, pattern.ctypes.data, GUARD, 1, None)
+        L.wrapDNNMemcpy(base.value + GUARD + nbytes, pattern.ctypes.data, GUARD, 1, None)
+        return base, C.c_void_p(base.value + GUARD)
+
+    def guards_intact(base, nbytes):
+        lo, hi = np.empty_like(pattern), np.empty_like(pattern)
+        L.wrapDNNMemcpy(lo.ctypes.data, base, GUARD, 2, None)
+        L.wrapDNNMemcpy(hi.ctypes.data, base.value + GUARD + nbytes, GUARD, 2, None)
+        return np.array_equal(lo, pattern) and np.array_equal(hi, pattern)
+
+    if kind in ("conv", "depthwise"):
+        N, Cc, H, W, K, R, pad, stride = shp
+        groups = Cc if kind == "depthwise" else 1
+        x = r.uniform(-1, 1, (N, Cc, H, W)).astype(np.float32)
+        w = he(r, K, Cc // groups, R, R)
+        P = (H + 2 * pad - R) // stride + 1
+        Q = (W + 2 * pad - R) // stride + 1
+        nbytes = N * K * P * Q * 4
+        base, y = guarded(nbytes)
+        xd, wd = A.up(x), A.up(w)
+        L.DNNConvFunc(A.handle(), xd.ptr, rt.dims(x.shape), wd.ptr, rt.dims(w.shape), None, 0, 1,
+                      groups, rt.dims((pad, pad)), rt.dims((stride, stride)), y)
+        want = ref.conv2d(x, w, None, (pad, pad), (stride, stride), groups)
+    elif kind == "pool":
+        x = r.uniform(-1, 1, shp).astype(np.float32)
+        N, Cc, H, W = shp
+        w1 = he(r, Cc, Cc, 1, 1)
+        t = A.conv(A.up(x), A.up(w1))               # a 16-bit tensor in the 16-bit modes
+        P, Q = (H + 2 - 3) // 2 + 1, (W + 2 - 3) // 2 + 1
+        nbytes = N * Cc * P * Q * 4
+        base, y = guarded(nbytes)
+        L.DNNMaxPoolFunc(A.handle(), t.ptr, rt.dims(shp), y, rt.dims((N, Cc, P, Q)), rt.dims((3, 3)),
+                         rt.dims((1, 1, 1, 1)), rt.dims((2, 2)))
+        want = ref.pool2d(ref.conv2d(x, w1), (3, 3), (1, 1), (2, 2))
+    else:
+        x = r.uniform(-1, 1, shp).astype(np.float32)
+        N, Cc, H, W = shp
+        w1 = he(r, Cc, Cc, 1, 1)
+        t = A.conv(A.up(x), A.up(w1))
+        nbytes = x.nbytes
+        base, y = guarded(nbytes)
+        L.DNNTensorOpFunc(A.handle(), 0, t.ptr, rt.dims(shp), 4, t.ptr, rt.dims(shp), 4, y,
+                          rt.dims(shp), 4, 1.0)
+        want = 2 * ref.conv2d(x, w1)
+    got = np.empty(want.shape, np.float32)
+    L.wrapDNNMemcpy(got.ctypes.data, y, got.nbytes, 2, None)
+    assert max_rel_err(got, want) <= TOL[mode]
+    assert guards_intact(base, nbytes)
+    L.wrapDNNDealloc(base)
