@@ -408,6 +408,9 @@ def main():
     torch.cuda.synchronize()
     if rt.last_error():
         raise SystemExit("runtime reported an error during warm-up")
+    # the same K steps on the GPU as the W warm-up steps leave it (cool, boost clocks): reported
+    # beside `value`, which is taken after the GPU has been under load for --warm-seconds
+    ms_burst = timed(step_resident, args.steps)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     t_end = time.perf_counter() + args.warm_seconds
     more = 0
@@ -424,6 +427,9 @@ def main():
     warm += more
 
     c0 = rt.counters()
+    if rank == 0:   # for profilers: which launch the timed region starts at
+        print(f"[bench] kernel launches before the timed region: {c0['launches']}", file=sys.stderr,
+              flush=True)
     ms_total = timed(step_resident, args.steps)
     c1 = rt.counters()
     for _ in range(3):
@@ -450,10 +456,26 @@ def main():
         raise SystemExit(f"runtime reported error {err}")
 
     # ---- parity of what was timed: the logits of a few images against the CPU oracle ----
+    # Every rank replays the same program once more with the pre-softmax tensor marked as an
+    # output as well (identical kernels up to the softmax) and the ranks' logits are gathered
+    # like the result is; rank 0 then compares rows of its own and of the last rank's shard.
+    g2 = builder(batch=per_rank, seed=0)
+    logits_all = None
+    if getattr(g2, "logits", None) is not None:
+        if g2.logits not in g2.outputs:
+            g2.mark_output(g2.logits)
+        p2 = g2.to_program()
+        p2.lower(fuse=args.fuse, dealloc_opt=True, pool_opt=True)
+        outs2 = [torch.empty(g2.shapes[v], dtype=torch.float32, device="cuda") for v in g2.outputs]
+        p2.run_raw(binding, x_host.data_ptr(), 1, [t.data_ptr() for t in outs2], 3)
+        logits_dev = outs2[g2.outputs.index(g2.logits)]
+        with torch.cuda.stream(stream):
+            logits_all = sharding.gather_logits(logits_dev) if world > 1 else logits_dev
+        stream.synchronize()
     parity = None
     if rank == 0:
-        parity = check_parity(args, g, builder, prog, binding, x_host, out_host, gathered, world,
-                              per_rank, rank_images, step_e2e)
+        parity = check_parity(args, builder, out_host, logits_all.cpu().numpy() if logits_all is not None
+                              else None, world, per_rank, rank_images, x_host)
 
     ms_step = ms_total / args.steps
     value = args.batch / (ms_step / 1000.0)
@@ -481,6 +503,9 @@ def main():
         "dtype": {"bf16": "bf16", "fp16": "f16", "fp32": "f32"}[args.math], "data": "synthetic",
         "config": workload_config(args.graph, args.batch, world, args.fuse),
         "warm_seconds": args.warm_seconds,
+        "burst": {"value": per_s(ms_burst), "unit": "images/s", "ms_per_step": ms_burst / args.steps,
+                  "how": "the same K steps right after the W warm-up steps, before the GPU has "
+                         "been loaded for warm_seconds"},
         "e2e": {"value": per_s(ms_e2e), "unit": "images/s",
                 "h2d_bytes_per_step": int(x_host.numel() * 4 * world),
                 "d2h_bytes_per_step": int(args.batch * n_out * 4),
@@ -542,18 +567,15 @@ def main():
         dist.destroy_process_group()
 
 
-def check_parity(args, g, builder, prog, binding, x_host, out_host, gathered, world, per_rank,
-                 rank_images, step_e2e):
+def check_parity(args, builder, out_host, logits_all, world, per_rank, rank_images, x_host):
     """Runs the CPU oracle on four images of the batch that was timed and compares (a) the
     timed program's own output, as the last end-to-end step left it in rank 0's host buffer, and
-    (b) the logits of the same images from a replay that also returns the pre-softmax tensor.
-    With several ranks two of the images belong to the last rank, so the gathered tensor is
-    what is checked."""
+    (b) the logits of the same images (`logits_all`, gathered over the ranks).  With several
+    ranks two of the images belong to the last rank, so the gathered tensors are what is
+    checked.  No step is run here: with several ranks a step is a collective, and only rank 0
+    comes this way."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from helpers import max_rel_err, run_graph_oracle, top1_agrees
-    # out_host holds the result of the last end-to-end step of the timed loops (every step runs
-    # the same batch); no further step is run here: with several ranks a step is a collective
-    # and only rank 0 comes this way
     picks = [(0, 0), (0, per_rank // 3), (world - 1, 2 * per_rank // 3), (world - 1, per_rank - 1)]
     imgs = []
     cache = {0: x_host.numpy()}
@@ -569,23 +591,12 @@ def check_parity(args, g, builder, prog, binding, x_host, out_host, gathered, wo
     res = {"images": len(picks), "rows": rows, "tolerance": PARITY_TOL[args.math],
            "output_max_abs_err": float(np.abs(got_out - want_out).max()),
            "top1_equal": bool(np.array_equal(got_out.argmax(1), want_out.argmax(1)))}
-    if world == 1:
-        # the same program with the logits marked as an output as well (identical kernels up
-        # to the softmax), on the same host batch
-        import ctypes as C
-        from occamy_b200 import replay
-        g2 = builder(batch=per_rank, seed=0)
-        if g2.logits not in g2.outputs:
-            g2.mark_output(g2.logits)
-        p2 = g2.to_program()
-        p2.lower(fuse=args.fuse, dealloc_opt=True, pool_opt=True)
-        outs2 = p2.run(binding, x_host.numpy())
-        got_logits = outs2[g2.outputs.index(g2.logits)][rows]
+    if logits_all is not None:
+        got_logits = logits_all[rows]
         res["max_rel"] = max_rel_err(got_logits, want_logits)
         ok, ties = top1_agrees(got_logits, want_logits)
         res["top1_equal"] = res["top1_equal"] and ok
     else:
-        # logits are not an output of the sharded run; probabilities bound them from above
         res["max_rel"] = max_rel_err(got_out, want_out)
     res["ok"] = bool(res["max_rel"] <= PARITY_TOL[args.math] and res["top1_equal"])
     if not res["ok"]:
