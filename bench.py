@@ -590,12 +590,15 @@ def check_parity(args, builder, out_host, logits_all, world, per_rank, rank_imag
     got_out = out_host.numpy()[rows]
     res = {"images": len(picks), "rows": rows, "tolerance": PARITY_TOL[args.math],
            "output_max_abs_err": float(np.abs(got_out - want_out).max()),
-           "top1_equal": bool(np.array_equal(got_out.argmax(1), want_out.argmax(1)))}
+           # identical top-1, except rows whose two largest reference values are closer than
+           # one bf16 step of their magnitude (see tests/helpers.py::top1_agrees)
+           "top1_equal": top1_agrees(got_out, want_out)[0]}
     if logits_all is not None:
         got_logits = logits_all[rows]
         res["max_rel"] = max_rel_err(got_logits, want_logits)
         ok, ties = top1_agrees(got_logits, want_logits)
         res["top1_equal"] = res["top1_equal"] and ok
+        res["near_ties_left_out"] = ties
     else:
         res["max_rel"] = max_rel_err(got_out, want_out)
     res["ok"] = bool(res["max_rel"] <= PARITY_TOL[args.math] and res["top1_equal"])
