@@ -176,7 +176,11 @@ CONV_ROWS = [("conv3x3 256->256 @14", 256, 256, 3, 14, 1, False),
              ("conv1x1 256->1024 @14 +res", 256, 1024, 1, 14, 1, True),
              ("conv1x1 512->2048 @7 +res", 512, 2048, 1, 7, 1, True),
              ("conv1x1 64->256 @56 +res", 64, 256, 1, 56, 1, True),
-             ("conv1x1 512->128 @28", 512, 128, 1, 28, 1, False)]
+             ("conv1x1 512->128 @28", 512, 128, 1, 28, 1, False),
+             # MobileNetV2's few-channel layers on large images
+             ("conv1x1 32->16 @112", 32, 16, 1, 112, 1, False),
+             ("conv1x1 16->96 @112", 16, 96, 1, 112, 1, False),
+             ("conv1x1 144->24 @56", 144, 24, 1, 56, 1, False)]
 
 
 def _conv_rows(h, rng, B, L, timed, wanted):
