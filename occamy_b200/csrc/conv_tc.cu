@@ -436,6 +436,7 @@ struct Plan {
   int dc;    // channels per output slab
   bool pn;   // pixel-N variant
   bool pair; // CTA-pair form: the grid is launched as clusters of two
+  bool duo;  // two independent CTAs per SM (one epilogue warp per TMEM quadrant)
   size_t smem;
   bool ok;
 };
@@ -451,6 +452,23 @@ static TcFastDiv make_fastdiv(int d) {
 }
 
 static int floordiv(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+
+#ifdef OCCAMY_TC_TIMERS
+// analysis builds only: the device words the kernels' role timers add to
+static long long *tc_timer_words() {
+  static long long *w = nullptr;
+  if (!w) {
+    cudaMalloc(&w, 20 * sizeof(long long));
+    cudaMemset(w, 0, 20 * sizeof(long long));
+  }
+  return w;
+}
+extern "C" void occamy_tc_timers(long long *out, int clear) {
+  cudaDeviceSynchronize();
+  cudaMemcpy(out, tc_timer_words(), 20 * sizeof(long long), cudaMemcpyDeviceToHost);
+  if (clear) cudaMemset(tc_timer_words(), 0, 20 * sizeof(long long));
+}
+#endif
 
 static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool counted,
                        bool allow_halo = true) {
@@ -474,6 +492,9 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   static const int a_part[6] = {0, 0, 0, 1, 1, 2};
   const int64_t plane = (int64_t)a.N * a.H * a.W * a.Cf;   // elements of one activation part
   p.err = err_word;
+#ifdef OCCAMY_TC_TIMERS
+  p.timers = tc_timer_words();
+#endif
   p.consts_ready = a.consts_ready;
   const bool flat = a.R == 1 && a.S == 1 && a.stride_h == 1 && a.stride_w == 1 && a.pad_h == 0 &&
                     a.pad_w == 0 && a.w_step == 0;
@@ -620,44 +641,96 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
     ok &= make_map(&p.tmD, a.y, 4, dims, st, box, dc * 2, counted);
     if (a.residual) ok &= make_map(&p.tmR, a.residual, 4, dims, st, box, dc * 2, counted);
   }
+  // One channel tile: every tile multiplies by the same weights.  If they are tiny they are
+  // fetched once per CTA into an area of their own instead of once per tile into the ring: all
+  // CTAs asking L2 for the same 16 to 32 lines of weights for every tile is what bounded the
+  // few-channel layers (1.5x on 32->16 and 16->96 channels at 112x112).  Measured: no gain at
+  // 6 to 9 KB of weights, slower at 8 KB (64->64) and 32 KB (64->256 with residual).
+  const int ksteps_tile = p.num_taps * p.cblocks;
+  const size_t b_tile_bytes = (size_t)(pair ? bn / 2 : bn) * bk * 2;
+  bool bres = !pn && !halo && !pair && p.tiles_k == 1 && ksteps_tile * b_tile_bytes <= 4 * 1024;
+#ifdef OCCAMY_TUNING
+  if (const char *f = getenv("OCCAMY_TC_BRES")) bres = bres && atoi(f) != 0;
+#endif
+  p.b_resident = bres ? 1 : 0;
   // shared memory: ring + output slabs + bias + barriers + alignment
   const size_t stage_bytes = pn     ? (size_t)(128 + 256) * bk * 2
                              : halo ? (size_t)p.halo_a_bytes
-                                    : 128 * bk * 2 + (size_t)(pair ? bn / 2 : bn) * bk * 2;
+                                    : 128 * bk * 2 + (bres ? 0 : b_tile_bytes);
   p.bias_floats = (a.K + bn - 1) / bn * bn;
   const size_t slab_bytes = (size_t)128 * dc * 2;
   const size_t fixed0 = pn ? 1024 + 2 * 256 * 128 + 8 * 80
                            : (size_t)p.bias_floats * 4 + 8 * 80 +
-                                 (halo ? (size_t)9 * bn * bk * 2 : 0);   // halo: resident weights
-  int dbuf = pn ? 0 : (3 + TC_NSTORE - 1) / TC_NSTORE * TC_NSTORE;
-  if (a.out_f32) dbuf = TC_NSTORE;      // written straight from registers: no slabs are staged
-  int stages;
-  if (!pn && a.residual) {
-    // The residual slab of an output slab is fetched into its buffer ahead of time, and a
-    // slab is consumed faster than the fetch takes: whatever shared memory three ring stages
-    // leave goes to slab buffers.
-    int min_stages = 3;
+                                 (halo ? (size_t)9 * bn * bk * 2 : 0) +   // halo: resident weights
+                                 (bres ? ksteps_tile * b_tile_bytes : 0);
+  // Two CTAs per SM for the 32-channel tiles.  Such a tile is a few hundred cycles of memory
+  // traffic, but each of the single-threaded roles (loads, MMA issue, slab stores) spends about
+  // a thousand cycles of dependent instructions and barrier round trips on it; two resident
+  // CTAs overlap those (measured 1.2x to 1.6x on the layers with up to 32 output channels; no
+  // gain for 64-channel tiles).  They share the SM's shared memory, registers (one epilogue warp per TMEM
+  // quadrant, 256 threads) and TMEM (at most 256 columns each).
+  bool duo = !pn && !halo && !pair && !a.split && !a.out_f32 && dc == 32 && bn == 32 && nsm >= 2;
 #ifdef OCCAMY_TUNING
-    if (const char *f = getenv("OCCAMY_TC_RES_STAGES")) min_stages = atoi(f) > 1 ? atoi(f) : min_stages;
+  if (const char *f = getenv("OCCAMY_TC_DUO"))
+    duo = atoi(f) != 0 && !pn && !halo && !pair && !a.split && !a.out_f32 && dc == 32 && bn == 32;
 #endif
-    dbuf = (int)((TC_SMEM_LIMIT - fixed0 - min_stages * stage_bytes) / slab_bytes);
-    if (dbuf > 8) dbuf = 8;
-    if (dbuf < 3) dbuf = 3;
-    dbuf = dbuf / TC_NSTORE * TC_NSTORE;
-    if (dbuf < TC_NSTORE * 2) dbuf = TC_NSTORE * 2;
+  int dbuf = 0, pend = 0, stages = 0;
+  for (;; duo = false) {
+    const size_t limit = duo ? TC_SMEM_DUO : (size_t)TC_SMEM_LIMIT;
+    dbuf = pn ? 0 : (3 + TC_NSTORE - 1) / TC_NSTORE * TC_NSTORE;
+    if (a.out_f32) dbuf = TC_NSTORE;      // written straight from registers: no slabs are staged
+    if (!pn && a.residual && !duo) {
+      // The residual slab of an output slab is fetched into its buffer ahead of time, and a
+      // slab is consumed faster than the fetch takes: whatever shared memory three ring stages
+      // leave goes to slab buffers.
+      int min_stages = 3;
+#ifdef OCCAMY_TUNING
+      if (const char *f = getenv("OCCAMY_TC_RES_STAGES")) min_stages = atoi(f) > 1 ? atoi(f) : min_stages;
+#endif
+      dbuf = (int)((limit - fixed0 - min_stages * stage_bytes) / slab_bytes);
+      if (dbuf > 8) dbuf = 8;
+      if (dbuf < 3) dbuf = 3;
+      dbuf = dbuf / TC_NSTORE * TC_NSTORE;
+      if (dbuf < TC_NSTORE * 2) dbuf = TC_NSTORE * 2;
+    }
+    // Stores in flight.  A store thread may run ahead of `pend` unfinished stores; each needs a
+    // buffer of its own on top of the ones that are filling.  The aim is about 48 KB of stores
+    // in flight per SM, as long as four ring stages remain: the layers with long reductions
+    // need those more.
+    pend = 0;
+    if (!pn && !a.out_f32) {
+      const size_t aim = duo ? 24 * 1024 : 48 * 1024;
+      pend = (int)((aim + TC_NSTORE * slab_bytes - 1) / (TC_NSTORE * slab_bytes)) - 1;
+      if (pend > 3) pend = 3;
+#ifdef OCCAMY_TUNING
+      if (const char *f = getenv("OCCAMY_TC_STORE_PEND")) pend = atoi(f) < 0 ? 0 : (atoi(f) > 3 ? 3 : atoi(f));
+#endif
+      for (; pend > 0; --pend) {
+        const int need = TC_NSTORE * (pend + 2);   // pend + 1 in a store, one filling, per thread
+        if (dbuf >= need) break;
+        if (fixed0 + need * slab_bytes + (duo ? 3 : 4) * stage_bytes <= limit) {
+          dbuf = need;
+          break;
+        }
+      }
+    }
+    const size_t fixed = fixed0 + dbuf * slab_bytes;
+    stages = fixed < limit ? (int)((limit - fixed) / stage_bytes) : 0;
+    if (stages > 8) stages = 8;
+    pl.smem = fixed + stages * stage_bytes;
+    if (!duo || stages >= 3) break;
   }
-  const size_t fixed = fixed0 + dbuf * slab_bytes;
-  stages = (int)((TC_SMEM_LIMIT - fixed) / stage_bytes);
-  if (stages > 8) stages = 8;
   if (stages < 2) ok = false;
+  pl.duo = duo;
   p.stages = stages;
   p.dbuf = dbuf;
-  pl.smem = fixed + stages * stage_bytes;
-  if (pl.smem < 120 * 1024) pl.smem = 120 * 1024;  // keep one CTA per SM (TMEM is per SM)
+  p.store_pend = pend;
+  // one CTA per SM (TMEM is per SM), or two for the duo form (its registers allow no third)
+  if (!duo && pl.smem < 120 * 1024) pl.smem = 120 * 1024;
 #ifdef OCCAMY_TUNING
   if (getenv("OCCAMY_TC_PLAN_LOG"))
-    fprintf(stderr, "[tcplan] K %d Cf %d RS %d px %dx%dx%d box %dx%dx%d bn %d dc %d pn %d bk %d stages %d dbuf %d tiles %d smem %zu\n",
-            a.K, a.Cf, a.R * a.S, Qg, Pg, Ng, p.tw, p.th, p.tn, bn, dc, (int)pn, bk, stages, dbuf,
+    fprintf(stderr, "[tcplan] K %d Cf %d RS %d px %dx%dx%d box %dx%dx%d bn %d dc %d pn %d bk %d stages %d dbuf %d pend %d duo %d tiles %d smem %zu\n",
+            a.K, a.Cf, a.R * a.S, Qg, Pg, Ng, p.tw, p.th, p.tn, bn, dc, (int)pn, bk, stages, dbuf, pend, (int)duo,
             p.total_tiles, pl.smem);
 #endif
   if (halo && !ok) return build_plan(a, err_word, num_sms, counted, false);   // e.g. the block map was refused
@@ -684,6 +757,14 @@ static void launch_any(const Plan &pl, int num_sms, cudaStream_t s) {
     grid = 2 * pl.p.total_tiles < num_sms ? 2 * pl.p.total_tiles : num_sms / 2 * 2;
   }
   bool ok;
+  if (pl.duo) {
+    grid = pl.p.total_tiles < 2 * num_sms ? pl.p.total_tiles : 2 * num_sms;
+    ok = pl.bn == 32   ? tc_launch_32_32_duo(pl.p, pl.mode, grid, pl.smem, s)
+         : pl.bn == 64 ? tc_launch_64_64_duo(pl.p, pl.mode, grid, pl.smem, s)
+                       : tc_launch_128_64_duo(pl.p, pl.mode, grid, pl.smem, s);
+    if (!ok) set_error(997, "tensor-core conv: no two-per-SM kernel for this epilogue");
+    return;
+  }
   switch (pl.bn) {
     case 32: ok = tc_launch_32_32(pl.p, pl.mode, grid, pl.smem, s); break;
     case 64: ok = tc_launch_64_64(pl.p, pl.mode, grid, pl.smem, s); break;

@@ -20,6 +20,7 @@ constexpr int TC_DBUF = 3;           // output slab buffers in shared memory
 constexpr int TC_MAX_TAPS = 64;
 constexpr int TC_MAX_AMAPS = 12;      // A tensor maps: 4 stride phases x 3 operand parts
 constexpr int TC_SMEM_LIMIT = 232448;  // 227 KB
+constexpr size_t TC_SMEM_DUO = 113 * 1024;  // per CTA when two share an SM (1 KB each is reserved)
 
 // Division of a tile index (< 2^31) by a positive constant: q = umulhi(x, mul) >> shift,
 // with mul == 0 standing for a divisor of one.
@@ -58,7 +59,12 @@ struct alignas(64) TcParams {
   int halo_wp;           //   pixels per block row (output width + 2)
   int halo_a_bytes;      //   bytes of one staged block, a multiple of 1024
   int bias_floats;       // K rounded up to whole channel tiles: bias entries kept in shared memory
-  int dbuf;              // output slab buffers in shared memory (3..8)
+  int dbuf;              // output slab buffers in shared memory (an even number, 4..12)
+  int store_pend;        // stores a store thread may leave in flight behind its newest (0..3)
+  int b_resident;        // one channel tile: the weight tiles of all k-steps are fetched once per CTA
+#ifdef OCCAMY_TC_TIMERS
+  long long *timers;     // 5 roles x 4 counters, or null
+#endif
   int n_mma;             // pixel-N variant: N of the MMA (pixels per tile rounded up to 16)
   int sp_tiles;          // pixel tiles (tiles_w * tiles_h * tiles_n); with TC_MODE_PAIR the tile
                          // index counts PAIRS of them and total_tiles = ceil(sp_tiles / 2) * tiles_k
@@ -66,6 +72,29 @@ struct alignas(64) TcParams {
 };
 
 // Epilogue flavours the pixel-M kernel is compiled for (template parameter MODE).
+// Per-role wait timers of CTA 0, for analysis builds only (-DOCCAMY_TC_TIMERS): four counters per
+// role -- cycles in up to three kinds of wait and the role's total.
+#ifdef OCCAMY_TC_TIMERS
+#define TCT_DECL                      \
+  long long tct_[4] = {0, 0, 0, 0};   \
+  const long long tct_start_ = clock64();
+#define TCT_WAIT(i, expr)                \
+  ([&]() {                               \
+    const long long t_ = clock64();      \
+    const bool r_ = (expr);              \
+    tct_[i] += clock64() - t_;           \
+    return r_;                           \
+  }())
+#define TCT_FLUSH(slot)                                                  \
+  if (blockIdx.x == 0 && p.timers) {                                     \
+    for (int i_ = 0; i_ < 3; ++i_) p.timers[(slot) * 4 + i_] += tct_[i_]; \
+    p.timers[(slot) * 4 + 3] += clock64() - tct_start_;                  \
+  }
+#else
+#define TCT_DECL
+#define TCT_WAIT(i, expr) (expr)
+#define TCT_FLUSH(slot)
+#endif
 constexpr int TC_MODE_RES = 1;     // adds a residual tensor
 constexpr int TC_MODE_CLAMP = 2;   // general clamp to [lo, hi]; otherwise ReLU
 constexpr int TC_MODE_F32 = 4;     // fp32 row-major output straight to global memory (GEMM head)
@@ -480,8 +509,12 @@ __device__ __forceinline__ TcTile tc_decode(const TcParams &p, int tile, uint32_
 //   last warp         second MMA issuer of the halo form (idle otherwise)
 // Every wait on an mbarrier is bounded; when a bound is hit the kernel records a code in the
 // error word, drains and returns.
+// Threads of a CTA: producer and MMA warps, 4 * EW epilogue warps, the slab-store warps and (for
+// the halo form, which exists with EW == 2 only) the warp of the second MMA issuer.
+constexpr int tc_block_threads(int ew) { return 64 + 128 * ew + 32 * TC_NSTORE + (ew == 1 ? 0 : 32); }
+
 template <int BN, int DC, int EW, int MODE>
-__global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
+__global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
     tc_conv_kernel(const __grid_constant__ TcParams p) {
   constexpr bool RES = (MODE & TC_MODE_RES) != 0;
   constexpr bool CLAMP = (MODE & TC_MODE_CLAMP) != 0;
@@ -521,7 +554,11 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   const uint32_t b_bytes = (uint32_t)BROWS * bk * 2u;
   const uint32_t sA = base;
   const uint32_t sB = sA + stages * a_bytes;
-  const uint32_t sD = sB + (HALO ? (uint32_t)p.num_taps : (uint32_t)stages) * b_bytes;   // dbuf output slabs
+  // weight tiles: one per ring stage, or (halo form, resident form) one per k-step of a tile
+  const bool bres = !HALO && !PAIR && p.b_resident != 0;
+  const uint32_t b_slots = HALO ? (uint32_t)p.num_taps
+                                : (bres ? (uint32_t)(p.num_taps * p.cblocks) : (uint32_t)stages);
+  const uint32_t sD = sB + b_slots * b_bytes;   // dbuf output slabs
   const uint32_t sMisc = sD + dbuf * SLAB_BYTES;
   uint8_t *misc_ptr = base_ptr + (sMisc - base);
   float *bias_s = reinterpret_cast<float *>(misc_ptr);          // bias of every output channel
@@ -594,11 +631,21 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
   // previous kernel in the stream.  Resident weights may be fetched early as well: the
   // producer requests the weight tiles of its first k-steps (halo form: all of them) now.
   int pre_b = 0;   // leading k-steps of the first tile whose weight tile is already on its way
+  // resident form: the weight tiles of every k-step, once, announced on the "weights landed" barrier
+  auto load_resident_b = [&]() {
+    mbar_expect_tx(wfull_bar, (uint32_t)ksteps * b_bytes);
+    int i = 0;
+    for (int t = 0; t < p.num_taps; ++t)
+      for (int cb = 0; cb < p.cblocks; ++cb, ++i)
+        tma_load_3d(sB + i * b_bytes, &p.tmB, wfull_bar, cb * bk, 0, t);
+  };
   if (!PAIR && warp == 0 && lane == 0 && p.consts_ready && (int)blockIdx.x < p.total_tiles) {
     if constexpr (HALO) {
       mbar_expect_tx(wfull_bar, (uint32_t)p.num_taps * b_bytes);
       for (int t = 0; t < p.num_taps; ++t)
         tma_load_3d(sB + t * b_bytes, &p.tmB, wfull_bar, 0, 0, t);
+    } else if (bres) {
+      load_resident_b();
     } else {
       const TcTile tl = tc_decode<BN>(p, blockIdx.x);
       pre_b = min(stages, ksteps);
@@ -645,13 +692,15 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           }
         }
       } else {
-      const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + b_bytes;
+      const uint32_t tx_bytes = (uint32_t)rows_valid * bk * 2u + (bres ? 0u : b_bytes);
+      if (bres && !p.consts_ready) load_resident_b();
+      TCT_DECL
       for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
         const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank);
         for (int t = 0; t < p.num_taps && !err_code; ++t) {
           const TcTap tap = p.taps[t];
           for (int cb = 0; cb < p.cblocks; ++cb) {
-            if (!mbar_wait_hot(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            if (!TCT_WAIT(0, mbar_wait_hot(empty_bar(stage), phase ^ 1u, abort_flag))) {
               err_code = 1;
               break;
             }
@@ -672,6 +721,8 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
             }
             if (pre_b > 0) {
               --pre_b;   // this stage's barrier is armed and its weight tile on its way
+            } else if (bres) {
+              mbar_expect_tx(full_bar(stage), tx_bytes);   // the weights are resident
             } else {
               mbar_expect_tx(full_bar(stage), tx_bytes);
               tma_load_3d(sB + stage * b_bytes, &p.tmB, full_bar(stage), cb * bk, tl.k0, t);
@@ -685,6 +736,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           }
         }
       }
+      TCT_FLUSH(0)
       }
     }
   } else if (warp == 1 || (HALO && warp == STORE_WARP + TC_NSTORE)) {
@@ -740,8 +792,10 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           tc_commit(tfull_bar(my_acc));
         }
       } else {
+      TCT_DECL
+      if (bres && !mbar_wait_hot(wfull_bar, 0, abort_flag)) err_code = 3;
       for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
-        if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+        if (!TCT_WAIT(0, mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) {
           err_code = 2;
           break;
         }
@@ -751,13 +805,13 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
         uint32_t accumulate = 0, accumulate_corr = 0;
         int cb_in_tap = 0, combo = 0;   // split operands: position inside the six-tap group
         for (int ks = 0; ks < ksteps; ++ks) {
-          if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
+          if (!TCT_WAIT(1, mbar_wait_hot(full_bar(stage), phase, abort_flag))) {
             err_code = 3;
             break;
           }
           tc_fence_after();
           const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
-          const uint64_t bdesc = make_smem_desc(sB + stage * b_bytes, bk);
+          const uint64_t bdesc = make_smem_desc(sB + (bres ? ks : stage) * b_bytes, bk);
           if constexpr (SPLIT) {
             // tap 0 of every group of six is hi * hi: main accumulator; the rest: corrections
             const bool corr = combo != 0;
@@ -795,6 +849,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
+      TCT_FLUSH(1)
       }
     }
   } else if (warp >= STORE_WARP && warp < STORE_WARP + TC_NSTORE) {
@@ -840,6 +895,8 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
         };
         for (int i = 0; i < dbuf / TC_NSTORE; ++i) ready_one();     // every buffer starts out free
         uint32_t d = 0;   // running slab number
+        uint32_t mine = 0;   // stores this thread has issued
+        TCT_DECL
         for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
           bool ghost = false;
           const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank, &ghost);
@@ -847,23 +904,37 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           for (int sl = 0; sl < nslab; ++sl, ++d) {
             if (d % TC_NSTORE != me) continue;
             const uint32_t b = d % (uint32_t)dbuf, ph = (d / (uint32_t)dbuf) & 1u;
-            if (!mbar_wait(dfull_bar(b), ph, abort_flag)) {
+            if (!TCT_WAIT(0, mbar_wait(dfull_bar(b), ph, abort_flag))) {
               err_code = 6;
               break;
             }
             if (!ghost)   // the duplicate tile of an odd last pair is computed, not stored
               tma_store_4d(&p.tmD, sD + b * SLAB_BYTES, tl.k0 + sl * DC, tl.q0, tl.p0, tl.n0);
             tma_store_commit();
-            // The store has read its buffer out long before my next slab is written (the
-            // other store thread's slab comes in between), so wait for that here and give
-            // the buffer straight to the slab dbuf further on: every buffer that is not in
-            // this one store is then filling (residual fetch, epilogue), which is what hides
-            // the residual's memory latency.
-            tma_store_wait_read<0>();
-            ready_one();
+            // A store gives its buffer back only after about a memory latency (1 to 2 us
+            // under load), and the bytes of the stores in flight over that time are what
+            // bounds the write bandwidth of an SM: with narrow slabs one store per thread is
+            // far too little.  So up to store_pend of my earlier stores may still be reading
+            // their buffers; the one before those is done, and its buffer goes to the slab
+            // dbuf further on.  Every buffer that is not in a store is then filling (residual
+            // fetch, epilogue), which is also what hides the residual's memory latency.
+#ifdef OCCAMY_TC_TIMERS
+            const long long tw_ = clock64();
+#endif
+            switch (p.store_pend) {
+              case 0: tma_store_wait_read<0>(); break;
+              case 1: tma_store_wait_read<1>(); break;
+              case 2: tma_store_wait_read<2>(); break;
+              default: tma_store_wait_read<3>(); break;
+            }
+#ifdef OCCAMY_TC_TIMERS
+            tct_[1] += clock64() - tw_;
+#endif
+            if (mine++ >= (uint32_t)p.store_pend) ready_one();
           }
         }
         tma_store_wait_read<0>();
+        if (me == 0) { TCT_FLUSH(4) }
       }
     }
   } else if (warp < STORE_WARP) {
@@ -886,6 +957,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
     uint32_t acc_phase = 0;
     uint32_t buf = 0, buf_phase = 0;         // slab buffer the next slab goes through
 
+    TCT_DECL
     for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
       const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank);
       const int nslab = min(NSLAB, (p.K - tl.k0 + DC - 1) / DC);
@@ -903,7 +975,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           f32_base = img * (int64_t)p.K * p.out_hw + (lin - img * p.out_hw);
         }
       }
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+      if (!TCT_WAIT(0, mbar_wait(tfull_bar(acc), acc_phase, abort_flag))) {
         err_code = 4;
         break;
       }
@@ -965,7 +1037,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
           return true;
         } else {
           // the buffer is free, or (residual) holds the slab to add
-          if (!mbar_wait(rfull_bar(buf), buf_phase, abort_flag)) return false;
+          if (!TCT_WAIT(1, mbar_wait(rfull_bar(buf), buf_phase, abort_flag))) return false;
           uint8_t *dptr = base_ptr + (sD - base) + buf * SLAB_BYTES;
           if constexpr (RES) {
 #pragma unroll
@@ -1043,6 +1115,7 @@ __global__ void __launch_bounds__(64 + 128 * EW + 32 * TC_NSTORE + 32, 1)
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (lane == 0 && quad == 0) { TCT_FLUSH(2 + part) }
   }
 
   if (err_code) {
@@ -1075,6 +1148,9 @@ bool tc_launch_256_32(const TcParams &p, int mode, int grid, size_t smem, cudaSt
 bool tc_launch_128_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
 bool tc_launch_64_64(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
 bool tc_launch_32_32(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+bool tc_launch_32_32_duo(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+bool tc_launch_64_64_duo(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
+bool tc_launch_128_64_duo(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s);
 
 // Launch with programmatic stream serialisation (see pdl_wait); `cluster` > 1 launches the
 // grid as thread-block clusters of that many CTAs.
@@ -1115,14 +1191,31 @@ inline bool tc_first_use_on_device(unsigned char (&done)[TC_MAX_DEVICES]) {
 
 // Body shared by the launchers: picks the instantiation for `mode`, raises its dynamic
 // shared memory limit once per device, launches.
-template <int BN, int DC, int MODE>
+template <int BN, int DC, int MODE, int EW = TC_EW>
 inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t s) {
   static unsigned char attr_done[TC_MAX_DEVICES] = {};
   if (tc_first_use_on_device(attr_done))
-    cudaFuncSetAttribute(tc_conv_kernel<BN, DC, TC_EW, MODE>,
+    cudaFuncSetAttribute(tc_conv_kernel<BN, DC, EW, MODE>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
-  tc_launch_pdl(tc_conv_kernel<BN, DC, TC_EW, MODE>, grid, 64 + 128 * TC_EW + 32 * TC_NSTORE + 32, smem,
+  tc_launch_pdl(tc_conv_kernel<BN, DC, EW, MODE>, grid, tc_block_threads(EW), smem,
                 s, p, (MODE & TC_MODE_PAIR) ? 2 : 1);
+}
+// The 16-bit flavours of a tile shape with one epilogue warp per TMEM quadrant: a CTA of
+// 256 threads, two of which fit an SM.
+template <int BN, int DC>
+inline bool tc_launch_mode_duo(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
+  constexpr int H = TC_MODE_F16, R = TC_MODE_RES, C = TC_MODE_CLAMP;
+  switch (mode) {
+    case 0: tc_launch_one<BN, DC, 0, 1>(p, grid, smem, s); return true;
+    case R: tc_launch_one<BN, DC, R, 1>(p, grid, smem, s); return true;
+    case C: tc_launch_one<BN, DC, C, 1>(p, grid, smem, s); return true;
+    case R | C: tc_launch_one<BN, DC, R | C, 1>(p, grid, smem, s); return true;
+    case H: tc_launch_one<BN, DC, H, 1>(p, grid, smem, s); return true;
+    case H | R: tc_launch_one<BN, DC, H | R, 1>(p, grid, smem, s); return true;
+    case H | C: tc_launch_one<BN, DC, H | C, 1>(p, grid, smem, s); return true;
+    case H | R | C: tc_launch_one<BN, DC, H | R | C, 1>(p, grid, smem, s); return true;
+    default: return false;
+  }
 }
 template <int BN, int DC, bool WITH_F32, bool WITH_HALO = false>
 inline bool tc_launch_mode(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {

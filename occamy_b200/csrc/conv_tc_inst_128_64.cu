@@ -8,4 +8,8 @@ bool tc_launch_128_64(const TcParams &p, int mode, int grid, size_t smem, cudaSt
   return tc_launch_mode<128, 64, true>(p, mode, grid, smem, s);
 }
 
+bool tc_launch_128_64_duo(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
+  return tc_launch_mode_duo<128, 64>(p, mode, grid, smem, s);
+}
+
 }  // namespace occ

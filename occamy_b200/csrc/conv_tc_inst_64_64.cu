@@ -8,4 +8,8 @@ bool tc_launch_64_64(const TcParams &p, int mode, int grid, size_t smem, cudaStr
   return tc_launch_mode<64, 64, true, true>(p, mode, grid, smem, s);
 }
 
+bool tc_launch_64_64_duo(const TcParams &p, int mode, int grid, size_t smem, cudaStream_t s) {
+  return tc_launch_mode_duo<64, 64>(p, mode, grid, smem, s);
+}
+
 }  // namespace occ

@@ -180,7 +180,15 @@ CONV_ROWS = [("conv3x3 256->256 @14", 256, 256, 3, 14, 1, False),
              # MobileNetV2's few-channel layers on large images
              ("conv1x1 32->16 @112", 32, 16, 1, 112, 1, False),
              ("conv1x1 16->96 @112", 16, 96, 1, 112, 1, False),
-             ("conv1x1 144->24 @56", 144, 24, 1, 56, 1, False)]
+             ("conv1x1 144->24 @56", 144, 24, 1, 56, 1, False),
+             # short reductions into few channels: two CTAs share an SM
+             ("conv1x1 64->64 @56", 64, 64, 1, 56, 1, False),
+             ("conv1x1 256->64 @56", 256, 64, 1, 56, 1, False),
+             ("conv1x1 256->128 /2 @56", 256, 128, 1, 56, 2, False),
+             ("conv1x1 96->24 @56", 96, 24, 1, 56, 1, False),
+             ("conv1x1 192->32 @28", 192, 32, 1, 28, 1, False),
+             ("conv1x1 384->64 @14", 384, 64, 1, 14, 1, False),
+             ("conv1x1 576->96 @14", 576, 96, 1, 14, 1, False)]
 
 
 def _conv_rows(h, rng, B, L, timed, wanted):
