@@ -556,10 +556,39 @@ template <int NP>
 struct DwRow {
   uint64_t v[3][NP];   // three columns x NP channel pairs as fp32 pairs
 };
+// packed fp16 arithmetic (fp16 mode): two channels per 32-bit word, no conversions
+struct DwRowH {
+  uint32_t v[3][4];    // three columns x eight channels
+};
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+__device__ __forceinline__ uint32_t h2_max_nan(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t h2_min_nan(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t h2_from_floats(float a, float b) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
 
 // CH = channels per thread: 4 (two CTAs per SM); 2 also compiles (four CTAs per SM) but is slower.
-template <int ST, bool PACKED_ACT, int CH, bool F16>
-__global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel(
+// H2 (fp16 mode, CH = 8, bounds that fp16 holds exactly): the thread owns all eight channels of
+// a 16-byte piece and computes on packed fp16 pairs as they lie in memory -- nine fma.rn.f16x2
+// per pair and output, sums kept in fp16 -- which cuts the instructions per output from about
+// 22 to about 7 and leaves the kernel to the memory system.  The sum of nine products of
+// values that the 1x1 layers then average is rounded to 11 bits nine times: below the 16-bit
+// storage rounding of the other layers, and inside the mode's 2e-2 on the logits (tested).
+template <int ST, bool PACKED_ACT, int CH, bool F16, bool H2 = false>
+__global__ void __launch_bounds__(256, CH == 2 ? 4 : 2) depthwise3x3_tile_kernel(
     const uint4 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
     uint32_t *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c, int ntiles,
     int run_len, int run_total, float act_lo, float act_hi, int act_flags, uint32_t act_hi2) {
@@ -627,11 +656,37 @@ __global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  uint64_t wv[9][NP];
+  static_assert(!H2 || (CH == 8 && F16 && PACKED_ACT), "packed fp16 arithmetic: eight channels, fp16");
+  constexpr int NW = H2 ? 9 : 1, NV = H2 ? 1 : 9;   // only one of the two weight sets exists
+  uint32_t wh[NW][4];    // H2: nine taps x eight channels as fp16 pairs
+  uint32_t bh[4] = {0u, 0u, 0u, 0u};
+  uint64_t wv[NV][NP];
   uint64_t bv[NP];
 #pragma unroll
   for (int j = 0; j < NP; ++j) bv[j] = 0;
-  if (active) {
+  if constexpr (H2) {
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      if (active) {
+        const float4 *wp = (const float4 *)(w + (int64_t)t * g.C + c8 * 8);
+        a = wp[0];
+        b = wp[1];
+      }
+      wh[t][0] = h2_from_floats(a.x, a.y);
+      wh[t][1] = h2_from_floats(a.z, a.w);
+      wh[t][2] = h2_from_floats(b.x, b.y);
+      wh[t][3] = h2_from_floats(b.z, b.w);
+    }
+    if (active && bias) {
+      const float4 *bp = (const float4 *)(bias + c8 * 8);
+      const float4 a = bp[0], b = bp[1];
+      bh[0] = h2_from_floats(a.x, a.y);
+      bh[1] = h2_from_floats(a.z, a.w);
+      bh[2] = h2_from_floats(b.x, b.y);
+      bh[3] = h2_from_floats(b.z, b.w);
+    }
+  } else if (active) {
 #pragma unroll
     for (int t = 0; t < 9; ++t) {
       const float2 *wp = (const float2 *)(w + (int64_t)t * g.C + c8 * 8 + sub * CH);
@@ -673,6 +728,63 @@ __global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel
       const uint32_t *src = reinterpret_cast<const uint32_t *>(dw_smem + buf * stage_vecs) +
                             ((col * ST) * G + gl) * 4 + sub * NP;
       uint32_t *yout = y + ((int64_t)n * g.P * g.Q + q) * C8 * 4 + c8 * 4 + sub * NP;
+      if constexpr (H2) {
+        auto load_row = [&](int ih, DwRowH &r) {
+#pragma unroll
+          for (int k = 0; k < 3; ++k) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(src + (ih * IW + k) * G * 4);
+            r.v[k][0] = v.x;
+            r.v[k][1] = v.y;
+            r.v[k][2] = v.z;
+            r.v[k][3] = v.w;
+          }
+        };
+        auto emit = [&](int p, const DwRowH &a, const DwRowH &bq, const DwRowH &cq) {
+          if (p >= g.P) return;
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t f = bh[j];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) f = h2_fma(a.v[k][j], wh[k][j], f);
+#pragma unroll
+            for (int k = 0; k < 3; ++k) f = h2_fma(bq.v[k][j], wh[3 + k][j], f);
+#pragma unroll
+            for (int k = 0; k < 3; ++k) f = h2_fma(cq.v[k][j], wh[6 + k][j], f);
+            if (act_flags & 1) f = h2_max_nan(f, 0u);
+            if (act_flags & 2) f = h2_min_nan(f, act_hi2);
+            o[j] = f;
+          }
+          *reinterpret_cast<uint4 *>(yout + (int64_t)p * g.Q * C8 * 4) = make_uint4(o[0], o[1], o[2], o[3]);
+        };
+        DwRowH r0, r1, r2;
+        const int pbase = t * TH;
+        if (ST == 1) {
+          load_row(0, r0);
+          load_row(1, r1);
+          for (int pl = 0; pl < TH; pl += 3) {
+            load_row(pl + 2, r2);
+            emit(pbase + pl, r0, r1, r2);
+            load_row(pl + 3, r0);
+            emit(pbase + pl + 1, r1, r2, r0);
+            load_row(pl + 4, r1);
+            emit(pbase + pl + 2, r2, r0, r1);
+          }
+        } else {
+          load_row(0, r0);
+          for (int pl = 0; pl < TH; pl += 3) {
+            load_row(2 * pl + 1, r1);
+            load_row(2 * pl + 2, r2);
+            emit(pbase + pl, r0, r1, r2);
+            load_row(2 * pl + 3, r0);
+            load_row(2 * pl + 4, r1);
+            emit(pbase + pl + 1, r2, r0, r1);
+            load_row(2 * pl + 5, r2);
+            load_row(2 * pl + 6, r0);
+            emit(pbase + pl + 2, r1, r2, r0);
+          }
+        }
+      } else {
       auto load_row = [&](int ih, DwRow<NP> &r) {
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
@@ -738,8 +850,177 @@ __global__ void __launch_bounds__(256, CH == 4 ? 2 : 4) depthwise3x3_tile_kernel
           emit(pbase + pl + 2, r1, r2, r0);
         }
       }
+      }
     }
     buf = buf == 2 ? 0 : buf + 1;
+  }
+}
+
+// 3x3 depthwise convolution in packed fp16 arithmetic without shared memory.  A thread owns the
+// eight channels of one 16-byte piece in one output column and walks down a strip of output
+// rows: the input rows of its window stay in registers (each is loaded once per thread), the
+// three columns of a row are three 16-byte loads that the neighbouring threads' loads overlap
+// (L1 serves the overlap), and the rows of the next two outputs are requested before the
+// current output is computed.  Lanes run over the channel pieces of a pixel first, then over columns, so every
+// load and store of a warp is one contiguous run of bytes.  About 7 instructions per output
+// (nine fma.rn.f16x2 per channel pair) against about 20 for the staged tile kernel.
+struct DwRow8 {
+  uint4 c[3];   // three input columns x eight channels (fp16 pairs)
+};
+__device__ __forceinline__ uint32_t dw_word(const uint4 &v, int j) {
+  return j == 0 ? v.x : (j == 1 ? v.y : (j == 2 ? v.z : v.w));
+}
+__device__ __forceinline__ uint4 dw_ldg16(const uint4 *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+template <int ST>
+__global__ void __launch_bounds__(128, 4)
+    depthwise3x3_strip_h2_kernel(const uint4 *__restrict__ x, const float *__restrict__ w,
+                                 const float *__restrict__ bias, uint4 *__restrict__ y, ConvGeom g,
+                                 int strips, int strip_rows, int64_t total, int act_flags,
+                                 uint32_t act_hi2, int ahead) {
+  const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;   // the launcher keeps total < 2^31
+  if (idx >= (uint32_t)total) return;
+  const int C8 = g.C / 8;
+  const int c8 = (int)(idx % (uint32_t)C8);
+  uint32_t r = idx / (uint32_t)C8;
+  const int q = (int)(r % (uint32_t)g.Q);
+  r /= (uint32_t)g.Q;
+  const int sidx = (int)(r % (uint32_t)strips);
+  const int n = (int)(r / (uint32_t)strips);
+  const int p0 = sidx * strip_rows;
+  const int p1 = min(p0 + strip_rows, g.P);
+  if (p0 >= p1) return;
+
+  uint32_t wh[9][4], bh[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+  for (int t = 0; t < 9; ++t) {
+    const float4 *wp = reinterpret_cast<const float4 *>(w + (int64_t)t * g.C + c8 * 8);
+    const float4 a = wp[0], b = wp[1];
+    wh[t][0] = h2_from_floats(a.x, a.y);
+    wh[t][1] = h2_from_floats(a.z, a.w);
+    wh[t][2] = h2_from_floats(b.x, b.y);
+    wh[t][3] = h2_from_floats(b.z, b.w);
+  }
+  if (bias) {
+    const float4 *bp = reinterpret_cast<const float4 *>(bias + c8 * 8);
+    const float4 a = bp[0], b = bp[1];
+    bh[0] = h2_from_floats(a.x, a.y);
+    bh[1] = h2_from_floats(a.z, a.w);
+    bh[2] = h2_from_floats(b.x, b.y);
+    bh[3] = h2_from_floats(b.z, b.w);
+  }
+  // Input columns of the window.  A column outside the image (first and last output column
+  // only) is read from the middle column instead and its three taps get weight zero, so the
+  // loop has no per-column test.
+  const int w0 = q * ST - g.pad_w;
+  const bool cok0 = w0 >= 0 && w0 < g.W, cok2 = w0 + 2 >= 0 && w0 + 2 < g.W;
+#pragma unroll
+  for (int t = 0; t < 9; t += 3)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (!cok0) wh[t][j] = 0u;
+      if (!cok2) wh[t + 2][j] = 0u;
+    }
+  const int64_t row_pieces = (int64_t)g.W * C8;
+  const int off0 = cok0 ? 0 : C8, off2 = cok2 ? 2 * C8 : C8;   // piece offsets inside a row
+  const int h_first = p0 * ST - g.pad_h;                 // first input row of the strip
+  const int h_last = min((p1 - 1) * ST - g.pad_h + 2, g.H - 1);   // last one it reads
+  // next row to load: rows are loaded strictly in order, so the pointer just steps
+  const uint4 *rp = x + (((int64_t)n * g.H + h_first) * g.W + w0) * C8 + c8;
+  int h_next = h_first;
+  // Rows further down are asked into L2 ahead of time (one request per thread for its middle
+  // column; a warp's requests cover its contiguous run of the row): the register window then
+  // only has to cover the L2 latency, not the DRAM latency.  Stride 2 has enough in flight.
+  auto load = [&](DwRow8 &row) {
+    if (h_next >= 0 && h_next <= h_last) {   // the same for all threads of a warp
+      row.c[0] = dw_ldg16(rp + off0);
+      row.c[1] = dw_ldg16(rp + C8);
+      row.c[2] = dw_ldg16(rp + off2);
+      if (ST == 1 && h_next + ahead <= h_last)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(rp + (int64_t)ahead * row_pieces + C8));
+    } else {
+      row.c[0] = row.c[1] = row.c[2] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    rp += row_pieces;
+    ++h_next;
+  };
+  // bounds as packed halves; "none" is -inf / +inf, so that both are always applied
+  const uint32_t lo2 = (act_flags & 1) ? 0u : 0xFC00FC00u;
+  const uint32_t hi2 = (act_flags & 2) ? act_hi2 : 0x7C007C00u;
+  uint4 *yp = y + (((int64_t)n * g.P + p0) * g.Q + q) * C8 + c8;
+  const int64_t out_row = (int64_t)g.Q * C8;
+  auto emit = [&](const DwRow8 &a, const DwRow8 &b, const DwRow8 &c) {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t f = bh[j];
+#pragma unroll
+      for (int k = 0; k < 3; ++k) f = h2_fma(dw_word(a.c[k], j), wh[k][j], f);
+#pragma unroll
+      for (int k = 0; k < 3; ++k) f = h2_fma(dw_word(b.c[k], j), wh[3 + k][j], f);
+#pragma unroll
+      for (int k = 0; k < 3; ++k) f = h2_fma(dw_word(c.c[k], j), wh[6 + k][j], f);
+      o[j] = h2_min_nan(h2_max_nan(f, lo2), hi2);
+    }
+    *yp = make_uint4(o[0], o[1], o[2], o[3]);
+    yp += out_row;
+  };
+  const int nout = p1 - p0;
+  if (ST == 1) {
+    // one new row per output, requested two outputs ahead: five row buffers in rotation
+    DwRow8 A, B, C, D, E;
+    load(A);
+    load(B);
+    load(C);
+    load(D);
+    for (int i = 0; i < nout; i += 5) {
+      load(E);
+      emit(A, B, C);
+      if (i + 1 >= nout) break;
+      load(A);
+      emit(B, C, D);
+      if (i + 2 >= nout) break;
+      load(B);
+      emit(C, D, E);
+      if (i + 3 >= nout) break;
+      load(C);
+      emit(D, E, A);
+      if (i + 4 >= nout) break;
+      load(D);
+      emit(E, A, B);
+    }
+  } else {
+    // stride 2: an output shares one input row with the next; two new rows per output
+    DwRow8 A, B, C, D, E;
+    load(A);
+    load(B);
+    load(C);
+    for (int i = 0; i < nout; i += 5) {
+      load(D);
+      load(E);
+      emit(A, B, C);
+      if (i + 1 >= nout) break;
+      load(A);
+      load(B);
+      emit(C, D, E);
+      if (i + 2 >= nout) break;
+      load(C);
+      load(D);
+      emit(E, A, B);
+      if (i + 3 >= nout) break;
+      load(E);
+      load(A);
+      emit(B, C, D);
+      if (i + 4 >= nout) break;
+      load(B);
+      load(C);
+      emit(D, E, A);
+    }
   }
 }
 
@@ -762,48 +1043,101 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
                         (act_hi == INFINITY || host_elem_value(hbits, f16) == act_hi);
     // Channels per thread: 4.  (2 halves the registers and doubles the resident CTAs, but the
     // kernel is bound by its instruction count, which grows: measured 1.4x slower.)
-    const int CH = 4;
+    // fp16 mode with bounds fp16 holds: 8, computed on packed fp16 pairs (see the kernel).
+    bool h2 = f16 && packed;
+#ifdef OCCAMY_TUNING
+    if (const char *f = getenv("OCCAMY_DW_H2")) h2 = h2 && atoi(f) != 0;
+#endif
+    // the kernel relies on a valid middle column and on 32-bit thread numbers
+    bool strip = h2 && g.pad_w >= 0 && g.pad_w <= 1 && total * 16 < (int64_t)1 << 31;
+#ifdef OCCAMY_TUNING
+    if (const char *f = getenv("OCCAMY_DW_STRIP")) strip = strip && atoi(f) != 0;
+#endif
+    if (strip) {
+      // Register strips (see the kernel): enough strips per column for a few waves of threads,
+      // but at least seven output rows each, so that the two halo rows and the weights a
+      // thread fetches stay a small part of its traffic.
+      const int64_t base = (int64_t)g.N * g.Q * C8;
+      // waves of threads the strips are cut for (measured: 2 best at stride 1, 4 at stride 2;
+      // 8 and 16 are 10 to 25 % slower) and rows ahead of the loads that are asked into L2
+      int waves = ST == 1 ? 2 : 4, ahead = 4;
+#ifdef OCCAMY_TUNING
+      if (const char *f = getenv("OCCAMY_DW_WAVES")) waves = atoi(f) > 0 ? atoi(f) : waves;
+      if (const char *f = getenv("OCCAMY_DW_AHEAD")) ahead = atoi(f) > 0 ? atoi(f) : ahead;
+#endif
+      const int64_t want = (int64_t)rt().num_sms * 512 * waves;
+      int strips = (int)((want + base - 1) / base);
+      const int most = g.P / 7 > 1 ? g.P / 7 : 1;
+      if (strips > most) strips = most;
+      if (strips < 1) strips = 1;
+      const int strip_rows = (g.P + strips - 1) / strips;
+      strips = (g.P + strip_rows - 1) / strip_rows;
+      const int64_t threads = base * strips;
+      const unsigned grid = (unsigned)((threads + 127) / 128);
+      const int act_flags = (act_lo == 0.0f ? 1 : 0) | (act_hi != INFINITY ? 2 : 0);
+      const uint32_t act_hi2 = (uint32_t)hbits * 0x10001u;
+      if (ST == 1)
+        depthwise3x3_strip_h2_kernel<1><<<grid, 128, 0, s>>>((const uint4 *)x, w_rsc, bias, (uint4 *)y, g,
+                                                            strips, strip_rows, threads, act_flags, act_hi2, ahead);
+      else
+        depthwise3x3_strip_h2_kernel<2><<<grid, 128, 0, s>>>((const uint4 *)x, w_rsc, bias, (uint4 *)y, g,
+                                                            strips, strip_rows, threads, act_flags, act_hi2, ahead);
+      count(CNT_LAUNCHES);
+      return;
+    }
+    const int CH = h2 ? 8 : 4;
     const int LG = 8 / CH;
-    int G = 0, cols = 0, tiles_q = 0;
+    // Geometry: G channel groups x `cols` columns per CTA (G * cols * LG <= 256 threads) and TH
+    // output rows per staged tile (a multiple of 3, the register rotation; three buffers within
+    // the CTA's share of the shared memory).  Scored by the share of threads with work times the
+    // share of the staged input that is not halo; a tile row may have at most 512 pieces (two per
+    // thread in the staging loop).
+    int G = 0, cols = 0, tiles_q = 0, TH = 0, ntiles = 0;
     double best = 0.0;
+    const size_t smem_cap = (size_t)(CH == 2 ? 50 : 100) * 1024;
     for (int cand = 16; cand >= 1; --cand) {
       if (C8 % cand) continue;
       const int cmax = 256 / (LG * cand);
       if (cmax < 1) continue;
-      const int tq = (g.Q + cmax - 1) / cmax;
-      const int cl = (g.Q + tq - 1) / tq;
-      const double util = (double)(cl * cand * LG) / 256.0 * (double)g.Q / (double)(cl * tq);
-      if (util > best * 1.05) {
-        best = util;
-        G = cand;
-        cols = cl;
-        tiles_q = tq;
+      const int tq0 = (g.Q + cmax - 1) / cmax;
+      for (int tq = tq0; tq <= tq0 + 3 && tq <= g.Q; ++tq) {
+        const int cl = (g.Q + tq - 1) / tq;
+        const int iw = (cl - 1) * ST + 3;
+        if (iw * cand > 512) continue;
+        int th_best = 0;
+        int64_t rows_best = 0;
+        for (int th = 3; th <= 18; th += 3) {
+          const int ih = (th - 1) * ST + 3;
+          if ((size_t)3 * ih * iw * cand * 16 > smem_cap) break;
+          const int64_t rows = (int64_t)((g.P + th - 1) / th) * ih;
+          if (th_best == 0 || rows < rows_best) {
+            th_best = th;
+            rows_best = rows;
+          }
+        }
+        if (th_best == 0) continue;
+        const double util = (double)(cl * cand * LG) / 256.0 * (double)g.Q / (double)(cl * tq);
+        const double fresh = (double)(g.P * ST) / (double)rows_best * (double)(cl * ST) / (double)iw;
+        const double score = util * (fresh < 1.0 ? fresh : 1.0);
+        if (score > best * 1.03) {
+          best = score;
+          G = cand;
+          cols = cl;
+          tiles_q = tq;
+          TH = th_best;
+          ntiles = (g.P + th_best - 1) / th_best;
+        }
       }
     }
     const int IW = (cols - 1) * ST + 3;
-    // Rows per tile (a multiple of 3, the register rotation): the choice that stages the fewest
-    // input rows over an image, three buffers within the CTA's share of the shared memory.
-    int TH = 0, ntiles = 0;
-    int64_t best_rows = 0;
-    for (int th = 3; th <= 18; th += 3) {
-      const int ih = (th - 1) * ST + 3;
-      if ((size_t)3 * ih * IW * G * 16 > (size_t)(CH == 4 ? 100 : 50) * 1024) break;
-      const int nt = (g.P + th - 1) / th;
-      const int64_t rows = (int64_t)nt * ih;
-      if (TH == 0 || rows < best_rows) {
-        TH = th;
-        ntiles = nt;
-        best_rows = rows;
-      }
-    }
-    if (G > 0 && TH > 0 && best >= 0.4) {
+    if (G > 0 && TH > 0 && best >= 0.25) {
       const size_t smem = (size_t)3 * ((TH - 1) * ST + 3) * IW * G * 16;
       const int tiles_c = C8 / G;
       // Runs of (image, row tile) pairs: one wave of equal runs over the CTA slots when the
       // strips alone do not fill them, else one run per strip.
       const int run_total = g.N * ntiles;
       const int base = tiles_q * tiles_c;
-      const int slots = rt().num_sms * (CH == 4 ? 2 : 4);
+      const int slots = rt().num_sms * (CH == 2 ? 4 : 2);
       int runs = slots / base;
       if (runs < 1) runs = 1;
       if (runs > run_total) runs = run_total;
@@ -827,13 +1161,18 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false, 4, true>, attr, lim);
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 4, true>, attr, lim);
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false, 4, true>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true, 8, true, true>, attr, lim);
+        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 8, true, true>, attr, lim);
       }
       auto go = [&](auto kern) {
         kern<<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint32_t *)y, g, G, cols, TH, tiles_q,
                                      tiles_c, ntiles, run_len, run_total, act_lo, act_hi, act_flags,
                                      act_hi2);
       };
-      if (f16) {
+      if (h2) {
+        if (ST == 1) go(depthwise3x3_tile_kernel<1, true, 8, true, true>);
+        else go(depthwise3x3_tile_kernel<2, true, 8, true, true>);
+      } else if (f16) {
         if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true, 4, true>);
         else if (ST == 1) go(depthwise3x3_tile_kernel<1, false, 4, true>);
         else if (packed) go(depthwise3x3_tile_kernel<2, true, 4, true>);
