@@ -557,9 +557,6 @@ struct DwRow {
   uint64_t v[3][NP];   // three columns x NP channel pairs as fp32 pairs
 };
 // packed fp16 arithmetic (fp16 mode): two channels per 32-bit word, no conversions
-struct DwRowH {
-  uint32_t v[3][4];    // three columns x eight channels
-};
 __device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
   uint32_t r;
   asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
@@ -581,13 +578,7 @@ __device__ __forceinline__ uint32_t h2_from_floats(float a, float b) {
 }
 
 // CH = channels per thread: 4 (two CTAs per SM); 2 also compiles (four CTAs per SM) but is slower.
-// H2 (fp16 mode, CH = 8, bounds that fp16 holds exactly): the thread owns all eight channels of
-// a 16-byte piece and computes on packed fp16 pairs as they lie in memory -- nine fma.rn.f16x2
-// per pair and output, sums kept in fp16 -- which cuts the instructions per output from about
-// 22 to about 7 and leaves the kernel to the memory system.  The sum of nine products of
-// values that the 1x1 layers then average is rounded to 11 bits nine times: below the 16-bit
-// storage rounding of the other layers, and inside the mode's 2e-2 on the logits (tested).
-template <int ST, bool PACKED_ACT, int CH, bool F16, bool H2 = false>
+template <int ST, bool PACKED_ACT, int CH, bool F16>
 __global__ void __launch_bounds__(256, CH == 2 ? 4 : 2) depthwise3x3_tile_kernel(
     const uint4 *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
     uint32_t *__restrict__ y, ConvGeom g, int G, int cols, int TH, int tiles_q, int tiles_c, int ntiles,
@@ -656,37 +647,11 @@ __global__ void __launch_bounds__(256, CH == 2 ? 4 : 2) depthwise3x3_tile_kernel
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
 
-  static_assert(!H2 || (CH == 8 && F16 && PACKED_ACT), "packed fp16 arithmetic: eight channels, fp16");
-  constexpr int NW = H2 ? 9 : 1, NV = H2 ? 1 : 9;   // only one of the two weight sets exists
-  uint32_t wh[NW][4];    // H2: nine taps x eight channels as fp16 pairs
-  uint32_t bh[4] = {0u, 0u, 0u, 0u};
-  uint64_t wv[NV][NP];
+  uint64_t wv[9][NP];
   uint64_t bv[NP];
 #pragma unroll
   for (int j = 0; j < NP; ++j) bv[j] = 0;
-  if constexpr (H2) {
-#pragma unroll
-    for (int t = 0; t < 9; ++t) {
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-      if (active) {
-        const float4 *wp = (const float4 *)(w + (int64_t)t * g.C + c8 * 8);
-        a = wp[0];
-        b = wp[1];
-      }
-      wh[t][0] = h2_from_floats(a.x, a.y);
-      wh[t][1] = h2_from_floats(a.z, a.w);
-      wh[t][2] = h2_from_floats(b.x, b.y);
-      wh[t][3] = h2_from_floats(b.z, b.w);
-    }
-    if (active && bias) {
-      const float4 *bp = (const float4 *)(bias + c8 * 8);
-      const float4 a = bp[0], b = bp[1];
-      bh[0] = h2_from_floats(a.x, a.y);
-      bh[1] = h2_from_floats(a.z, a.w);
-      bh[2] = h2_from_floats(b.x, b.y);
-      bh[3] = h2_from_floats(b.z, b.w);
-    }
-  } else if (active) {
+  if (active) {
 #pragma unroll
     for (int t = 0; t < 9; ++t) {
       const float2 *wp = (const float2 *)(w + (int64_t)t * g.C + c8 * 8 + sub * CH);
@@ -728,63 +693,6 @@ __global__ void __launch_bounds__(256, CH == 2 ? 4 : 2) depthwise3x3_tile_kernel
       const uint32_t *src = reinterpret_cast<const uint32_t *>(dw_smem + buf * stage_vecs) +
                             ((col * ST) * G + gl) * 4 + sub * NP;
       uint32_t *yout = y + ((int64_t)n * g.P * g.Q + q) * C8 * 4 + c8 * 4 + sub * NP;
-      if constexpr (H2) {
-        auto load_row = [&](int ih, DwRowH &r) {
-#pragma unroll
-          for (int k = 0; k < 3; ++k) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(src + (ih * IW + k) * G * 4);
-            r.v[k][0] = v.x;
-            r.v[k][1] = v.y;
-            r.v[k][2] = v.z;
-            r.v[k][3] = v.w;
-          }
-        };
-        auto emit = [&](int p, const DwRowH &a, const DwRowH &bq, const DwRowH &cq) {
-          if (p >= g.P) return;
-          uint32_t o[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t f = bh[j];
-#pragma unroll
-            for (int k = 0; k < 3; ++k) f = h2_fma(a.v[k][j], wh[k][j], f);
-#pragma unroll
-            for (int k = 0; k < 3; ++k) f = h2_fma(bq.v[k][j], wh[3 + k][j], f);
-#pragma unroll
-            for (int k = 0; k < 3; ++k) f = h2_fma(cq.v[k][j], wh[6 + k][j], f);
-            if (act_flags & 1) f = h2_max_nan(f, 0u);
-            if (act_flags & 2) f = h2_min_nan(f, act_hi2);
-            o[j] = f;
-          }
-          *reinterpret_cast<uint4 *>(yout + (int64_t)p * g.Q * C8 * 4) = make_uint4(o[0], o[1], o[2], o[3]);
-        };
-        DwRowH r0, r1, r2;
-        const int pbase = t * TH;
-        if (ST == 1) {
-          load_row(0, r0);
-          load_row(1, r1);
-          for (int pl = 0; pl < TH; pl += 3) {
-            load_row(pl + 2, r2);
-            emit(pbase + pl, r0, r1, r2);
-            load_row(pl + 3, r0);
-            emit(pbase + pl + 1, r1, r2, r0);
-            load_row(pl + 4, r1);
-            emit(pbase + pl + 2, r2, r0, r1);
-          }
-        } else {
-          load_row(0, r0);
-          for (int pl = 0; pl < TH; pl += 3) {
-            load_row(2 * pl + 1, r1);
-            load_row(2 * pl + 2, r2);
-            emit(pbase + pl, r0, r1, r2);
-            load_row(2 * pl + 3, r0);
-            load_row(2 * pl + 4, r1);
-            emit(pbase + pl + 1, r2, r0, r1);
-            load_row(2 * pl + 5, r2);
-            load_row(2 * pl + 6, r0);
-            emit(pbase + pl + 2, r1, r2, r0);
-          }
-        }
-      } else {
       auto load_row = [&](int ih, DwRow<NP> &r) {
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
@@ -849,7 +757,6 @@ __global__ void __launch_bounds__(256, CH == 2 ? 4 : 2) depthwise3x3_tile_kernel
           load_row(2 * pl + 6, r0);
           emit(pbase + pl + 2, r1, r2, r0);
         }
-      }
       }
     }
     buf = buf == 2 ? 0 : buf + 1;
@@ -1085,7 +992,7 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
       count(CNT_LAUNCHES);
       return;
     }
-    const int CH = h2 ? 8 : 4;
+    const int CH = 4;
     const int LG = 8 / CH;
     // Geometry: G channel groups x `cols` columns per CTA (G * cols * LG <= 256 threads) and TH
     // output rows per staged tile (a multiple of 3, the register rotation; three buffers within
@@ -1161,18 +1068,13 @@ void launch_depthwise_bf16(const bf16 *x, const float *w_rsc, const float *bias,
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, false, 4, true>, attr, lim);
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 4, true>, attr, lim);
         cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, false, 4, true>, attr, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<1, true, 8, true, true>, attr, lim);
-        cudaFuncSetAttribute(depthwise3x3_tile_kernel<2, true, 8, true, true>, attr, lim);
       }
       auto go = [&](auto kern) {
         kern<<<grid, 256, smem, s>>>((const uint4 *)x, w_rsc, bias, (uint32_t *)y, g, G, cols, TH, tiles_q,
                                      tiles_c, ntiles, run_len, run_total, act_lo, act_hi, act_flags,
                                      act_hi2);
       };
-      if (h2) {
-        if (ST == 1) go(depthwise3x3_tile_kernel<1, true, 8, true, true>);
-        else go(depthwise3x3_tile_kernel<2, true, 8, true, true>);
-      } else if (f16) {
+      if (f16) {
         if (ST == 1 && packed) go(depthwise3x3_tile_kernel<1, true, 4, true>);
         else if (ST == 1) go(depthwise3x3_tile_kernel<1, false, 4, true>);
         else if (packed) go(depthwise3x3_tile_kernel<2, true, 4, true>);
