@@ -514,6 +514,57 @@ def test_conv_on_cta_pairs(case, mode, act_mode):
     assert err.max() <= TOL[mode]
 
 
+# (N, C, H, W, stride): several strips per column, odd sizes, channel counts whose 16-byte pieces
+# are not a power of two, images smaller than a strip, stride 2 with even and odd extents
+DW_STRIP_CASES = [(2, 32, 33, 17, 1), (2, 96, 29, 29, 2), (1, 144, 56, 56, 1), (3, 8, 7, 7, 1),
+                  (1, 24, 40, 12, 2), (2, 40, 112, 20, 1), (1, 960, 7, 7, 1), (2, 16, 3, 3, 1)]
+
+
+@pytest.mark.parametrize("case", DW_STRIP_CASES)
+def test_depthwise_fp16_register_strips(case):
+    """fp16 mode runs 3x3 depthwise convolutions on packed fp16 pairs, a thread walking down a
+    strip of rows: sums are kept in fp16, so the bound is tighter than the mode's 2e-2 but looser
+    than one rounding (nine roundings to 11 bits plus the stored output's)."""
+    N, C, H, W, st = case
+    r = rng(hash(case) % 2**31)
+    x = r.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = he(r, C, 1, 3, 3)
+    rt.set_math_mode(rt.MATH_F16)
+    c0 = rt.counters()
+    y = A.conv(A.up(x), A.up(w), None, (1, 1), (st, st), C, None).numpy()
+    assert rt.counters()["launches"] > c0["launches"]
+    x16 = x.astype(np.float16).astype(np.float32)
+    w16 = w.astype(np.float16).astype(np.float32)
+    want = ref.conv2d(x16, w16, None, (1, 1), (st, st), C, act=5)
+    assert y.shape == want.shape
+    assert max_rel_err(y, want) <= 4e-3
+
+
+# (N, C, H, W, K): layers with one channel tile and tiny weights (fetched once per CTA) and with
+# 32-channel tiles (two CTAs per SM), large enough that every CTA walks through several tiles
+FEW_CHANNEL_CASES = [(4, 32, 112, 112, 16), (2, 16, 112, 112, 96), (6, 144, 56, 56, 24),
+                     (8, 96, 56, 56, 24), (16, 192, 28, 28, 32)]
+
+
+@pytest.mark.parametrize("mode", [rt.MATH_BF16, rt.MATH_F16])
+@pytest.mark.parametrize("case", FEW_CHANNEL_CASES)
+@pytest.mark.parametrize("act_mode", [1, 3])
+def test_conv_with_few_channels(case, mode, act_mode):
+    N, C, H, W, K = case
+    r = rng(hash(case) % 2**31)
+    x = r.uniform(-1, 1, (N, C, H, W)).astype(np.float32)
+    w = he(r, K, C, 1, 1)
+    b = r.normal(0, 0.5, K).astype(np.float32)
+    rt.set_math_mode(mode)
+    y = A.conv(A.up(x), A.up(w), A.up(b), (0, 0), (1, 1), 1, act_mode).numpy()
+    lo, hi = (0.0, 6.0) if act_mode == 3 else (0.0, 0.0)
+    want = ref.conv2d(x, w, b, (0, 0), (1, 1), 1, act=act_mode, lo=lo, hi=hi)
+    assert np.isfinite(y).all()
+    # per image, so that a tile written to the wrong place or not at all cannot hide
+    err = np.abs(y - want).reshape(N, -1).max(axis=1) / np.abs(want).max()
+    assert err.max() <= TOL[mode]
+
+
 def test_fp32_mode_runs_on_the_tensor_cores():
     """fp32 mode, dense 3x3 and 1x1 convolutions and the classifier GEMM: tensor-core launches
     are counted, no CUDA-core convolution / GEMM launch is, and the result is within the fp32
