@@ -178,7 +178,8 @@ int64_t *CUDATranspose6DInt64Func(int64_t *in, int64_t *dimIn, int64_t *out, int
  *     than bf16 (the precision of TF32) at the same speed and bytes, for networks whose
  *     activations stay below 65504 in magnitude -- MobileNetV2, whose ReLU6 bounds them, needs
  *     it to stay within 2e-2.  A value beyond that range becomes infinity, never a silently
- *     wrong finite number.
+ *     wrong finite number.  In this mode the 3x3 depthwise convolution also keeps its sums of
+ *     nine products in fp16 (all other kernels accumulate in fp32 in both 16-bit modes).
  * Also settable with the environment variable OCCAMY_MATH=fp32|bf16|fp16 before the first
  * call. */
 void occamy_set_math_mode(int mode);

@@ -56,7 +56,7 @@ def _bf16_tensor(h, rng, N, Cc, H, W):
     return y
 
 
-def run(batch=256, reps=20, only="", math=rt.MATH_BF16):
+def run(batch=256, reps=20, only="", math=rt.MATH_BF16, role_timers=False):
     """Times the rows whose name contains one of the comma-separated pieces of `only` (all rows
     when empty); returns [(name, algorithmic MB, ms, GB/s, fraction of the copy bandwidth)] and
     the peak used."""
@@ -77,10 +77,26 @@ def run(batch=256, reps=20, only="", math=rt.MATH_BF16):
     peak, peak_src = _hbm_peak()
     B = args.batch
     rows = []
+    # Analysis builds of the library (-DOCCAMY_TC_TIMERS) count, for CTA 0 of every tensor-core
+    # convolution launch, the cycles each role spends in its barrier waits and in total.
+    timers = None
+    if role_timers:
+        raw = C.CDLL(rt.LIB_PATH)
+        if not hasattr(raw, "occamy_tc_timers"):
+            raise SystemExit("--role-timers needs a library built with OCCAMY_NVCC_EXTRA=-DOCCAMY_TC_TIMERS")
+        raw.occamy_tc_timers.argtypes = [C.POINTER(C.c_longlong), C.c_int]
+        tbuf = (C.c_longlong * 20)()
+        timers = lambda: (raw.occamy_tc_timers(tbuf, 1), list(tbuf))[1]
+    ROLES = (("loads", ("ring slot free",)), ("MMA issue", ("accumulator free", "operands landed")),
+             ("epilogue 0", ("accumulator full", "slab buffer ready")),
+             ("epilogue 1", ("accumulator full", "slab buffer ready")),
+             ("slab store 0", ("slab written", "earlier store read out")))
 
     def timed(name, nbytes, fn):
         if wanted and not any(t in name for t in wanted):
             return
+        if timers:
+            timers()
         for _ in range(3):
             fn()
         ms = []
@@ -96,6 +112,13 @@ def run(batch=256, reps=20, only="", math=rt.MATH_BF16):
         t = statistics.median(ms)
         gbs = nbytes / t / 1e6
         rows.append((name, nbytes / 1e6, t, gbs, gbs / peak))
+        if timers:
+            v = timers()
+            for i, (role, kinds) in enumerate(ROLES):
+                total = v[4 * i + 3]
+                if total:
+                    waits = ", ".join(f"{k} {v[4 * i + j] / total:.2f}" for j, k in enumerate(kinds))
+                    print(f"#   {name}: {role:12s} share of its time waiting for: {waits}")
         err = rt.last_error()
         if err:
             raise SystemExit(f"{name}: runtime error {err}")
@@ -255,10 +278,13 @@ def main():
     ap.add_argument("--only", default="", help="run only the rows whose name contains one of "
                                                "these comma-separated pieces of text")
     ap.add_argument("--math", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--role-timers", action="store_true",
+                    help="print the per-role wait shares of the tensor-core convolution kernel "
+                         "(needs a library built with OCCAMY_NVCC_EXTRA=-DOCCAMY_TC_TIMERS)")
     args = ap.parse_args()
     B = args.batch
     rows, peak, peak_src = run(B, args.reps, args.only,
-                               rt.MATH_BF16 if args.math == "bf16" else rt.MATH_F16)
+                               rt.MATH_BF16 if args.math == "bf16" else rt.MATH_F16, args.role_timers)
     lines = [f"# memory-bound operator kernels through the C ABI, batch {B}, {args.math} mode; "
              f"peak = {peak:.0f} GB/s ({peak_src} copy bandwidth)",
              "# op | MB (algorithmic) | ms | GB/s | frac of peak"]
