@@ -1197,6 +1197,29 @@ inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t
   if (tc_first_use_on_device(attr_done))
     cudaFuncSetAttribute(tc_conv_kernel<BN, DC, EW, MODE>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
+  if constexpr (EW == 1) {
+    // Two CTAs per SM are what the launch was sized for.  Every CTA of a launch has to be
+    // resident from the start: a kernel launched behind this one allocates its TMEM before it
+    // waits for this one to finish, so a CTA of this launch that started late could wait for
+    // TMEM that is only freed after it has run.  If the device grants one CTA per SM at this
+    // shared-memory size (asked once per size), the grid is cut to one wave of those.
+    static size_t asked_smem[TC_MAX_DEVICES] = {};
+    static int per_sm[TC_MAX_DEVICES] = {}, sms[TC_MAX_DEVICES] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < TC_MAX_DEVICES) {
+      if (asked_smem[dev] != smem) {
+        int n = 0, m = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tc_conv_kernel<BN, DC, EW, MODE>,
+                                                          tc_block_threads(EW), smem) != cudaSuccess)
+          n = 1;
+        cudaDeviceGetAttribute(&m, cudaDevAttrMultiProcessorCount, dev);
+        per_sm[dev] = n < 1 ? 1 : (n > 2 ? 2 : n);
+        sms[dev] = m;
+        asked_smem[dev] = smem;
+      }
+      if (sms[dev] > 0 && grid > per_sm[dev] * sms[dev]) grid = per_sm[dev] * sms[dev];
+    }
+  }
   tc_launch_pdl(tc_conv_kernel<BN, DC, EW, MODE>, grid, tc_block_threads(EW), smem,
                 s, p, (MODE & TC_MODE_PAIR) ? 2 : 1);
 }

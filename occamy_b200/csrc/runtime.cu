@@ -185,28 +185,47 @@ void *scratch_get(int slot, size_t bytes) {
 }
 
 uint64_t host_hash(const void *src, size_t bytes) {
-  // Fingerprint used to notice that a host buffer taken for a constant has changed: FNV-1a
-  // over the length, the first and last 512 bytes, and 64-byte blocks spread evenly over the
-  // whole buffer (up to 256 of them), so that a change in the interior is seen too.  A few
-  // tens of kilobytes are read whatever the size of the constant.
+  // Fingerprint used to notice that a host buffer taken for a constant has changed: a
+  // multiplicative hash over the length, the first and last 512 bytes, and 64-byte blocks
+  // spread evenly over the whole buffer (up to 256 of them), so that a change in the interior
+  // is seen too.  A few tens of kilobytes are read whatever the size of the constant.  Eight
+  // bytes per step in four independent lanes: this runs for every constant of every inference
+  // (a byte-serial hash cost 20 us per constant, 2 ms per ResNet-50 inference, and made small
+  // batches host-bound).
   const unsigned char *b = (const unsigned char *)src;
-  uint64_t h = 1469598103934665603ull ^ bytes;
+  uint64_t lane[4] = {1469598103934665603ull ^ bytes, 0x9e3779b97f4a7c15ull, 0xc2b2ae3d27d4eb4full,
+                      0x165667b19e3779f9ull};
   auto mix = [&](size_t lo, size_t hi) {
-    for (size_t i = lo; i < hi; ++i) h = (h ^ b[i]) * 1099511628211ull;
+    size_t i = lo;
+    for (; i + 32 <= hi; i += 32) {
+      uint64_t w[4];
+      memcpy(w, b + i, 32);
+      for (int j = 0; j < 4; ++j) lane[j] = (lane[j] ^ w[j]) * 1099511628211ull;
+    }
+    for (int j = 0; i < hi; ++i, j = (j + 1) & 3) lane[j] = (lane[j] ^ b[i]) * 1099511628211ull;
   };
   const size_t head = bytes < 512 ? bytes : 512;
   mix(0, head);
   if (bytes > 512) mix(bytes - 512 > head ? bytes - 512 : head, bytes);
   if (bytes > 1024) {
     const size_t inner = bytes - 1024;
-    const size_t blocks = inner / 64 < 256 ? inner / 64 : 256;
+    size_t blocks = inner / 64 < 256 ? inner / 64 : 256;
+#ifdef OCCAMY_TUNING
+    static const int forced = getenv("OCCAMY_HASH_BLOCKS") ? atoi(getenv("OCCAMY_HASH_BLOCKS")) : -1;
+    if (forced >= 0 && (size_t)forced < blocks) blocks = (size_t)forced;
+#endif
     for (size_t k = 0; k < blocks; ++k) {
       // block k starts at an even share of the interior, rounded down to 8 bytes
       const size_t at = 512 + ((inner - 64) * k / (blocks > 1 ? blocks - 1 : 1) & ~(size_t)7);
       mix(at, at + 64);
     }
   }
-  return h;
+  uint64_t h = lane[0];
+  for (int j = 1; j < 4; ++j) {
+    h ^= lane[j] + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+    h *= 1099511628211ull;
+  }
+  return h ^ (h >> 29);
 }
 
 }  // namespace occ
