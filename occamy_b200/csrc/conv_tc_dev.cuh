@@ -9,6 +9,7 @@
 
 #include <cmath>
 #include <cstdint>
+#include <type_traits>
 
 namespace occ {
 
@@ -794,6 +795,66 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
       } else {
       TCT_DECL
       if (bres && !mbar_wait_hot(wfull_bar, 0, abort_flag)) err_code = 3;
+      if constexpr (!SPLIT) {
+        // This thread's instruction stream is the kernel's critical path on the tensor-bound
+        // layers: the tensor pipe takes MMAs in order and holds very few that have not started,
+        // so every instruction between the last MMA of one k-step and the first of the next is
+        // time the pipe runs dry (an extra loop and a flag per k-step measured 17 % on the 3x3
+        // layers).  Hence: one copy of the tile loop per number of MMAs in a k-step, the
+        // k-step body straight-line, descriptors as 32-bit halves that advance by adding, the
+        // accumulate flag a predicate.
+        const uint64_t a0 = make_smem_desc(sA, bk), b0 = make_smem_desc(sB, bk);
+        const uint32_t a_hi = (uint32_t)(a0 >> 32), b_hi = (uint32_t)(b0 >> 32);
+        const uint32_t a_lo0 = (uint32_t)a0, b_lo0 = (uint32_t)b0;
+        const uint32_t a_step = a_bytes >> 4, b_step = b_bytes >> 4;   // one stage, in descriptor units
+        auto run_tiles = [&](auto nk_c) {
+          constexpr int NK = decltype(nk_c)::value;   // MMAs per k-step: bk / 16
+          uint32_t a_lo = a_lo0, b_lo = b_lo0;
+          for (int tile = tile0; tile < p.total_tiles; tile += tstep) {
+            if (!TCT_WAIT(0, mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) {
+              err_code = 2;
+              return;
+            }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
+            for (int ks = 0; ks < ksteps; ++ks) {
+              if (!TCT_WAIT(1, mbar_wait_hot(full_bar(stage), phase, abort_flag))) {
+                err_code = 3;
+                return;
+              }
+              tc_fence_after();
+              const uint32_t bl = bres ? b_lo0 + (uint32_t)ks * b_step : b_lo;
+#pragma unroll
+              for (int kk = 0; kk < NK; ++kk) {
+                const uint32_t accumulate = kk ? 1u : (uint32_t)(ks != 0);
+                if constexpr (PAIR)   // the same offsets in the other CTA hold its pixels and B half
+                  mma_lohi_pair(d_tmem, a_lo + 2u * kk, a_hi, bl + 2u * kk, b_hi, IDESC, accumulate);
+                else
+                  mma_lohi(d_tmem, a_lo + 2u * kk, a_hi, bl + 2u * kk, b_hi, IDESC, accumulate);
+              }
+              if constexpr (PAIR) tc_commit_pair(empty_bar(stage));   // frees the stage in both CTAs
+              else tc_commit(empty_bar(stage));
+              a_lo += a_step;
+              b_lo += b_step;
+              if (++stage == stages) {
+                stage = 0;
+                phase ^= 1u;
+                a_lo = a_lo0;
+                b_lo = b_lo0;
+              }
+            }
+            if constexpr (PAIR) tc_commit_pair(tfull_bar(acc));
+            else tc_commit(tfull_bar(acc));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+          }
+        };
+        if (!err_code) {
+          if (bk == 64) run_tiles(std::integral_constant<int, 4>{});
+          else if (bk == 32) run_tiles(std::integral_constant<int, 2>{});
+          else run_tiles(std::integral_constant<int, 1>{});
+        }
+      } else {
       for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
         if (!TCT_WAIT(0, mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) {
           err_code = 2;
@@ -848,6 +909,7 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
         else tc_commit(tfull_bar(acc));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+      }
       }
       TCT_FLUSH(1)
       }
