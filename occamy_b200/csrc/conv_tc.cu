@@ -128,38 +128,51 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_conv_pn_kernel(const __grid_
                              ((uint32_t)(p.n_mma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      for (int tile = blockIdx.x; tile < p.total_tiles && !err_code; tile += gridDim.x) {
-        if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          err_code = 2;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
-        uint32_t accumulate = 0;
-        for (int ks = 0; ks < ksteps; ++ks) {
-          if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
-            err_code = 3;
-            break;
+      // Straight-line k-step body, one copy of the tile loop per MMAs-per-k-step, descriptors
+      // as 32-bit halves: this thread's instructions between two k-steps are time the tensor
+      // pipe runs dry (see tc_conv_kernel).
+      const uint64_t w0 = make_smem_desc(sW, bk), x0 = make_smem_desc(sX, bk);
+      const uint32_t w_hi = (uint32_t)(w0 >> 32), x_hi = (uint32_t)(x0 >> 32);
+      const uint32_t w_lo0 = (uint32_t)w0, x_lo0 = (uint32_t)x0;
+      const uint32_t w_step = (uint32_t)w_bytes >> 4, x_step = (uint32_t)x_bytes >> 4;
+      auto run_tiles = [&](auto nk_c) {
+        constexpr int NK = decltype(nk_c)::value;
+        uint32_t w_lo = w_lo0, x_lo = x_lo0;
+        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+          if (!mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+            err_code = 2;
+            return;
           }
           tc_fence_after();
-          const uint64_t wdesc = make_smem_desc(sW + stage * w_bytes, bk);
-          const uint64_t xdesc = make_smem_desc(sX + stage * x_bytes, bk);
-          for (int kk = 0; kk < bk / 16; ++kk) {
-            tc_mma_bf16(d_tmem, wdesc + (uint64_t)(2 * kk), xdesc + (uint64_t)(2 * kk), idesc,
-                        accumulate);
-            accumulate = 1;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+          for (int ks = 0; ks < ksteps; ++ks) {
+            if (!mbar_wait_hot(full_bar(stage), phase, abort_flag)) {
+              err_code = 3;
+              return;
+            }
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < NK; ++kk)
+              mma_lohi(d_tmem, w_lo + 2u * kk, w_hi, x_lo + 2u * kk, x_hi, idesc,
+                       kk ? 1u : (uint32_t)(ks != 0));
+            tc_commit(empty_bar(stage));
+            w_lo += w_step;
+            x_lo += x_step;
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+              w_lo = w_lo0;
+              x_lo = x_lo0;
+            }
           }
-          tc_commit(empty_bar(stage));
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          tc_commit(tfull_bar(acc));
+          acc ^= 1;
+          if (acc == 0) acc_phase ^= 1u;
         }
-        if (err_code) break;
-        tc_commit(tfull_bar(acc));
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-      }
+      };
+      if (bk == 64) run_tiles(std::integral_constant<int, 4>{});
+      else if (bk == 32) run_tiles(std::integral_constant<int, 2>{});
+      else run_tiles(std::integral_constant<int, 1>{});
     }
   } else {
     const float act_lo = p.lo, act_hi = p.hi;
