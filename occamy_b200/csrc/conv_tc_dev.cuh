@@ -557,6 +557,13 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
   const uint32_t sB = sA + stages * a_bytes;
   // weight tiles: one per ring stage, or (halo form, resident form) one per k-step of a tile
   const bool bres = !HALO && !PAIR && p.b_resident != 0;
+  // Activations and weights of a k-step are requested by two threads of different warps (the
+  // weight loader is the warp that issues MMAs in the halo form, idle otherwise): one thread
+  // needs about 750 cycles for a barrier poll, the arming arrival and two TMA requests, more
+  // than the 512 cycles in which the tensor pipe finishes a 256-channel k-step.
+  constexpr bool SPLIT_LOAD = !HALO && !PAIR && EW == 2;
+  const bool two_loaders = SPLIT_LOAD && !bres;
+  constexpr int WLOAD_WARP = 2 + 4 * EW + TC_NSTORE;
   const uint32_t b_slots = HALO ? (uint32_t)p.num_taps
                                 : (bres ? (uint32_t)(p.num_taps * p.cblocks) : (uint32_t)stages);
   const uint32_t sD = sB + b_slots * b_bytes;   // dbuf output slabs
@@ -587,7 +594,7 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
     tma_prefetch_map(&p.tmB);
     if (!F32) tma_prefetch_map(&p.tmD);
     for (int s = 0; s < stages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), two_loaders ? 2 : 1);   // one arming arrival per loading thread
       mbar_init(empty_bar(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -640,7 +647,8 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
       for (int cb = 0; cb < p.cblocks; ++cb, ++i)
         tma_load_3d(sB + i * b_bytes, &p.tmB, wfull_bar, cb * bk, 0, t);
   };
-  if (!PAIR && warp == 0 && lane == 0 && p.consts_ready && (int)blockIdx.x < p.total_tiles) {
+  if (!PAIR && warp == (two_loaders ? WLOAD_WARP : 0) && lane == 0 && p.consts_ready &&
+      (int)blockIdx.x < p.total_tiles) {
     if constexpr (HALO) {
       mbar_expect_tx(wfull_bar, (uint32_t)p.num_taps * b_bytes);
       for (int t = 0; t < p.num_taps; ++t)
@@ -652,7 +660,8 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
       pre_b = min(stages, ksteps);
       int t = 0, cb = 0;
       for (int s = 0; s < pre_b; ++s) {
-        mbar_expect_tx(full_bar(s), (uint32_t)rows_valid * bk * 2u + b_bytes);
+        // a lone loader arms the barrier for both operands here; of two, each arms its own
+        mbar_expect_tx(full_bar(s), two_loaders ? b_bytes : (uint32_t)rows_valid * bk * 2u + b_bytes);
         tma_load_3d(sB + s * b_bytes, &p.tmB, full_bar(s), cb * bk, tl.k0, t);
         if (++cb == p.cblocks) {
           cb = 0;
@@ -720,7 +729,9 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
               }
               continue;
             }
-            if (pre_b > 0) {
+            if (two_loaders) {
+              mbar_expect_tx(full_bar(stage), tx_bytes - b_bytes);   // the weight loader arms its own
+            } else if (pre_b > 0) {
               --pre_b;   // this stage's barrier is armed and its weight tile on its way
             } else if (bres) {
               mbar_expect_tx(full_bar(stage), tx_bytes);   // the weights are resident
@@ -997,6 +1008,33 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
         }
         tma_store_wait_read<0>();
         if (me == 0) { TCT_FLUSH(4) }
+      }
+    }
+  } else if (SPLIT_LOAD && warp == WLOAD_WARP) {
+    // ------------------------------------------------------------ weight loader (see two_loaders)
+    if (lane == 0 && two_loaders) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
+        const TcTile tl = tc_decode<BN, PAIR>(p, tile, rank);
+        for (int t = 0; t < p.num_taps && !err_code; ++t) {
+          for (int cb = 0; cb < p.cblocks; ++cb) {
+            if (pre_b > 0) {
+              --pre_b;   // requested before the wait for the previous kernel
+            } else {
+              if (!mbar_wait_hot(empty_bar(stage), phase ^ 1u, abort_flag)) {
+                err_code = 1;
+                break;
+              }
+              mbar_expect_tx(full_bar(stage), b_bytes);
+              tma_load_3d(sB + stage * b_bytes, &p.tmB, full_bar(stage), cb * bk, tl.k0, t);
+            }
+            if (++stage == stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
       }
     }
   } else if (warp < STORE_WARP) {
