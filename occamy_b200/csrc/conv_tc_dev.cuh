@@ -806,7 +806,7 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
       } else {
       TCT_DECL
       if (bres && !mbar_wait_hot(wfull_bar, 0, abort_flag)) err_code = 3;
-      if constexpr (!SPLIT) {
+      {
         // This thread's instruction stream is the kernel's critical path on the tensor-bound
         // layers: the tensor pipe takes MMAs in order and holds very few that have not started,
         // so every instruction between the last MMA of one k-step and the first of the next is
@@ -828,6 +828,10 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
             }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * ACC_COLS);
+            // split operands: tap 0 of every group of six is hi * hi and goes to the main
+            // accumulator, the other five (corrections) to the second one
+            uint32_t seen_main = 0, seen_corr = 0;
+            int cb_in_tap = 0, combo = 0;
             for (int ks = 0; ks < ksteps; ++ks) {
               if (!TCT_WAIT(1, mbar_wait_hot(full_bar(stage), phase, abort_flag))) {
                 err_code = 3;
@@ -835,13 +839,28 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
               }
               tc_fence_after();
               const uint32_t bl = bres ? b_lo0 + (uint32_t)ks * b_step : b_lo;
+              if constexpr (SPLIT) {
+                const bool corr = combo != 0;
+                const uint32_t d = corr ? d_tmem + (uint32_t)BN : d_tmem;
+                const uint32_t first = corr ? seen_corr : seen_main;
 #pragma unroll
-              for (int kk = 0; kk < NK; ++kk) {
-                const uint32_t accumulate = kk ? 1u : (uint32_t)(ks != 0);
-                if constexpr (PAIR)   // the same offsets in the other CTA hold its pixels and B half
-                  mma_lohi_pair(d_tmem, a_lo + 2u * kk, a_hi, bl + 2u * kk, b_hi, IDESC, accumulate);
-                else
-                  mma_lohi(d_tmem, a_lo + 2u * kk, a_hi, bl + 2u * kk, b_hi, IDESC, accumulate);
+                for (int kk = 0; kk < NK; ++kk)
+                  mma_lohi(d, a_lo + 2u * kk, a_hi, bl + 2u * kk, b_hi, IDESC, kk ? 1u : first);
+                if (corr) seen_corr = 1u;
+                else seen_main = 1u;
+                if (++cb_in_tap == p.cblocks) {
+                  cb_in_tap = 0;
+                  if (++combo == 6) combo = 0;
+                }
+              } else {
+#pragma unroll
+                for (int kk = 0; kk < NK; ++kk) {
+                  const uint32_t accumulate = kk ? 1u : (uint32_t)(ks != 0);
+                  if constexpr (PAIR)   // the same offsets in the other CTA hold its pixels and B half
+                    mma_lohi_pair(d_tmem, a_lo + 2u * kk, a_hi, bl + 2u * kk, b_hi, IDESC, accumulate);
+                  else
+                    mma_lohi(d_tmem, a_lo + 2u * kk, a_hi, bl + 2u * kk, b_hi, IDESC, accumulate);
+                }
               }
               if constexpr (PAIR) tc_commit_pair(empty_bar(stage));   // frees the stage in both CTAs
               else tc_commit(empty_bar(stage));
@@ -865,62 +884,6 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
           else if (bk == 32) run_tiles(std::integral_constant<int, 2>{});
           else run_tiles(std::integral_constant<int, 1>{});
         }
-      } else {
-      for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
-        if (!TCT_WAIT(0, mbar_wait_hot(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) {
-          err_code = 2;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t d_main = tmem_base + (uint32_t)(acc * ACC_COLS);
-        uint32_t d_tmem = d_main;
-        uint32_t accumulate = 0, accumulate_corr = 0;
-        int cb_in_tap = 0, combo = 0;   // split operands: position inside the six-tap group
-        for (int ks = 0; ks < ksteps; ++ks) {
-          if (!TCT_WAIT(1, mbar_wait_hot(full_bar(stage), phase, abort_flag))) {
-            err_code = 3;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t adesc = make_smem_desc(sA + stage * a_bytes, bk);
-          const uint64_t bdesc = make_smem_desc(sB + (bres ? ks : stage) * b_bytes, bk);
-          if constexpr (SPLIT) {
-            // tap 0 of every group of six is hi * hi: main accumulator; the rest: corrections
-            const bool corr = combo != 0;
-            d_tmem = corr ? d_main + (uint32_t)BN : d_main;
-            for (int kk = 0; kk < bk / 16; ++kk) {
-              tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
-                          corr ? accumulate_corr : accumulate);
-              if (corr) accumulate_corr = 1;
-              else accumulate = 1;
-            }
-            if (++cb_in_tap == p.cblocks) {
-              cb_in_tap = 0;
-              if (++combo == 6) combo = 0;
-            }
-          } else
-          for (int kk = 0; kk < bk / 16; ++kk) {
-            if constexpr (PAIR)   // the same offsets in the other CTA hold its pixels and B half
-              mma_lohi_pair(d_tmem, (uint32_t)adesc + 2u * kk, (uint32_t)(adesc >> 32),
-                            (uint32_t)bdesc + 2u * kk, (uint32_t)(bdesc >> 32), IDESC, accumulate);
-            else
-              tc_mma_bf16(d_tmem, adesc + (uint64_t)(2 * kk), bdesc + (uint64_t)(2 * kk), IDESC,
-                          accumulate);
-            accumulate = 1;
-          }
-          if constexpr (PAIR) tc_commit_pair(empty_bar(stage));   // frees the stage in both CTAs
-          else tc_commit(empty_bar(stage));
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
-        if (err_code) break;
-        if constexpr (PAIR) tc_commit_pair(tfull_bar(acc));
-        else tc_commit(tfull_bar(acc));
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-      }
       }
       TCT_FLUSH(1)
       }

@@ -492,7 +492,8 @@ def test_fp16_mode_is_finer_than_bf16_and_overflows_to_infinity():
 # 1x1 layers large enough for the planner to choose 256-channel tiles, with at least 1024 input
 # channels: they run as CTA pairs (two SMs per 256-pixel tile).  101 images of 14 x 14 give an
 # odd number of 128-pixel tiles, so the last pair has only one real tile.
-PAIR_CASES = [(100, 1024, 14, 14, 512, 1, 0), (101, 1024, 14, 14, 256, 1, 0), (200, 2048, 7, 7, 512, 1, 0)]
+PAIR_CASES = [(100, 1024, 14, 14, 512, 1, 0), (101, 1024, 14, 14, 256, 1, 0), (200, 2048, 7, 7, 512, 1, 0),
+              (33, 256, 14, 14, 256, 3, 1), (40, 512, 7, 7, 512, 3, 1)]
 
 
 @pytest.mark.parametrize("mode", [rt.MATH_BF16, rt.MATH_F16])
