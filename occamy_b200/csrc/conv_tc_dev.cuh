@@ -1257,32 +1257,17 @@ inline bool tc_first_use_on_device(unsigned char (&done)[TC_MAX_DEVICES]) {
 template <int BN, int DC, int MODE, int EW = TC_EW>
 inline void tc_launch_one(const TcParams &p, int grid, size_t smem, cudaStream_t s) {
   static unsigned char attr_done[TC_MAX_DEVICES] = {};
-  if (tc_first_use_on_device(attr_done))
+  if (tc_first_use_on_device(attr_done)) {
     cudaFuncSetAttribute(tc_conv_kernel<BN, DC, EW, MODE>,
                          cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_LIMIT);
-  if constexpr (EW == 1) {
-    // Two CTAs per SM are what the launch was sized for.  Every CTA of a launch has to be
-    // resident from the start: a kernel launched behind this one allocates its TMEM before it
-    // waits for this one to finish, so a CTA of this launch that started late could wait for
-    // TMEM that is only freed after it has run.  If the device grants one CTA per SM at this
-    // shared-memory size (asked once per size), the grid is cut to one wave of those.
-    static size_t asked_smem[TC_MAX_DEVICES] = {};
-    static int per_sm[TC_MAX_DEVICES] = {}, sms[TC_MAX_DEVICES] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < TC_MAX_DEVICES) {
-      if (asked_smem[dev] != smem) {
-        int n = 0, m = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, tc_conv_kernel<BN, DC, EW, MODE>,
-                                                          tc_block_threads(EW), smem) != cudaSuccess)
-          n = 1;
-        cudaDeviceGetAttribute(&m, cudaDevAttrMultiProcessorCount, dev);
-        per_sm[dev] = n < 1 ? 1 : (n > 2 ? 2 : n);
-        sms[dev] = m;
-        asked_smem[dev] = smem;
-      }
-      if (sms[dev] > 0 && grid > per_sm[dev] * sms[dev]) grid = per_sm[dev] * sms[dev];
-    }
+    // all of the SM's configurable memory as shared memory: the kernel reads nothing through
+    // L1, and two CTAs of the 113 KB form fit an SM only then
+    cudaFuncSetAttribute(tc_conv_kernel<BN, DC, EW, MODE>,
+                         cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   }
+  // (A launch of the two-per-SM form whose CTAs were not all resident at once would still be
+  // safe behind a dependent launch: dependents start only after every CTA of this grid has
+  // executed launch_dependents, which comes after its TMEM allocation.)
   tc_launch_pdl(tc_conv_kernel<BN, DC, EW, MODE>, grid, tc_block_threads(EW), smem,
                 s, p, (MODE & TC_MODE_PAIR) ? 2 : 1);
 }
