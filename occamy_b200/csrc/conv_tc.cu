@@ -666,7 +666,11 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   // 6 to 9 KB of weights, slower at 8 KB (64->64) and 32 KB (64->256 with residual).
   const int ksteps_tile = p.num_taps * p.cblocks;
   const size_t b_tile_bytes = (size_t)(pair ? bn / 2 : bn) * bk * 2;
-  bool bres = !pn && !halo && !pair && p.tiles_k == 1 && ksteps_tile * b_tile_bytes <= 4 * 1024;
+  // (With two CTAs per SM the single loading thread of a CTA is what the others wait for, and
+  // weights of up to 16 KB pay as well: 144->24 at 56x56 has nine k-steps of 1 KB each.)
+  const bool duo_wanted = !pn && !halo && !pair && !a.split && !a.out_f32 && dc == 32 && bn == 32 && nsm >= 2;
+  bool bres = !pn && !halo && !pair && p.tiles_k == 1 &&
+              ksteps_tile * b_tile_bytes <= (size_t)(duo_wanted ? 16 : 4) * 1024;
 #ifdef OCCAMY_TUNING
   if (const char *f = getenv("OCCAMY_TC_BRES")) bres = bres && atoi(f) != 0;
 #endif
@@ -687,7 +691,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
   // CTAs overlap those (measured 1.2x to 1.6x on the layers with up to 32 output channels; no
   // gain for 64-channel tiles).  They share the SM's shared memory, registers (one epilogue warp per TMEM
   // quadrant, 256 threads) and TMEM (at most 256 columns each).
-  bool duo = !pn && !halo && !pair && !a.split && !a.out_f32 && dc == 32 && bn == 32 && nsm >= 2;
+  bool duo = duo_wanted;
 #ifdef OCCAMY_TUNING
   if (const char *f = getenv("OCCAMY_TC_DUO"))
     duo = atoi(f) != 0 && !pn && !halo && !pair && !a.split && !a.out_f32 && dc == 32 && bn == 32;
