@@ -915,10 +915,32 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
             }
           }
         };
-        for (uint32_t i = 0; i < me && r_tile < p.total_tiles; ++i) r_advance();
+        // Without a residual a hand-out needs no coordinates, and when every tile has the same
+        // number of slabs the count of this CTA's slabs says where to stop: no cursor at all.
+        // (This thread's instructions per slab are what the few-channel layers with wide
+        // outputs wait for; divisions by the runtime buffer count are replaced by counters
+        // that step by TC_NSTORE for the same reason.)
+        const bool uniform = !RES && (p.tiles_k == 1 || p.K % BN == 0);
+        uint32_t left = 0;   // uniform form: hand-outs this thread still owes
+        if (uniform && tile0 < p.total_tiles) {
+          const uint32_t my_tiles = (uint32_t)((p.total_tiles - tile0 + tstep - 1) / tstep);
+          const uint32_t per_tile = (uint32_t)min(NSLAB, (p.tiles_k == 1 ? p.K + DC - 1 : BN) / DC);
+          const uint32_t total = my_tiles * per_tile;
+          left = total > me ? (total - me + TC_NSTORE - 1) / TC_NSTORE : 0u;
+        }
+        if (!uniform)
+          for (uint32_t i = 0; i < me && r_tile < p.total_tiles; ++i) r_advance();
+        uint32_t rb = me;   // buffer of my next hand-out: steps by TC_NSTORE around the ring
         auto ready_one = [&]() {          // hand out slab r_next, move to my next one
+          if (uniform) {
+            if (left == 0) return;
+            --left;
+            mbar_arrive(rfull_bar(rb));
+            rb += TC_NSTORE;
+            if (rb >= (uint32_t)dbuf) rb -= (uint32_t)dbuf;
+            return;
+          }
           if (r_tile >= p.total_tiles) return;
-          const uint32_t rb = r_next % (uint32_t)dbuf;
           if constexpr (RES) {
             mbar_expect_tx(rfull_bar(rb), (uint32_t)rows_valid * DC * 2u);
             tma_load_4d(sD + rb * SLAB_BYTES, &p.tmR, rfull_bar(rb), rt_.k0 + r_sl * DC, rt_.q0,
@@ -927,11 +949,14 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
             mbar_arrive(rfull_bar(rb));
           }
           r_next += TC_NSTORE;
+          rb += TC_NSTORE;
+          if (rb >= (uint32_t)dbuf) rb -= (uint32_t)dbuf;
           for (int i = 0; i < TC_NSTORE && r_tile < p.total_tiles; ++i) r_advance();
         };
         for (int i = 0; i < dbuf / TC_NSTORE; ++i) ready_one();     // every buffer starts out free
         uint32_t d = 0;   // running slab number
         uint32_t mine = 0;   // stores this thread has issued
+        uint32_t b = me, ph = 0;   // buffer and barrier phase of my next slab
         TCT_DECL
         for (int tile = tile0; tile < p.total_tiles && !err_code; tile += tstep) {
           bool ghost = false;
@@ -939,7 +964,6 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
           const int nslab = nslab_of(tl);
           for (int sl = 0; sl < nslab; ++sl, ++d) {
             if (d % TC_NSTORE != me) continue;
-            const uint32_t b = d % (uint32_t)dbuf, ph = (d / (uint32_t)dbuf) & 1u;
             if (!TCT_WAIT(0, mbar_wait(dfull_bar(b), ph, abort_flag))) {
               err_code = 6;
               break;
@@ -967,6 +991,11 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
             tct_[1] += clock64() - tw_;
 #endif
             if (mine++ >= (uint32_t)p.store_pend) ready_one();
+            b += TC_NSTORE;
+            if (b >= (uint32_t)dbuf) {
+              b -= (uint32_t)dbuf;
+              ph ^= 1u;
+            }
           }
         }
         tma_store_wait_read<0>();
