@@ -206,7 +206,10 @@ bool prepare_dense(const float *x, const float *w, const float *bias, const Conv
     a.row_elems = Wp * Cp;
   } else {
     if (g.C % 8 != 0) return false;
-    Cp = (g.C + 15) / 16 * 16;   // the MMA takes 16 channels at a time: pad with zero channels
+    // Pixels are padded to a multiple of 32 bytes with zero channels: rows at a 48-byte pitch
+    // (24 channels) load at little more than half the speed of rows at 64 (measured:
+    // 24->144 at 56x56, 0.044 ms padded, 0.072 ms not).
+    Cp = (g.C + 15) / 16 * 16;
     a.H = g.H; a.W = g.W; a.Cf = Cp;
     a.R = g.R; a.S = g.S;
     a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
