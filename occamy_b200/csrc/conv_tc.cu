@@ -728,7 +728,7 @@ static Plan build_plan(const TcConvArgs &a, int *err_word, int num_sms, bool cou
       if (dbuf < TC_NSTORE * 2) dbuf = TC_NSTORE * 2;
     }
     // Stores in flight.  A store thread may run ahead of `pend` unfinished stores; each needs a
-    // buffer of its own on top of the ones that are filling.  The aim is about 48 KB of stores
+    // buffer of its own on top of the ones that are filling.  Sized for about 48 KB of stores
     // in flight per SM, as long as four ring stages remain: the layers with long reductions
     // need those more.
     pend = 0;

@@ -558,9 +558,9 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
   // weight tiles: one per ring stage, or (halo form, resident form) one per k-step of a tile
   const bool bres = !HALO && !PAIR && p.b_resident != 0;
   // Activations and weights of a k-step are requested by two threads of different warps (the
-  // weight loader is the warp that issues MMAs in the halo form, idle otherwise): one thread
-  // needs about 750 cycles for a barrier poll, the arming arrival and two TMA requests, more
-  // than the 512 cycles in which the tensor pipe finishes a 256-channel k-step.
+  // weight loader is the warp that issues MMAs in the halo form, idle otherwise): a lone loading
+  // thread was busy 78 % of the time on the 3x3 layers (barrier poll, arming arrival and two
+  // TMA requests per k-step).  Measured 3 % on those layers, nothing elsewhere.
   constexpr bool SPLIT_LOAD = !HALO && !PAIR && EW == 2;
   const bool two_loaders = SPLIT_LOAD && !bres;
   constexpr int WLOAD_WARP = 2 + 4 * EW + TC_NSTORE;
@@ -971,13 +971,13 @@ __global__ void __launch_bounds__(tc_block_threads(EW), EW == 1 ? 2 : 1)
             if (!ghost)   // the duplicate tile of an odd last pair is computed, not stored
               tma_store_4d(&p.tmD, sD + b * SLAB_BYTES, tl.k0 + sl * DC, tl.q0, tl.p0, tl.n0);
             tma_store_commit();
-            // A store gives its buffer back only after about a memory latency (1 to 2 us
-            // under load), and the bytes of the stores in flight over that time are what
-            // bounds the write bandwidth of an SM: with narrow slabs one store per thread is
-            // far too little.  So up to store_pend of my earlier stores may still be reading
-            // their buffers; the one before those is done, and its buffer goes to the slab
-            // dbuf further on.  Every buffer that is not in a store is then filling (residual
-            // fetch, epilogue), which is also what hides the residual's memory latency.
+            // Up to store_pend of my earlier stores may still be reading their buffers; the
+            // one before those is done, and its buffer goes to the slab dbuf further on.
+            // Every buffer that is not in a store is then filling (residual fetch, epilogue),
+            // which is also what hides the residual's memory latency.  (Waiting for each
+            // store before the next is issued costs this thread up to a quarter of its time
+            // on layers with narrow slabs; several in flight measured 6 % on 16->96 channels
+            // and nothing on the wide layers.)
 #ifdef OCCAMY_TC_TIMERS
             const long long tw_ = clock64();
 #endif
