@@ -213,7 +213,8 @@ CONV_ROWS = [("conv3x3 256->256 @14", 256, 256, 3, 14, 1, False),
              ("conv1x1 96->24 @56", 96, 24, 1, 56, 1, False),
              ("conv1x1 192->32 @28", 192, 32, 1, 28, 1, False),
              ("conv1x1 384->64 @14", 384, 64, 1, 14, 1, False),
-             ("conv1x1 576->96 @14", 576, 96, 1, 14, 1, False)]
+             ("conv1x1 576->96 @14", 576, 96, 1, 14, 1, False),
+             ("conv1x1 24->144 @56", 24, 144, 1, 56, 1, False)]
 
 
 def _conv_rows(h, rng, B, L, timed, wanted):
