@@ -364,18 +364,7 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// tcgen05.mma with each operand descriptor given as its two 32-bit halves: only the low
-// half (start address) changes from one MMA to the next, and 32-bit arithmetic keeps the
-// single issuing thread's instruction count down.
+// One MMA; the descriptors arrive as 32-bit halves (address field in the low word).
 __device__ __forceinline__ void mma_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
                                          uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
